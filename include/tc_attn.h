@@ -1,0 +1,313 @@
+/*
+ * tc_attn.h -- C ABI of the B200 attention / KV-cache library (libtc_attn.so).
+ *
+ * These entry points are the call shapes of the reference engine's GPU
+ * attention block: the kernels and host launchers that
+ * tinycoder::gpu::GPUModel (include/GPUCompute.hpp:195-331) invokes with raw
+ * device pointers inside its per-layer loops.  Each declaration names the
+ * reference launch it replaces (path inside the reference project, line range).
+ *
+ * Conventions (the reference's own, kept):
+ *   - every pointer is a DEVICE pointer owned by the caller unless the comment
+ *     says HOST; the library never allocates device memory and never
+ *     synchronises (the reference forbids allocation inside launches for CUDA
+ *     graph capture, include/gpu/GpuAttentionKernels.hpp:1133-1135);
+ *   - the stream is explicit (`tc_stream` is a cudaStream_t);
+ *   - layouts are row-major, token-major: q/out [seq][nHeads][hd] f32;
+ *     K/V cache [row][nKV][hd]; int8 pool [row][nKV][hd] int8 with scales
+ *     [row][nKV] f32; partials partAcc [seq][nHeads][numChunks][hd],
+ *     partM/partL [seq][nHeads][numChunks] (include/GPUCompute.hpp:1203-1204);
+ *   - the GQA map is kvHead = qHead / (nHeads / nKV)
+ *     (include/gpu/GpuAttentionKernels.hpp:226);
+ *   - a position may arrive as a host value or as a device scalar (`devPos`,
+ *     read at kernel time so that a captured graph can be replayed; the
+ *     reference's *Pos kernel twins, GpuAttentionKernels.hpp:355-363);
+ *   - functions return 0 on success or a TC_E* code; they never throw, abort
+ *     or fall back to a CPU path.  tc_last_error() gives the message of the
+ *     calling thread's last failure.
+ *   - not thread-safe per (stream, workspace) pair, re-entrant across distinct
+ *     pairs (one host thread per GPU may drive its own device).
+ */
+#ifndef TC_ATTN_H
+#define TC_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *tc_stream; /* cudaStream_t */
+
+enum {
+    TC_OK = 0,
+    TC_EINVAL = 1,        /* bad shape / pointer / alignment */
+    TC_ECONTEXT_FULL = 2, /* the write would pass the window: nothing was launched
+                             (GPUComputeForward.cu:3366-3372, ModelForward.cpp:57-63) */
+    TC_ECUDA = 3,         /* a CUDA runtime / driver call failed */
+    TC_EUNSUPPORTED = 4,  /* shape outside what the kernels are built for */
+    TC_EWORKSPACE = 5,    /* caller's partial buffers are too small */
+    TC_EDEVICE = 6        /* a kernel recorded a device-side error (bounded wait ran out) */
+};
+
+const char *tc_strerror(int code);
+const char *tc_last_error(void);
+/* Reads and clears the device-side error word of the current device
+ * (synchronises the given stream).  0 = no kernel gave up on a wait. */
+int tc_device_status(tc_stream stream, uint32_t *flags);
+
+/* ------------------------------------------------------------------------- */
+/* KV append                                                                   */
+/* ------------------------------------------------------------------------- */
+
+/* Replaces kQ35StoreKV (include/gpu/GpuQwen35Kernels.hpp:497-516; launch
+ * src/cpp/core/cuda/forward/GPUComputeMoE.cu:3132): rows cachePos+s of kDst/vDst
+ * receive kSrc/vSrc [seqLen][nKV*hd] verbatim.  devPos (nullable) overrides
+ * cachePos.  kvHalf != 0 stores fp16 (the KV16 cache of
+ * include/gpu/GpuElementwiseKernels.hpp:64-89).  maxRows bounds the write:
+ * cachePos + seqLen > maxRows returns TC_ECONTEXT_FULL (host position only). */
+int tc_kv_append(const float *kSrc, const float *vSrc, void *kDst, void *vDst,
+                 int kvHalf, uint32_t seqLen, uint32_t nKV, uint32_t hd,
+                 uint32_t cachePos, const uint32_t *devPos, uint32_t maxRows,
+                 tc_stream stream);
+
+/* Replaces kStoreKVRope / kStoreKVRopePos and, with q != NULL, the fused
+ * kRoPEQStoreKV / kRoPEQStoreKVPos (include/gpu/GpuElementwiseKernels.hpp:452-483;
+ * include/gpu/GpuAttentionKernels.hpp:389-533; launches
+ * GPUComputeForward.cu:3878-3895): V verbatim, K rotated NEOX-style with the
+ * angle row ropePos+s, into row cachePos+s; q [seqLen][nHeads][hd] rotated in
+ * place.  cosT/sinT: [rows][hd/2] f32.  devPos (nullable) replaces both
+ * cachePos and ropePos. */
+int tc_kv_append_rope(float *q, const float *kSrc, const float *vSrc, void *kDst,
+                      void *vDst, int kvHalf, uint32_t seqLen, uint32_t nHeads,
+                      uint32_t nKV, uint32_t hd, uint32_t cachePos,
+                      uint32_t ropePos, const uint32_t *devPos,
+                      const float *cosT, const float *sinT, uint32_t maxRows,
+                      tc_stream stream);
+
+/* Replaces kRoPEQ / kRoPEQPos (include/gpu/GpuElementwiseKernels.hpp:425-448;
+ * include/gpu/GpuAttentionKernels.hpp:364-387). */
+int tc_rope_q(float *q, const float *cosT, const float *sinT, uint32_t seqLen,
+              uint32_t nHeads, uint32_t hd, uint32_t pos, const uint32_t *devPos,
+              tc_stream stream);
+
+/* Replaces kQ35QuantKV8 (include/gpu/GpuQwen35Kernels.hpp:586-637; launches
+ * GPUComputeMoE.cu:3056-3063, 3103-3105): quantise rows srcTokenBase+t of the
+ * f32 k/v [row][nKV][hd] into rows dstTokenBase+t of the int8 pool, one f32
+ * scale per (row, kv head): scale = amax/127 (1 when amax == 0),
+ * q = clamp(lrintf(x/scale), -128, 127).  Bit-exact with the reference.
+ * devDstBase (nullable) overrides dstTokenBase at kernel time. */
+int tc_kv_quantize_i8(const float *k, const float *v, int8_t *k8, int8_t *v8,
+                      float *ks, float *vs, uint32_t tokens, uint32_t nKV,
+                      uint32_t hd, uint64_t dstTokenBase, uint64_t srcTokenBase,
+                      const uint32_t *devDstBase, uint64_t maxRows,
+                      tc_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* decode attention                                                            */
+/* ------------------------------------------------------------------------- */
+
+/* Bytes of partial storage for one decode call: fills the three sizes (in
+ * bytes) the caller must give pAcc / pM / pL for `batch` sequences and
+ * `numChunks` chunk slots (the reference sizes them in
+ * src/cpp/core/cuda/forward/GPUComputeUpload.cu:354-365 for one token). */
+int tc_attn_workspace_bytes(uint32_t batch, uint32_t nHeads, uint32_t hd,
+                            uint32_t numChunks, size_t *accBytes,
+                            size_t *mBytes, size_t *lBytes);
+
+/* Chunk grid the library would pick for a window: the reference's
+ * attnChunk_/attnChunks_ rule (GPUComputeUpload.cu:318-334; at most 512 chunks,
+ * chunk a multiple of 32).  The decode entry points accept any numChunks >= 1;
+ * they use at most numChunks chunk slots and choose their own tiling inside. */
+int tc_split_geometry(uint32_t maxSeqLen, uint32_t nHeads, uint32_t hd,
+                      uint32_t *chunkSize, uint32_t *numChunks);
+
+/* Replaces kQ35WarpAttention8Split + kAttnCombinePartial, and the eager
+ * kQ35WarpAttention8 (include/gpu/GpuQwen35Kernels.hpp:519-581, 641-692;
+ * launches GPUComputeMoE.cu:3073-3090): one query token, attention over rows
+ * [0, cachePos] of an int8 store, out [nHeads][hd] f32.  devPos (nullable)
+ * overrides cachePos at kernel time (then cachePos is the host's upper bound
+ * and sizes the grid).  pAcc/pM/pL hold numChunks chunk slots per head;
+ * chunkSize is the caller's chunk (a hint: the kernel tiles the range itself).
+ * totalRows = rows allocated in the pool (>= cachePos+1). */
+int tc_attn_decode_i8(const float *q, const int8_t *k8, const int8_t *v8,
+                      const float *ks, const float *vs, float *out, float *pAcc,
+                      float *pM, float *pL, uint32_t nHeads, uint32_t nKV,
+                      uint32_t hd, uint32_t cachePos, const uint32_t *devPos,
+                      uint64_t totalRows, uint32_t numChunks, uint32_t chunkSize,
+                      float invSqrt, tc_stream stream);
+
+/* Batched form of the above for `batch` independent sequences that live in ONE
+ * int8 pool (the serving mix: one decode step of many sessions).  Sequence b
+ * occupies pool rows [rowBase[b], rowBase[b] + lens[b]); rowBase == NULL means
+ * b * rowsPerSeq.  lens / rowBase are DEVICE arrays (uint32 / uint64); maxLen is
+ * the host's upper bound on lens[] and sizes the grid.  q/out: [batch][nHeads][hd].
+ * partialsOnly != 0 skips the merge and leaves (m, l, acc) per chunk in
+ * pAcc/pM/pL -- the form a context-axis split across GPUs exchanges;
+ * *chunksUsed (HOST, nullable) receives the chunk slots written per head. */
+typedef struct tc_decode_i8_batch {
+    const float *q;
+    float *out;
+    const int8_t *k8, *v8;
+    const float *ks, *vs;
+    float *pAcc, *pM, *pL;
+    const uint32_t *lens;    /* device [batch] */
+    const uint64_t *rowBase; /* device [batch] or NULL */
+    uint64_t rowsPerSeq;
+    uint64_t totalRows;
+    uint32_t batch, nHeads, nKV, hd;
+    uint32_t maxLen;
+    uint32_t numChunks;
+    float invSqrt;
+    int partialsOnly;
+    uint32_t *chunksUsed; /* HOST out, nullable */
+} tc_decode_i8_batch;
+
+int tc_attn_decode_i8_batch(const tc_decode_i8_batch *d, tc_stream stream);
+
+/* Replaces launchDecodeAttentionSplit (include/gpu/GpuAttentionKernels.hpp:
+ * 1129-1230; launch GPUComputeForward.cu:3897-3902): split-KV decode over an
+ * f32 (kvHalf == 0) or fp16 (kvHalf != 0) cache, seqLen query rows (the
+ * reference only calls it with seqLen == 1), row s attends [0, pos + s].
+ * q81Out (nullable): the merge also emits the Q8_1 blocks of the output
+ * (40-byte slots per 32 values, GpuAttentionKernels.hpp:1068-1096). */
+int tc_attn_decode_kv(const float *q, const void *kvK, const void *kvV,
+                      float *attnOut, float *pAcc, float *pM, float *pL,
+                      uint32_t seqLen, uint32_t nHeads, uint32_t nKV, uint32_t hd,
+                      uint32_t pos, const uint32_t *devPos, uint64_t totalRows,
+                      uint32_t numChunks, uint32_t chunkSize, float invSqrt,
+                      int kvHalf, uint8_t *q81Out, tc_stream stream);
+
+/* Replaces kAttnCombinePartial / kAttnCombinePartialW4
+ * (include/gpu/GpuAttentionKernels.hpp:909-946, 1003-1098): merge numChunks
+ * partials per (token, head): M = max m_c, w_c = exp2((m_c-M)*log2e), chunks
+ * with l_c <= 0 skipped, out = sum w_c acc_c / sum w_c l_c.  Also the merge
+ * step of a context split across GPUs (numChunks = gathered partials). */
+int tc_attn_merge_partials(const float *pAcc, const float *pM, const float *pL,
+                           float *out, uint32_t seqLen, uint32_t nHeads,
+                           uint32_t numChunks, uint32_t hd, uint8_t *q81Out,
+                           tc_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* prefill attention                                                           */
+/* ------------------------------------------------------------------------- */
+
+/* Scratch bytes tc_attn_prefill_f16 needs (fp16 twins of q and of the K/V
+ * rows; the reference keeps attnQ16 / attnKV16 for the same purpose,
+ * GPUComputeForward.cu:3952-3968). */
+int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t nHeads,
+                                      uint32_t nKV, uint32_t hd, size_t *bytes);
+
+/* Replaces the materialised dense prefill: kF32ToF16 x3, cuBLAS QK^T,
+ * kAttnSoftmaxCausal, cuBLAS PV (GPUComputeForward.cu:3937-4026;
+ * include/gpu/GpuAttentionKernels.hpp:323-353): causal attention of seqLen
+ * query rows over cache rows [0, seqLen) (cachePos == 0), fp16 operands,
+ * f32 accumulation, f32 softmax, probabilities rounded to fp16.  q f32
+ * [seqLen][nHeads][hd]; kvK/kvV f32 cache rows; out f32.  No seqLen cap (the
+ * reference stops at 512 because it materialises the score matrix). */
+int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV,
+                        float *out, void *scratch, size_t scratchBytes,
+                        uint32_t seqLen, uint32_t nHeads, uint32_t nKV,
+                        uint32_t hd, float invSqrt, tc_stream stream);
+
+/* Replaces kWarpAttention / kWarpAttentionPos and kQ35WarpAttention
+ * (include/gpu/GpuAttentionKernels.hpp:211-272, 537-599;
+ * include/gpu/GpuQwen35Kernels.hpp:2437-2492): causal attention of seqLen query
+ * rows, row s over cache rows [0, cachePos + s], f32 or fp16 cache, f32 math. */
+int tc_attn_prefill_kv(const float *q, const void *kvK, const void *kvV,
+                       float *out, uint32_t seqLen, uint32_t nHeads,
+                       uint32_t nKV, uint32_t hd, uint32_t cachePos,
+                       const uint32_t *devPos, uint64_t totalRows, float invSqrt,
+                       int kvHalf, tc_stream stream);
+
+/* Replaces kQ35WarpAttention8Prefill / kQ35PrefillAttnSharedKV8
+ * (include/gpu/GpuQwen35Kernels.hpp:2306-2435; launches GPUComputeMoE.cu:
+ * 3110-3130): causal attention of seqLen query rows over an int8 store. */
+int tc_attn_prefill_i8(const float *q, const int8_t *k8, const int8_t *v8,
+                       const float *ks, const float *vs, float *out,
+                       uint32_t seqLen, uint32_t nHeads, uint32_t nKV,
+                       uint32_t hd, uint32_t cachePos, const uint32_t *devPos,
+                       uint64_t totalRows, float invSqrt, tc_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* attention-output epilogues                                                  */
+/* ------------------------------------------------------------------------- */
+
+/* Replaces kQ35SigmoidGate (include/gpu/GpuQwen35Kernels.hpp:479-493):
+ * attnOut[s][h][e] *= sigmoid(qGate[s][h][hd + e]), qGate rows [nHeads][2*hd]. */
+int tc_attn_sigmoid_gate(float *attnOut, const float *qGate, uint32_t seqLen,
+                         uint32_t nHeads, uint32_t hd, tc_stream stream);
+
+/* ------------------------------------------------------------------------- */
+/* context planner (host only, no CUDA)                                        */
+/* ------------------------------------------------------------------------- */
+
+enum { TC_KV_F32 = 0, TC_KV_I8 = 1 };
+
+/* POD mirror of tinycoder::detail::ContextRequest (include/ContextPlan.hpp:21-61). */
+typedef struct tc_context_request {
+    uint32_t requested;          /* 0 = auto (2048) */
+    uint32_t modelMax;           /* 0 = unknown (4096 assumed) */
+    uint32_t numLayers;
+    uint32_t numAttentionLayers; /* layers that own K/V slots */
+    uint32_t numKVHeads;
+    uint32_t headDim;
+    uint32_t ropeDims;           /* cos/sin row width */
+    uint32_t int8KvSupported;
+    uint32_t forceKv;            /* TC_KV_F32 / TC_KV_I8, honoured when forceKvSet */
+    uint32_t forceKvSet;
+    uint64_t weightBytes;
+    uint64_t freeVram;           /* 0 = no usable GPU */
+    uint64_t availableRam;
+    uint64_t gpuFixedOverhead;   /* tc_context_request_init sets the default */
+} tc_context_request;
+
+/* POD mirror of tinycoder::detail::ContextPlan (include/ContextPlan.hpp:65-72);
+ * `reason` is the sentence the engine prints. */
+typedef struct tc_context_plan {
+    uint32_t seqLen;     /* granted window; 0 = nothing fits */
+    uint32_t maxAllowed; /* largest fit of the whole ladder */
+    uint32_t kv;         /* TC_KV_F32 / TC_KV_I8 */
+    uint32_t kvMirror;   /* f32 store + int8 decode mirror */
+    uint32_t kvOnGpu;
+    uint32_t reduced;    /* the request was cut to what memory holds */
+    uint64_t kvBytes;
+    char reason[256];
+} tc_context_plan;
+
+void tc_context_request_init(tc_context_request *r);
+/* kvBytesPerToken / kvStoreBytesPerToken (src/cpp/core/ContextPlan.cpp:58-78). */
+uint64_t tc_kv_bytes_per_token(const tc_context_request *r, uint32_t kv, uint32_t mirror);
+uint64_t tc_kv_store_bytes_per_token(const tc_context_request *r, uint32_t kv, uint32_t mirror);
+/* planContext (src/cpp/core/ContextPlan.cpp:80-246). */
+int tc_context_plan_compute(const tc_context_request *r, tc_context_plan *plan);
+/* probeFreeVramBytes / probeTotalVramBytes (src/cpp/core/ContextPlan.cpp:248-272)
+ * for the current device; 0 when there is none. */
+uint64_t tc_probe_free_vram_bytes(void);
+uint64_t tc_probe_total_vram_bytes(void);
+
+/* KV pool geometry of one session (src/cpp/core/cuda/forward/GPUComputeUpload.cu:
+ * 1254-1323; include/GPUCompute.hpp:844-899): byte sizes the engine allocates. */
+typedef struct tc_kv_pool_geometry {
+    uint64_t kvLayerStride;   /* bytes of ONE layer's K (or V): maxSeq*nKV*hd*elem */
+    uint32_t kvSlots;         /* layers that own a slot */
+    uint64_t kvAllocBytes;    /* per K and per V; 0 when int8 is the store */
+    uint64_t kv8LayerStride;  /* int8 elements per slot: (maxSeq+16)*nKV*hd */
+    uint64_t kv8ScaleStride;  /* bytes of scales per slot: (maxSeq+16)*nKV*4 */
+    uint64_t kv8AllocBytes;   /* per K8 and per V8; 0 when no int8 pool */
+    uint64_t kv8ScaleAllocBytes;
+    uint32_t attnChunk, attnChunks;
+    uint64_t partialAccBytes, partialMLBytes;
+} tc_kv_pool_geometry;
+
+int tc_kv_pool_geometry_compute(uint32_t maxSeqLen, uint32_t nLayersOnGpu,
+                                uint32_t fullAttentionInterval, uint32_t nHeads,
+                                uint32_t nKV, uint32_t hd, int kvHalf,
+                                int kvStoreI8, int kvMirror,
+                                tc_kv_pool_geometry *g);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TC_ATTN_H */

@@ -1,0 +1,161 @@
+"""int8-KV decode attention on the GPU against the oracle (tolerance 1e-3
+relative / 1e-4 absolute on f32 outputs) and against double precision."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tinycoder_inference_b200 import ops, synth
+from tests.util import assert_close, dev, host, make_i8_store
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_single(nH, nKV, hd, ctx, numChunks, seed, extra_rows=0, dev_pos=False):
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((1, nH, hd), dtype=np.float32)
+    k = rng.standard_normal((ctx, nKV, hd), dtype=np.float32)
+    v = rng.standard_normal((ctx, nKV, hd), dtype=np.float32)
+    k8, v8, ks, vs = make_i8_store(k, v, nKV, hd, extra_rows)
+    inv = 1.0 / math.sqrt(hd)
+    want = oracle.attention_i8(q, k8[:ctx], v8[:ctx], ks[:ctx], vs[:ctx], 1, nH, nKV, hd, ctx - 1, inv)
+    exact = oracle.attention_f64(q, k8[:ctx], v8[:ctx], ks[:ctx], vs[:ctx], 1, nH, nKV, hd, ctx - 1, inv)
+    out = torch.full((1, nH, hd), float("nan"), device="cuda")
+    ws = ops.workspace(1, nH, hd, numChunks)
+    for w in ws:
+        w.fill_(float("nan"))  # poison: a slot that is read without being written shows up
+    pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda") if dev_pos else None
+    bound = ctx - 1 + (extra_rows if dev_pos else 0)  # with a device position the host value is an upper bound
+    ops.decode_i8(dev(q), dev(k8), dev(v8), dev(ks), dev(vs), out, ws, nH, nKV, hd, bound, numChunks,
+                  invSqrt=inv, dev_pos=pos)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    got = host(out)
+    assert np.isfinite(got).all()
+    assert_close(got, want, what=f"decode_i8 nH={nH} nKV={nKV} ctx={ctx} vs oracle")
+    assert_close(got, exact, what=f"decode_i8 nH={nH} nKV={nKV} ctx={ctx} vs f64")
+    return got
+
+
+@pytest.mark.parametrize("ctx", [1, 2, 15, 16, 17, 31, 32, 33, 127, 128, 129, 1000, 8192])
+def test_7b_shape_context_edges(ctx):
+    _run_single(28, 4, 128, ctx, numChunks=256, seed=ctx)
+
+
+@pytest.mark.parametrize("nH,nKV", [(40, 8), (14, 2), (12, 2), (8, 8), (8, 1), (5, 1), (21, 3), (16, 4), (6, 6)])
+def test_head_layouts(nH, nKV):
+    _run_single(nH, nKV, 128, 777, numChunks=64, seed=nH * 10 + nKV)
+
+
+@pytest.mark.parametrize("numChunks", [1, 2, 3, 512])
+def test_chunk_slot_capacity(numChunks):
+    _run_single(28, 4, 128, 5000, numChunks=numChunks, seed=numChunks)
+
+
+def test_rows_past_the_length_are_ignored():
+    # garbage int8 rows and NaN scales sit right behind the live rows
+    _run_single(28, 4, 128, 1000, numChunks=128, seed=3, extra_rows=200)
+
+
+def test_device_position():
+    _run_single(28, 4, 128, 1234, numChunks=128, seed=4, extra_rows=300, dev_pos=True)
+
+
+def test_32b_shape_long_context():
+    _run_single(40, 8, 128, 40000, numChunks=512, seed=5)
+
+
+def test_large_magnitudes_and_zero_rows():
+    nH, nKV, hd, ctx = 28, 4, 128, 600
+    rng = np.random.default_rng(9)
+    q = rng.standard_normal((1, nH, hd), dtype=np.float32) * 40.0
+    q[0, 3] = 0.0
+    k = rng.standard_normal((ctx, nKV, hd), dtype=np.float32) * 0.05
+    v = rng.standard_normal((ctx, nKV, hd), dtype=np.float32) * 500.0
+    v[10] = 0.0
+    k[11] = 0.0
+    v[12:20] *= 1e-4
+    k8, v8, ks, vs = make_i8_store(k, v, nKV, hd)
+    inv = 1.0 / math.sqrt(hd)
+    want = oracle.attention_i8(q, k8, v8, ks, vs, 1, nH, nKV, hd, ctx - 1, inv)
+    out = torch.empty((1, nH, hd), device="cuda")
+    ops.decode_i8(dev(q), dev(k8), dev(v8), dev(ks), dev(vs), out, ops.workspace(1, nH, hd, 64), nH, nKV, hd,
+                  ctx - 1, 64, invSqrt=inv)
+    # outputs are O(500): the absolute floor scales with the data
+    assert_close(host(out), want, rtol=1e-3, atol=1e-4 * 500, what="scaled magnitudes")
+
+
+def test_batch_of_ragged_sequences_in_one_pool():
+    nH, nKV, hd = 28, 4, 128
+    lens = np.array([1, 33, 512, 700, 2048, 95, 1500, 31], np.uint32)
+    B, rows_per_seq = len(lens), 2048 + 16
+    rng = np.random.default_rng(21)
+    q = rng.standard_normal((B, nH, hd), dtype=np.float32)
+    k8 = rng.integers(-128, 128, (B, rows_per_seq, nKV, hd), dtype=np.int8)
+    v8 = rng.integers(-128, 128, (B, rows_per_seq, nKV, hd), dtype=np.int8)
+    ks = np.full((B, rows_per_seq, nKV), np.nan, np.float32)
+    vs = np.full((B, rows_per_seq, nKV), np.nan, np.float32)
+    inv = 1.0 / math.sqrt(hd)
+    want = np.zeros((B, nH, hd), np.float32)
+    for b, n in enumerate(lens):
+        k = rng.standard_normal((n, nKV, hd), dtype=np.float32)
+        v = rng.standard_normal((n, nKV, hd), dtype=np.float32)
+        a, c, d, e = oracle.quant_kv8(k, v, nKV, hd)
+        k8[b, :n], v8[b, :n], ks[b, :n], vs[b, :n] = a, c, d, e
+        want[b] = oracle.attention_i8(q[b:b + 1], a, c, d, e, 1, nH, nKV, hd, int(n) - 1, inv)[0]
+    out = torch.full((B, nH, hd), float("nan"), device="cuda")
+    numChunks = 64
+    ws = ops.workspace(B, nH, hd, numChunks)
+    for w in ws:
+        w.fill_(float("nan"))
+    used = ops.decode_i8_batch(dev(q), dev(k8), dev(v8), dev(ks), dev(vs), out, ws, dev(lens), B, nH, nKV, hd,
+                               int(lens.max()), numChunks, rows_per_seq=rows_per_seq, invSqrt=inv)
+    torch.cuda.synchronize()
+    assert 1 <= used <= numChunks and ops.device_status() == 0
+    assert_close(host(out), want, what="ragged batch")
+    # explicit row bases (sequences placed out of order in the pool) give the same answer
+    order = np.array([3, 0, 7, 1, 6, 2, 5, 4])
+    base = (order.astype(np.uint64) * rows_per_seq)
+    k8p, v8p, ksp, vsp = (np.empty_like(x) for x in (k8, v8, ks, vs))
+    for b in range(B):
+        k8p[order[b]], v8p[order[b]], ksp[order[b]], vsp[order[b]] = k8[b], v8[b], ks[b], vs[b]
+    out2 = torch.empty_like(out)
+    ops.decode_i8_batch(dev(q), dev(k8p), dev(v8p), dev(ksp), dev(vsp), out2, ws, dev(lens), B, nH, nKV, hd,
+                        int(lens.max()), numChunks, row_base=dev(base), invSqrt=inv)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+
+
+def test_partials_contract_and_merge_entry_point():
+    """partialsOnly leaves (m, l, acc) in the reference's layout; the separate
+    merge entry point (and the oracle's merge) turn them into the same output."""
+    nH, nKV, hd, ctx, numChunks = 28, 4, 128, 3000, 32
+    rng = np.random.default_rng(8)
+    q = rng.standard_normal((1, nH, hd), dtype=np.float32)
+    k8, v8, ks, vs = make_i8_store(rng.standard_normal((ctx, nKV, hd), dtype=np.float32),
+                                   rng.standard_normal((ctx, nKV, hd), dtype=np.float32), nKV, hd)
+    ws = ops.workspace(1, nH, hd, numChunks)
+    for w in ws:
+        w.zero_()
+    out = torch.zeros((1, nH, hd), device="cuda")
+    lens = torch.tensor([ctx], dtype=torch.int32, device="cuda")
+    used = ops.decode_i8_batch(dev(q), dev(k8), dev(v8), dev(ks), dev(vs), out, ws, lens, 1, nH, nKV, hd, ctx,
+                               numChunks, partials_only=True)
+    assert used > 1
+    acc, m, l = (host(w) for w in ws)
+    want = oracle.attention_i8(q, k8, v8, ks, vs, 1, nH, nKV, hd, ctx - 1, 1.0 / math.sqrt(hd))
+    merged = oracle.combine_partials(acc, m, l, 1, nH, numChunks, hd)   # unused slots hold l == 0
+    assert_close(merged, want, what="oracle merge of GPU partials")
+    out2 = torch.empty_like(out)
+    ops.merge_partials(ws[0], ws[1], ws[2], out2, 1, nH, numChunks, hd)
+    assert_close(host(out2), want, what="GPU merge of GPU partials")
+    # determinism: the same call twice gives the same bits
+    ws2 = ops.workspace(1, nH, hd, numChunks)
+    for w in ws2:
+        w.zero_()
+    ops.decode_i8_batch(dev(q), dev(k8), dev(v8), dev(ks), dev(vs), out, ws2, lens, 1, nH, nKV, hd, ctx,
+                        numChunks, partials_only=True)
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, b) for a, b in zip(ws, ws2))

@@ -1,0 +1,137 @@
+"""KV writers on the GPU against the oracle: int8 quantise+append (bit-exact),
+f32/fp16 append with and without the fused rotation (bit-exact)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tinycoder_inference_b200 import capi, ops
+from tinycoder_inference_b200 import synth
+from tests.util import dev, host
+
+pytestmark = pytest.mark.gpu
+
+
+def _quant_case(tokens, nKV, hd, dst_base, src_base, seed, special=False):
+    rng = np.random.default_rng(seed)
+    rows = src_base + tokens
+    k = rng.standard_normal((rows, nKV, hd), dtype=np.float32)
+    v = rng.standard_normal((rows, nKV, hd), dtype=np.float32) * 3.0
+    if special and tokens >= 4:
+        k[src_base + 0] = 0.0                      # amax == 0 -> scale 1
+        v[src_base + 1] = 0.0
+        k[src_base + 2, :, 0] = 1e-30               # tiny amax
+        v[src_base + 3, 0, :] = np.float32(127.5)   # ties at the clamp edge
+        k[src_base + 3, 0, ::2] = 0.5
+        k[src_base + 3, 0, 1::2] = np.float32(63.5)  # x/s lands on .5 -> round half even
+    want = oracle.quant_kv8(k, v, nKV, hd, dst_base=dst_base, src_base=src_base, tokens=tokens)
+    total = dst_base + tokens + 3
+    k8 = torch.full((total, nKV, hd), 77, dtype=torch.int8, device="cuda")
+    v8 = torch.full((total, nKV, hd), 77, dtype=torch.int8, device="cuda")
+    ks = torch.full((total, nKV), -5.0, device="cuda")
+    vs = torch.full((total, nKV), -5.0, device="cuda")
+    ops.kv_quantize_i8(dev(k), dev(v), k8, v8, ks, vs, tokens, nKV, hd, dst_base, src_base)
+    torch.cuda.synchronize()
+    sl = slice(dst_base, dst_base + tokens)
+    for got, ref in zip((k8, v8, ks, vs), want):
+        assert np.array_equal(host(got)[sl], ref[sl])
+    # rows outside [dst_base, dst_base + tokens) are untouched
+    assert (host(k8)[dst_base + tokens:] == 77).all() and (host(ks)[:dst_base] == -5.0).all()
+
+
+@pytest.mark.parametrize("tokens,nKV,hd,dst,src", [
+    (8192, 4, 128, 0, 0),      # the 7B-shaped store of the decode configs
+    (4096, 4, 128, 0, 0),      # the prefill mirror
+    (1, 4, 128, 777, 0),       # one decode token appended at pos
+    (37, 8, 128, 100, 5),      # mirror rebuild from row 5 of the f32 cache into row 100
+    (129, 2, 64, 3, 0),
+    (65, 4, 256, 0, 2),        # the reference's own head_dim
+    (5, 1, 32, 0, 0),
+    (3, 3, 96, 1, 1),
+])
+def test_quantize_bit_exact(tokens, nKV, hd, dst, src):
+    _quant_case(tokens, nKV, hd, dst, src, seed=tokens + hd, special=True)
+
+
+def test_quantize_zero_tokens_and_device_base():
+    nKV, hd = 4, 128
+    k = torch.randn(4, nKV, hd, device="cuda")
+    k8 = torch.zeros(16, nKV, hd, dtype=torch.int8, device="cuda")
+    s = torch.zeros(16, nKV, device="cuda")
+    ops.kv_quantize_i8(k, k, k8, k8.clone(), s, s.clone(), 0, nKV, hd)
+    base = torch.tensor([9], dtype=torch.int32, device="cuda")
+    v8 = torch.zeros_like(k8)
+    vs = torch.zeros_like(s)
+    ops.kv_quantize_i8(k, k, k8, v8, s, vs, 4, nKV, hd, dst_base=0, dev_dst_base=base)
+    torch.cuda.synchronize()
+    want = oracle.quant_kv8(host(k), host(k), nKV, hd, dst_base=9)
+    assert np.array_equal(host(k8)[9:13], want[0][9:13]) and (host(k8)[:9] == 0).all()
+    assert np.array_equal(host(vs)[9:13], want[3][9:13])
+
+
+def test_quantize_past_the_pool_is_refused():
+    nKV, hd = 4, 128
+    k = torch.randn(4, nKV, hd, device="cuda")
+    k8 = torch.zeros(8, nKV, hd, dtype=torch.int8, device="cuda")
+    s = torch.zeros(8, nKV, device="cuda")
+    with pytest.raises(capi.ContextFull):
+        ops.kv_quantize_i8(k, k, k8, k8, s, s, 4, nKV, hd, dst_base=6)
+
+
+@pytest.mark.parametrize("half", [False, True])
+@pytest.mark.parametrize("rope", [False, True])
+@pytest.mark.parametrize("seqLen,nH,nKV,hd,cachePos", [(1, 14, 2, 64, 2047), (512, 28, 4, 128, 0), (7, 40, 8, 128, 33),
+                                                      (3, 4, 4, 256, 5)])
+def test_append_bit_exact(half, rope, seqLen, nH, nKV, hd, cachePos):
+    rng = np.random.default_rng(seqLen * 31 + hd)
+    rows = cachePos + seqLen + 2
+    kSrc = rng.standard_normal((seqLen, nKV, hd), dtype=np.float32)
+    vSrc = rng.standard_normal((seqLen, nKV, hd), dtype=np.float32)
+    q = rng.standard_normal((seqLen, nH, hd), dtype=np.float32)
+    dt = np.float16 if half else np.float32
+    kRef = np.full((rows, nKV, hd), 9, dt)
+    vRef = np.full((rows, nKV, hd), 9, dt)
+    kDst, vDst = dev(kRef), dev(vRef)
+    if rope:
+        cosT, sinT = oracle.rope_tables(rows, hd, 1e6)
+        oracle.kv_append(kSrc, vSrc, kRef, vRef, seqLen, nKV, hd, cachePos, cachePos, cosT, sinT)
+        qRef = oracle.rope_q(q, cosT, sinT, seqLen, nH, hd, cachePos)
+        qd = dev(q)
+        ops.kv_append_rope(qd, dev(kSrc), dev(vSrc), kDst, vDst, seqLen, nH, nKV, hd, cachePos, cachePos,
+                           dev(cosT), dev(sinT))
+        assert np.array_equal(host(qd), qRef)
+        q2 = dev(q)
+        ops.rope_q(q2, dev(cosT), dev(sinT), seqLen, nH, hd, cachePos)
+        assert np.array_equal(host(q2), qRef)
+    else:
+        oracle.kv_append(kSrc, vSrc, kRef, vRef, seqLen, nKV, hd, cachePos)
+        ops.kv_append(dev(kSrc), dev(vSrc), kDst, vDst, seqLen, nKV, hd, cachePos)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(kDst).view(np.uint8), kRef.view(np.uint8))
+    assert np.array_equal(host(vDst).view(np.uint8), vRef.view(np.uint8))
+
+
+def test_append_device_position_and_window_guard():
+    nKV, hd = 4, 128
+    kSrc = torch.randn(1, nKV, hd, device="cuda")
+    kDst = torch.zeros(16, nKV, hd, device="cuda")
+    vDst = torch.zeros(16, nKV, hd, device="cuda")
+    pos = torch.tensor([11], dtype=torch.int32, device="cuda")
+    ops.kv_append(kSrc, kSrc, kDst, vDst, 1, nKV, hd, 0, dev_pos=pos)
+    torch.cuda.synchronize()
+    assert torch.equal(kDst[11], kSrc[0]) and float(kDst[:11].abs().sum()) == 0.0
+    with pytest.raises(capi.ContextFull):
+        ops.kv_append(kSrc, kSrc, kDst, vDst, 1, nKV, hd, 16)
+
+
+def test_cpu_engine_append_is_within_tolerance_of_gpu_form():
+    # Model::storeKVWithRoPE rounds the two products separately; the GPU form fuses one.
+    seqLen, nKV, hd = 5, 4, 128
+    rng = np.random.default_rng(3)
+    kSrc = rng.standard_normal((seqLen, nKV, hd), dtype=np.float32)
+    cosT, sinT = oracle.rope_tables(16, hd, 1e6)
+    a = np.zeros((16, nKV, hd), np.float32)
+    b = np.zeros_like(a)
+    oracle.kv_append(kSrc, kSrc, a, np.zeros_like(a), seqLen, nKV, hd, 3, 3, cosT, sinT)
+    oracle.kv_append_cpu(kSrc, kSrc, b, np.zeros_like(b), seqLen, 3, nKV, hd, cosT, sinT)
+    assert np.allclose(a, b, rtol=1e-6, atol=1e-6)

@@ -1,0 +1,169 @@
+// merge.cu -- log-sum-exp merge of split-KV partials into the attention output.
+//
+// The contract is the reference's (include/gpu/GpuAttentionKernels.hpp:909-946):
+// for one (token, q-head) with chunk partials (m_c, l_c, acc_c[hd]):
+//   M = max_c m_c;  w_c = exp2((m_c - M) * log2e);  chunks with l_c <= 0 skipped;
+//   out = sum_c w_c acc_c / sum_c w_c l_c   (0 when nothing contributed).
+// One block per (head, token): 8 warps each fold every 8th chunk with 128-bit
+// loads (a lane owns 4 consecutive dims per 128-dim group), then the 8 warp
+// partials are folded through shared memory -- the shape of the reference's
+// kAttnCombinePartialW4 (:1003-1098).  The same kernel merges partials gathered
+// from other GPUs when the context axis is split across ranks.
+//
+// Optional epilogue: the Q8_1 blocks of the output for the GEMV that follows
+// attention (40-byte slots {fp16 d, fp16 sum, int8 q[32]}, :1068-1096).  The
+// block sum is folded in the reference's order (lane = element index inside the
+// block, xor butterfly 16..1) so the fp16 sum matches bit for bit on equal input.
+#include "tc_common.cuh"
+
+namespace tc {
+
+template <int NV4>
+__global__ void __launch_bounds__(256)
+mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM, const float *__restrict__ pL,
+                    float *__restrict__ out, uint32_t nHeads, uint32_t numChunks, uint32_t activeHost,
+                    uint32_t hd, const uint32_t *__restrict__ devLens, uint32_t lenAdd, uint32_t chunkTokens,
+                    uint8_t *__restrict__ q81) {
+    constexpr int NW = 8;
+    const uint32_t head = blockIdx.x, s = blockIdx.y;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint64_t base = (static_cast<uint64_t>(s) * nHeads + head) * numChunks;
+    // numChunks is the slot stride; only the first `active` slots were written
+    uint32_t active = activeHost < numChunks ? activeHost : numChunks;
+    if (devLens != nullptr) {
+        const uint32_t len = devLens[s] + lenAdd;
+        const uint32_t need = (len + chunkTokens - 1) / chunkTokens;
+        active = need < numChunks ? need : numChunks;
+    }
+    float M = kNegBig;
+    for (uint32_t c = warp; c < active; c += NW) M = fmaxf(M, pM[base + c]);
+    float4 acc[NV4];
+#pragma unroll
+    for (int j = 0; j < NV4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float lsum = 0.0f;
+    const uint32_t nvec = hd >> 2;
+    for (uint32_t c = warp; c < active; c += NW) {
+        const float lc = pL[base + c];
+        if (lc <= 0.0f) continue;
+        const float w = exp2f((pM[base + c] - M) * kLog2e);
+        lsum += w * lc;
+        const float4 *pac = reinterpret_cast<const float4 *>(pAcc + (base + c) * hd);
+#pragma unroll
+        for (int j = 0; j < NV4; ++j) {
+            const uint32_t i = lane + 32u * j;
+            if (i < nvec) {
+                const float4 a = pac[i];
+                acc[j].x = fmaf(w, a.x, acc[j].x);
+                acc[j].y = fmaf(w, a.y, acc[j].y);
+                acc[j].z = fmaf(w, a.z, acc[j].z);
+                acc[j].w = fmaf(w, a.w, acc[j].w);
+            }
+        }
+    }
+    __shared__ float sm[NW], sl[NW];
+    __shared__ float4 sacc[NW][NV4][32];
+    __shared__ float sout[NV4 * 128];
+    if (lane == 0) {
+        sm[warp] = M;
+        sl[warp] = lsum;
+    }
+#pragma unroll
+    for (int j = 0; j < NV4; ++j) sacc[warp][j][lane] = acc[j];
+    __syncthreads();
+    if (warp == 0) {
+        float gM = kNegBig;
+#pragma unroll
+        for (int w2 = 0; w2 < NW; ++w2) gM = fmaxf(gM, sm[w2]);
+        float gL = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NV4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w2 = 0; w2 < NW; ++w2) {
+            const float w = exp2f((sm[w2] - gM) * kLog2e);
+            gL += w * sl[w2];
+#pragma unroll
+            for (int j = 0; j < NV4; ++j) {
+                const float4 a = sacc[w2][j][lane];
+                acc[j].x = fmaf(w, a.x, acc[j].x);
+                acc[j].y = fmaf(w, a.y, acc[j].y);
+                acc[j].z = fmaf(w, a.z, acc[j].z);
+                acc[j].w = fmaf(w, a.w, acc[j].w);
+            }
+        }
+        const float inv = gL > 0.0f ? 1.0f / gL : 0.0f;
+        float4 *op = reinterpret_cast<float4 *>(out + (static_cast<uint64_t>(s) * nHeads + head) * hd);
+#pragma unroll
+        for (int j = 0; j < NV4; ++j) {
+            const uint32_t i = lane + 32u * j;
+            if (i < nvec) {
+                const float4 r = make_float4(acc[j].x * inv, acc[j].y * inv, acc[j].z * inv, acc[j].w * inv);
+                op[i] = r;
+                reinterpret_cast<float4 *>(sout)[i] = r;
+            }
+        }
+    }
+    if (q81 == nullptr) return;
+    __syncthreads();
+    const uint32_t nBlk = hd >> 5;
+    for (uint32_t b = warp; b < nBlk; b += NW) {
+        const float v = sout[b * 32 + lane];
+        float amax = fabsf(v), sum = v;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        }
+        const float d = __fdiv_rn(amax, 127.0f);
+        uint8_t *blk = q81 + ((static_cast<uint64_t>(s) * nHeads + head) * nBlk + b) * 40u;
+        reinterpret_cast<int8_t *>(blk + 4)[lane] =
+                amax == 0.0f ? static_cast<int8_t>(0) : static_cast<int8_t>(roundf(__fdiv_rn(v, d)));
+        if (lane == 0) {
+            __half *ds = reinterpret_cast<__half *>(blk);
+            ds[0] = __float2half(d);
+            ds[1] = __float2half(sum);
+        }
+    }
+}
+
+int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out, uint32_t seqLen,
+                uint32_t nHeads, uint32_t numChunks, uint32_t activeHost, uint32_t hd, const uint32_t *devLens,
+                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, cudaStream_t st) {
+    dim3 grid(nHeads, seqLen);
+    if (hd <= 128)
+        mergePartialsKernel<1><<<grid, 256, 0, st>>>(pAcc, pM, pL, out, nHeads, numChunks, activeHost, hd,
+                                                     devLens, lenAdd, chunkTokens, q81);
+    else
+        mergePartialsKernel<2><<<grid, 256, 0, st>>>(pAcc, pM, pL, out, nHeads, numChunks, activeHost, hd,
+                                                     devLens, lenAdd, chunkTokens, q81);
+    TC_CUDA_OK(cudaGetLastError());
+    return TC_OK;
+}
+
+}  // namespace tc
+
+extern "C" {
+
+int tc_attn_merge_partials(const float *pAcc, const float *pM, const float *pL, float *out, uint32_t seqLen,
+                           uint32_t nHeads, uint32_t numChunks, uint32_t hd, uint8_t *q81Out,
+                           tc_stream stream) {
+    TC_REQUIRE(pAcc && pM && pL && out, TC_EINVAL, "tc_attn_merge_partials: null pointer");
+    TC_REQUIRE(hd >= 32 && hd <= 256 && (hd % 32u) == 0, TC_EUNSUPPORTED,
+               "tc_attn_merge_partials: hd=%u must be a multiple of 32 in [32, 256]", hd);
+    TC_REQUIRE(numChunks >= 1 && nHeads >= 1, TC_EINVAL, "tc_attn_merge_partials: empty shape");
+    TC_REQUIRE(seqLen <= 65535, TC_EUNSUPPORTED, "tc_attn_merge_partials: seqLen %u > 65535", seqLen);
+    if (seqLen == 0) return TC_OK;
+    return tc::launchMerge(pAcc, pM, pL, out, seqLen, nHeads, numChunks, numChunks, hd, nullptr, 0, 1, q81Out,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int tc_attn_workspace_bytes(uint32_t batch, uint32_t nHeads, uint32_t hd, uint32_t numChunks, size_t *accBytes,
+                            size_t *mBytes, size_t *lBytes) {
+    TC_REQUIRE(accBytes && mBytes && lBytes, TC_EINVAL, "tc_attn_workspace_bytes: null output");
+    const size_t n = static_cast<size_t>(batch) * nHeads * numChunks;
+    *accBytes = n * hd * sizeof(float);
+    *mBytes = n * sizeof(float);
+    *lBytes = n * sizeof(float);
+    return TC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,200 @@
+"""Thin torch-tensor front of the C ABI (one function per entry point).
+
+torch is used for device memory and streams only; every call goes through
+libtc_attn.so.  Tensors must live on the current CUDA device and be contiguous.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from . import capi
+from .capi import check, lib
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "device-resident contiguous tensor required"
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def device_status() -> int:
+    flags = C.c_uint32(0)
+    check(lib.tc_device_status(_stream(), C.byref(flags)))
+    return flags.value
+
+
+# ---- KV writers ---------------------------------------------------------------
+
+def kv_quantize_i8(k, v, k8, v8, ks, vs, tokens, nKV, hd, dst_base=0, src_base=0, dev_dst_base=None):
+    """k, v f32 [rows][nKV][hd] -> rows dst_base.. of the int8 pool k8/v8 + scales ks/vs."""
+    max_rows = k8.numel() // (nKV * hd)
+    check(lib.tc_kv_quantize_i8(_ptr(k), _ptr(v), _ptr(k8), _ptr(v8), _ptr(ks), _ptr(vs), tokens, nKV, hd,
+                                dst_base, src_base, _ptr(dev_dst_base), max_rows, _stream()))
+
+
+def kv_append(kSrc, vSrc, kDst, vDst, seqLen, nKV, hd, cachePos, dev_pos=None):
+    half = kDst.dtype == torch.float16
+    max_rows = kDst.numel() // (nKV * hd)
+    check(lib.tc_kv_append(_ptr(kSrc), _ptr(vSrc), _ptr(kDst), _ptr(vDst), int(half), seqLen, nKV, hd, cachePos,
+                           _ptr(dev_pos), max_rows, _stream()))
+
+
+def kv_append_rope(q, kSrc, vSrc, kDst, vDst, seqLen, nHeads, nKV, hd, cachePos, ropePos, cosT, sinT,
+                   dev_pos=None):
+    half = kDst.dtype == torch.float16
+    max_rows = kDst.numel() // (nKV * hd)
+    check(lib.tc_kv_append_rope(_ptr(q), _ptr(kSrc), _ptr(vSrc), _ptr(kDst), _ptr(vDst), int(half), seqLen,
+                                nHeads, nKV, hd, cachePos, ropePos, _ptr(dev_pos), _ptr(cosT), _ptr(sinT),
+                                max_rows, _stream()))
+
+
+def rope_q(q, cosT, sinT, seqLen, nHeads, hd, pos, dev_pos=None):
+    check(lib.tc_rope_q(_ptr(q), _ptr(cosT), _ptr(sinT), seqLen, nHeads, hd, pos, _ptr(dev_pos), _stream()))
+
+
+# ---- decode -------------------------------------------------------------------
+
+def workspace(batch, nHeads, hd, numChunks, device=None):
+    a, m, l = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    check(lib.tc_attn_workspace_bytes(batch, nHeads, hd, numChunks, C.byref(a), C.byref(m), C.byref(l)))
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    return (torch.empty(a.value // 4, dtype=torch.float32, device=dev),
+            torch.empty(m.value // 4, dtype=torch.float32, device=dev),
+            torch.empty(l.value // 4, dtype=torch.float32, device=dev))
+
+
+def split_geometry(maxSeqLen, nHeads, hd):
+    a, b = C.c_uint32(), C.c_uint32()
+    rc = lib.tc_split_geometry(maxSeqLen, nHeads, hd, C.byref(a), C.byref(b))
+    check(rc)
+    return a.value, b.value
+
+
+def decode_i8(q, k8, v8, ks, vs, out, ws, nHeads, nKV, hd, cachePos, numChunks, chunkSize=0, invSqrt=None,
+              dev_pos=None):
+    """One query token over rows [0, cachePos] of an int8 store."""
+    if invSqrt is None:
+        invSqrt = 1.0 / math.sqrt(hd)
+    total_rows = k8.numel() // (nKV * hd)
+    pAcc, pM, pL = ws
+    check(lib.tc_attn_decode_i8(_ptr(q), _ptr(k8), _ptr(v8), _ptr(ks), _ptr(vs), _ptr(out), _ptr(pAcc),
+                                _ptr(pM), _ptr(pL), nHeads, nKV, hd, cachePos, _ptr(dev_pos), total_rows,
+                                numChunks, chunkSize, invSqrt, _stream()))
+
+
+def decode_i8_batch(q, k8, v8, ks, vs, out, ws, lens, batch, nHeads, nKV, hd, maxLen, numChunks,
+                    rows_per_seq=0, row_base=None, invSqrt=None, partials_only=False):
+    """`batch` sequences in one pool; returns the chunk slots used per head."""
+    if invSqrt is None:
+        invSqrt = 1.0 / math.sqrt(hd)
+    pAcc, pM, pL = ws
+    used = C.c_uint32(0)
+    d = capi.DecodeI8Batch()
+    d.q, d.out = q.data_ptr(), out.data_ptr()
+    d.k8, d.v8, d.ks, d.vs = k8.data_ptr(), v8.data_ptr(), ks.data_ptr(), vs.data_ptr()
+    d.pAcc, d.pM, d.pL = pAcc.data_ptr(), pM.data_ptr(), pL.data_ptr()
+    d.lens = lens.data_ptr()
+    d.rowBase = row_base.data_ptr() if row_base is not None else None
+    d.rowsPerSeq = rows_per_seq
+    d.totalRows = k8.numel() // (nKV * hd)
+    d.batch, d.nHeads, d.nKV, d.hd = batch, nHeads, nKV, hd
+    d.maxLen, d.numChunks = maxLen, numChunks
+    d.invSqrt = invSqrt
+    d.partialsOnly = int(partials_only)
+    d.chunksUsed = C.pointer(used)
+    check(lib.tc_attn_decode_i8_batch(C.byref(d), _stream()))
+    return used.value
+
+
+def decode_kv(q, kvK, kvV, out, ws, seqLen, nHeads, nKV, hd, pos, numChunks, chunkSize=0, invSqrt=None,
+              dev_pos=None, q81=None):
+    if invSqrt is None:
+        invSqrt = 1.0 / math.sqrt(hd)
+    half = kvK.dtype == torch.float16
+    total_rows = kvK.numel() // (nKV * hd)
+    pAcc, pM, pL = ws
+    check(lib.tc_attn_decode_kv(_ptr(q), _ptr(kvK), _ptr(kvV), _ptr(out), _ptr(pAcc), _ptr(pM), _ptr(pL),
+                                seqLen, nHeads, nKV, hd, pos, _ptr(dev_pos), total_rows, numChunks, chunkSize,
+                                invSqrt, int(half), _ptr(q81), _stream()))
+
+
+def merge_partials(pAcc, pM, pL, out, seqLen, nHeads, numChunks, hd, q81=None):
+    check(lib.tc_attn_merge_partials(_ptr(pAcc), _ptr(pM), _ptr(pL), _ptr(out), seqLen, nHeads, numChunks, hd,
+                                     _ptr(q81), _stream()))
+
+
+# ---- prefill ------------------------------------------------------------------
+
+def prefill_f16_scratch_bytes(seqLen, nHeads, nKV, hd) -> int:
+    b = C.c_size_t()
+    check(lib.tc_attn_prefill_f16_scratch_bytes(seqLen, nHeads, nKV, hd, C.byref(b)))
+    return b.value
+
+
+def prefill_f16(q, kvK, kvV, out, scratch, seqLen, nHeads, nKV, hd, invSqrt=None):
+    if invSqrt is None:
+        invSqrt = 1.0 / math.sqrt(hd)
+    check(lib.tc_attn_prefill_f16(_ptr(q), _ptr(kvK), _ptr(kvV), _ptr(out), _ptr(scratch),
+                                  scratch.numel() * scratch.element_size(), seqLen, nHeads, nKV, hd, invSqrt,
+                                  _stream()))
+
+
+def prefill_kv(q, kvK, kvV, out, seqLen, nHeads, nKV, hd, cachePos, invSqrt=None, dev_pos=None):
+    if invSqrt is None:
+        invSqrt = 1.0 / math.sqrt(hd)
+    half = kvK.dtype == torch.float16
+    total_rows = kvK.numel() // (nKV * hd)
+    check(lib.tc_attn_prefill_kv(_ptr(q), _ptr(kvK), _ptr(kvV), _ptr(out), seqLen, nHeads, nKV, hd, cachePos,
+                                 _ptr(dev_pos), total_rows, invSqrt, int(half), _stream()))
+
+
+def prefill_i8(q, k8, v8, ks, vs, out, seqLen, nHeads, nKV, hd, cachePos, invSqrt=None, dev_pos=None):
+    if invSqrt is None:
+        invSqrt = 1.0 / math.sqrt(hd)
+    total_rows = k8.numel() // (nKV * hd)
+    check(lib.tc_attn_prefill_i8(_ptr(q), _ptr(k8), _ptr(v8), _ptr(ks), _ptr(vs), _ptr(out), seqLen, nHeads,
+                                 nKV, hd, cachePos, _ptr(dev_pos), total_rows, invSqrt, _stream()))
+
+
+def sigmoid_gate(attnOut, qGate, seqLen, nHeads, hd):
+    check(lib.tc_attn_sigmoid_gate(_ptr(attnOut), _ptr(qGate), seqLen, nHeads, hd, _stream()))
+
+
+# ---- planner (host) -------------------------------------------------------------
+
+def context_request(**kw) -> capi.ContextRequest:
+    r = capi.ContextRequest()
+    lib.tc_context_request_init(C.byref(r))
+    for k, v in kw.items():
+        setattr(r, k, int(v))
+    return r
+
+
+def plan_context(req: capi.ContextRequest) -> dict:
+    p = capi.ContextPlan()
+    check(lib.tc_context_plan_compute(C.byref(req), C.byref(p)))
+    return p.as_dict()
+
+
+def kv_bytes_per_token(req, kv, mirror) -> int:
+    return int(lib.tc_kv_bytes_per_token(C.byref(req), int(kv), int(mirror)))
+
+
+def kv_store_bytes_per_token(req, kv, mirror) -> int:
+    return int(lib.tc_kv_store_bytes_per_token(C.byref(req), int(kv), int(mirror)))
+
+
+def kv_pool_geometry(maxSeqLen, nLayersOnGpu, fullAttentionInterval, nHeads, nKV, hd, kvHalf=False,
+                     kvStoreI8=False, kvMirror=False) -> capi.KvPoolGeometry:
+    g = capi.KvPoolGeometry()
+    check(lib.tc_kv_pool_geometry_compute(maxSeqLen, nLayersOnGpu, fullAttentionInterval, nHeads, nKV, hd,
+                                          int(kvHalf), int(kvStoreI8), int(kvMirror), C.byref(g)))
+    return g
