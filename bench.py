@@ -1,0 +1,387 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path.
+
+Default workload (`--workload decode32k`): Qwen2.5-7B-shaped decode attention over
+an int8 KV store at context 32768 -- 28 query heads, 4 KV heads, head_dim 128,
+batch 1 per GPU, one decode step = the attention of all 28 layers (each layer has
+its own KV pool, so a step streams 28 x 34.6 MB = 969 MB, far more than the 126 MB
+L2: no layer's KV survives in cache until the next step).  Metric: algorithmic KV
+bytes (int8 rows + f32 scales, read once) per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload decode32k|decode8k_b8|c4_32b_128k|ragged64|prefill4k]
+
+N > 1 (torchrun): every rank runs the same per-GPU workload on its own sequences
+(sharding by sequence, no data-path collective) -- weak scaling; the time is the
+max over ranks, the value the sum of bytes over ranks divided by it.
+
+`--impl reference` times the reference engine's CPU attention path (its own
+thread pool and AVX-512 leaf kernels behind the restated task loop, built from
+the reference sources into oracle/_ref; the plain C restatement when that
+library is absent) on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (nHeads, nKV, hd, ctx, batch, layers)
+    "decode32k": (28, 4, 128, 32768, 1, 28),
+    "decode8k_b8": (28, 4, 128, 8192, 8, 28),
+    "decode8k_b1": (28, 4, 128, 8192, 1, 28),
+    "c4_32b_128k": (40, 8, 128, 131072, 1, 8),  # 8 of the 64 layers resident (64 x 277 MB pools are cycled per 8)
+}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid):
+        self.uuid = uuid
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def algorithmic_bytes(nKV, hd, tokens):
+    """int8 K and V rows plus one f32 scale each per (token, kv head), read once."""
+    return tokens * nKV * 2 * (hd + 4)
+
+
+# ---------------------------------------------------------------------------------
+# CPU baseline / reference arm
+# ---------------------------------------------------------------------------------
+
+def cpu_attention_sample(nH, nKV, hd, ctx, budget_s=12.0, threads=0):
+    """Times the reference CPU attention on ONE layer of the workload (the CPU
+    engine keeps K/V in f32 only, so it attends over the dequantised f32 copy of
+    the int8 store).  Returns (seconds per layer, cores, kind, sample text)."""
+    import numpy as np
+
+    import oracle
+    from tinycoder_inference_b200 import synth
+
+    q = synth.normal(2, 1, (1, nH, hd))
+    k = synth.normal(2, 2, (ctx, nKV, hd))
+    v = synth.normal(2, 3, (ctx, nKV, hd))
+    k8, v8, ks, vs = oracle.quant_kv8(k, v, nKV, hd)
+    kf = (k8.astype(np.float32) * ks[:, :, None]).astype(np.float32)
+    vf = (v8.astype(np.float32) * vs[:, :, None]).astype(np.float32)
+    use_ref = oracle.ref_available() and oracle.ref().has_avx512()
+    if use_ref:
+        ref = oracle.ref()
+        cores = ref.pool_init(threads)
+        run = lambda: ref.attention_fused(q, kf, vf, ctx - 1, 1, nH, nKV, hd)  # noqa: E731
+        kind = "reference"
+        how = ("reference ThreadPool::parallelFor2D(1 x %d kv heads) + AVX-512 dot/axpy leaves, restated "
+               "attentionFused task loop" % nKV)
+    else:
+        cores = 1
+        run = lambda: oracle.attention_fused_cpu(q, kf, vf, 1, ctx - 1, nH, nKV, hd)  # noqa: E731
+        kind = "port"
+        how = "scalar C restatement of Model::attentionFused"
+    run()
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        run()
+        reps += 1
+        if time.perf_counter() - t0 > budget_s or reps >= 400:
+            break
+    per_layer = (time.perf_counter() - t0) / reps
+    sample = f"1 layer x {reps} repetitions, f32 copy of the int8 store, ctx {ctx}; {how}"
+    return per_layer, cores, kind, sample
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    nH, nKV, hd, ctx, batch, layers = WORKLOADS[args.workload]
+    budget = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
+    # a "step" of the CPU arm is a bounded sample: one layer, repeated
+    times = []
+    cores, kind, sample = 1, "port", ""
+    for i in range(args.warmup + args.steps):
+        per_layer, cores, kind, sample = cpu_attention_sample(nH, nKV, hd, ctx, budget_s=budget / 4)
+        if i >= args.warmup:
+            times.append(per_layer)
+    per_layer = sum(times) / len(times)
+    gbs = algorithmic_bytes(nKV, hd, ctx) / per_layer / 1e9
+    line = {
+        "impl": "reference", "metric": "decode_attn_kv_gbs_ctx32k", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": per_layer * layers * batch * 1e3, "us_per_layer": per_layer * 1e6,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.workload, args.gpus),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name, gpus):
+    nH, nKV, hd, ctx, batch, layers = WORKLOADS[name]
+    return {"workload": f"{name}: {nH} q heads / {nKV} kv heads / head_dim {hd}, int8 KV, context {ctx}, "
+                        f"batch {batch} per GPU, {layers} layers per step",
+            "sharding": "by sequence, one replica of the workload per GPU, no collective" if gpus > 1 else "single GPU",
+            "l2": f"inputs larger than L2: a step streams {layers} distinct KV pools "
+                  f"({layers * batch * algorithmic_bytes(nKV, hd, ctx) / 1e6:.0f} MB)",
+            "launch": "cuda_graph"}
+
+
+# ---------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode32k", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from tinycoder_inference_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+
+    nH, nKV, hd, ctx, batch, layers = WORKLOADS[args.workload]
+    inv = 1.0 / math.sqrt(hd)
+    rows = ctx + 16
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x7C0DE002 + rank)
+    # one int8 pool per layer holding `batch` sequences; built by the library's own
+    # quantiser from seeded N(0,1) f32 rows (bit-exact with the reference quantiser)
+    k8 = torch.empty((layers, batch, rows, nKV, hd), dtype=torch.int8, device=dev)
+    v8 = torch.empty_like(k8)
+    ks = torch.zeros((layers, batch, rows, nKV), device=dev)
+    vs = torch.zeros_like(ks)
+    for l in range(layers):
+        for b in range(batch):
+            kf = torch.randn((ctx, nKV, hd), generator=g, device=dev)
+            vf = torch.randn((ctx, nKV, hd), generator=g, device=dev)
+            ops.kv_quantize_i8(kf, vf, k8[l, b], v8[l, b], ks[l, b], vs[l, b], ctx, nKV, hd)
+    q = torch.randn((layers, batch, nH, hd), generator=g, device=dev)
+    out = torch.empty_like(q)
+    chunk, chunks = ops.split_geometry(ctx, nH, hd)
+    ws = ops.workspace(batch, nH, hd, chunks)
+    lens = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize()
+
+    def step():
+        for l in range(layers):
+            if batch == 1:
+                ops.decode_i8(q[l], k8[l, 0], v8[l, 0], ks[l, 0], vs[l, 0], out[l], ws, nH, nKV, hd, ctx - 1, chunks,
+                              chunk, inv)
+            else:
+                ops.decode_i8_batch(q[l], k8[l], v8[l], ks[l], vs[l], out[l], ws, lens, batch, nH, nKV, hd, ctx,
+                                    chunks, rows_per_seq=rows, invSqrt=inv)
+
+    launches_per_step = layers * 2
+    step()
+    torch.cuda.synchronize()
+    graph = None
+    if not args.no_graph:
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            step()
+        torch.cuda.current_stream().wait_stream(s)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+    run = graph.replay if graph is not None else step
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    props = torch.cuda.get_device_properties(local)
+    gpu_id = str(getattr(props, "uuid", local))
+    if "-" in gpu_id and not gpu_id.startswith("GPU-"):
+        gpu_id = "GPU-" + gpu_id
+    sampler = ClockSampler(gpu_id)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        run()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ms_per_step = ms / args.steps
+    bytes_per_step_gpu = layers * batch * algorithmic_bytes(nKV, hd, ctx)
+    value = world * bytes_per_step_gpu / (ms_per_step * 1e-3) / 1e9
+    us_per_layer = ms_per_step * 1e3 / layers
+
+    # ---- end to end through the C ABI with HOST buffers ---------------------------
+    # per layer: the new token's q, k, v come from pinned host memory, k/v are
+    # quantised and appended at the last row, attention runs, the result goes back
+    hq = torch.randn((layers, batch, nH, hd)).pin_memory()
+    hk = torch.randn((layers, batch, nKV, hd)).pin_memory()
+    hv = torch.randn((layers, batch, nKV, hd)).pin_memory()
+    hout = torch.empty((layers, batch, nH, hd)).pin_memory()
+    dq = torch.empty((batch, nH, hd), device=dev)
+    dk = torch.empty((batch, nKV, hd), device=dev)
+    dv = torch.empty((batch, nKV, hd), device=dev)
+    dout = torch.empty((batch, nH, hd), device=dev)
+
+    def e2e_step():
+        for l in range(layers):
+            dq.copy_(hq[l], non_blocking=True)
+            dk.copy_(hk[l], non_blocking=True)
+            dv.copy_(hv[l], non_blocking=True)
+            for b in range(batch):
+                ops.kv_quantize_i8(dk[b], dv[b], k8[l, b], v8[l, b], ks[l, b], vs[l, b], 1, nKV, hd, dst_base=ctx - 1)
+            if batch == 1:
+                ops.decode_i8(dq, k8[l, 0], v8[l, 0], ks[l, 0], vs[l, 0], dout, ws, nH, nKV, hd, ctx - 1, chunks,
+                              chunk, inv)
+            else:
+                ops.decode_i8_batch(dq, k8[l], v8[l], ks[l], vs[l], dout, ws, lens, batch, nH, nKV, hd, ctx, chunks,
+                                    rows_per_seq=rows, invSqrt=inv)
+            hout[l].copy_(dout, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_steps = max(3, min(args.steps, 50))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
+    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms_per_step = float(t.item()) / e2e_steps
+    e2e_value = world * bytes_per_step_gpu / (e2e_ms_per_step * 1e-3) / 1e9
+    clocks = sampler.stop() if rank == 0 else None
+    dev_flags = ops.device_status()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    per_gpu_gbs = bytes_per_step_gpu / (ms_per_step * 1e-3) / 1e9
+    line = {
+        "metric": "decode_attn_kv_gbs_ctx32k" if args.workload == "decode32k" else f"decode_attn_kv_gbs_{args.workload}",
+        "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "us_per_layer": us_per_layer, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 KV, f32 q/out (fp16 hi+lo tensor-core products, f32 accumulate)",
+        "data": "synthetic", "config": workload_config(args.workload, world),
+        "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": per_gpu_gbs / pk["hbm_gbs"], "peak_source": pk["source"],
+                     "traffic": None,
+                     "note": "algorithmic bytes per layer / (step time / layers); split and merge launches both inside"},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms_per_step,
+                "h2d_bytes_per_step": layers * batch * (nH + 2 * nKV) * hd * 4,
+                "d2h_bytes_per_step": layers * batch * nH * hd * 4},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks, "device_error_flags": dev_flags,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        per_layer, cores, kind, sample = cpu_attention_sample(nH, nKV, hd, ctx)
+        line["cpu_baseline"] = {"value": algorithmic_bytes(nKV, hd, ctx) / per_layer / 1e9, "unit": "GB/s",
+                                "cores": cores, "kind": kind, "sample": sample, "us_per_layer": per_layer * 1e6}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -216,7 +216,8 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const float svA = v0 ? sV[g] : 0.0f, svB = v1 ? sV[g + 8] : 0.0f;
 
         // ---- S^T = K . Q^T (16 tokens x 8 heads) ----
-        float sc[4] = {0.f, 0.f, 0.f, 0.f};
+        // two accumulators (hi and lo parts of q) keep the MMA dependency chains short
+        float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};
         const uint32_t kTile = smemAddr(st + (hL * T + sub * 16) * kHD);
 #pragma unroll
         for (int cp = 0; cp < 4; ++cp) {
@@ -231,15 +232,17 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 const uint32_t a0 = biasedPairLo(r0), a1 = biasedPairLo(r1), a2 = biasedPairHi(r0),
                                a3 = biasedPairHi(r1);
                 mmaF16(sc, a0, a1, a2, a3, qhi[2 * cp][0], qhi[2 * cp][1]);
-                mmaF16(sc, a0, a1, a2, a3, qlo[2 * cp][0], qlo[2 * cp][1]);
+                mmaF16(sc2, a0, a1, a2, a3, qlo[2 * cp][0], qlo[2 * cp][1]);
             }
             {
                 const uint32_t a0 = biasedPairLo(r2), a1 = biasedPairLo(r3), a2 = biasedPairHi(r2),
                                a3 = biasedPairHi(r3);
                 mmaF16(sc, a0, a1, a2, a3, qhi[2 * cp + 1][0], qhi[2 * cp + 1][1]);
-                mmaF16(sc, a0, a1, a2, a3, qlo[2 * cp + 1][0], qlo[2 * cp + 1][1]);
+                mmaF16(sc2, a0, a1, a2, a3, qlo[2 * cp + 1][0], qlo[2 * cp + 1][1]);
             }
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[i] += sc2[i];
         // log2-domain scores; rows past the range are masked out
         const float ninf = -INFINITY;
         const float s00 = v0 ? sc[0] * (skA * cs0) : ninf;

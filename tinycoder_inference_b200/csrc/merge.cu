@@ -4,11 +4,9 @@
 // for one (token, q-head) with chunk partials (m_c, l_c, acc_c[hd]):
 //   M = max_c m_c;  w_c = exp2((m_c - M) * log2e);  chunks with l_c <= 0 skipped;
 //   out = sum_c w_c acc_c / sum_c w_c l_c   (0 when nothing contributed).
-// One block per (head, token): 8 warps each fold every 8th chunk with 128-bit
-// loads (a lane owns 4 consecutive dims per 128-dim group), then the 8 warp
-// partials are folded through shared memory -- the shape of the reference's
-// kAttnCombinePartialW4 (:1003-1098).  The same kernel merges partials gathered
-// from other GPUs when the context axis is split across ranks.
+// One block per (head, token), 8 warps; a lane owns 4 consecutive dims per
+// 128-dim group (128-bit loads).  The same kernel merges partials gathered from
+// other GPUs when the context axis is split across ranks.
 //
 // Optional epilogue: the Q8_1 blocks of the output for the GEMV that follows
 // attention (40-byte slots {fp16 d, fp16 sum, int8 q[32]}, :1068-1096).  The
@@ -18,6 +16,14 @@
 
 namespace tc {
 
+constexpr int kMergeMaxChunks = 4096;
+
+// Phase 1: all 256 threads read (m, l) of the active chunks at once, the block
+// takes the max, and the per-chunk weights w_c = exp2((m_c - M) * log2e) (0 for
+// empty chunks) land in shared memory.  Phase 2: warp w accumulates chunks
+// w, w+8, ... with independent 128-bit loads (nothing in the loop depends on a
+// previous load, so all of a warp's reads are in flight together -- the merge is
+// a latency problem, not a bandwidth one).  Phase 3: the 8 warp sums are added.
 template <int NV4>
 __global__ void __launch_bounds__(256)
 mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM, const float *__restrict__ pL,
@@ -35,23 +41,54 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
         const uint32_t need = (len + chunkTokens - 1) / chunkTokens;
         active = need < numChunks ? need : numChunks;
     }
+    __shared__ float sw[kMergeMaxChunks];
+    __shared__ float sred[NW];
+    __shared__ float4 sacc[NW][NV4][32];
+    __shared__ float sout[NV4 * 128];
+
+    // ---- phase 1: max, weights, normaliser ----
     float M = kNegBig;
-    for (uint32_t c = warp; c < active; c += NW) M = fmaxf(M, pM[base + c]);
+    for (uint32_t c = threadIdx.x; c < active; c += 256) {
+        const float m = pM[base + c];
+        sw[c] = m;
+        M = fmaxf(M, m);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) sred[warp] = M;
+    __syncthreads();
+    M = sred[0];
+#pragma unroll
+    for (int w2 = 1; w2 < NW; ++w2) M = fmaxf(M, sred[w2]);
+    __syncthreads();
+    float lsum = 0.0f;
+    for (uint32_t c = threadIdx.x; c < active; c += 256) {
+        const float lc = pL[base + c];
+        const float w = lc > 0.0f ? exp2f((sw[c] - M) * kLog2e) : 0.0f;
+        sw[c] = w;
+        lsum = fmaf(w, lc > 0.0f ? lc : 0.0f, lsum);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+    if (lane == 0) sred[warp] = lsum;
+    __syncthreads();
+    lsum = 0.0f;
+#pragma unroll
+    for (int w2 = 0; w2 < NW; ++w2) lsum += sred[w2];
+
+    // ---- phase 2: weighted sum of the accumulators ----
     float4 acc[NV4];
 #pragma unroll
     for (int j = 0; j < NV4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    float lsum = 0.0f;
     const uint32_t nvec = hd >> 2;
+#pragma unroll 4
     for (uint32_t c = warp; c < active; c += NW) {
-        const float lc = pL[base + c];
-        if (lc <= 0.0f) continue;
-        const float w = exp2f((pM[base + c] - M) * kLog2e);
-        lsum += w * lc;
+        const float w = sw[c];
         const float4 *pac = reinterpret_cast<const float4 *>(pAcc + (base + c) * hd);
 #pragma unroll
         for (int j = 0; j < NV4; ++j) {
             const uint32_t i = lane + 32u * j;
-            if (i < nvec) {
+            if (i < nvec && w != 0.0f) {  // an empty chunk's accumulator may hold anything
                 const float4 a = pac[i];
                 acc[j].x = fmaf(w, a.x, acc[j].x);
                 acc[j].y = fmaf(w, a.y, acc[j].y);
@@ -60,43 +97,27 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
             }
         }
     }
-    __shared__ float sm[NW], sl[NW];
-    __shared__ float4 sacc[NW][NV4][32];
-    __shared__ float sout[NV4 * 128];
-    if (lane == 0) {
-        sm[warp] = M;
-        sl[warp] = lsum;
-    }
 #pragma unroll
     for (int j = 0; j < NV4; ++j) sacc[warp][j][lane] = acc[j];
     __syncthreads();
+    // ---- phase 3 ----
     if (warp == 0) {
-        float gM = kNegBig;
-#pragma unroll
-        for (int w2 = 0; w2 < NW; ++w2) gM = fmaxf(gM, sm[w2]);
-        float gL = 0.0f;
-#pragma unroll
-        for (int j = 0; j < NV4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int w2 = 0; w2 < NW; ++w2) {
-            const float w = exp2f((sm[w2] - gM) * kLog2e);
-            gL += w * sl[w2];
-#pragma unroll
-            for (int j = 0; j < NV4; ++j) {
-                const float4 a = sacc[w2][j][lane];
-                acc[j].x = fmaf(w, a.x, acc[j].x);
-                acc[j].y = fmaf(w, a.y, acc[j].y);
-                acc[j].z = fmaf(w, a.z, acc[j].z);
-                acc[j].w = fmaf(w, a.w, acc[j].w);
-            }
-        }
-        const float inv = gL > 0.0f ? 1.0f / gL : 0.0f;
+        const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
         float4 *op = reinterpret_cast<float4 *>(out + (static_cast<uint64_t>(s) * nHeads + head) * hd);
 #pragma unroll
         for (int j = 0; j < NV4; ++j) {
+            float4 r = sacc[0][j][lane];
+#pragma unroll
+            for (int w2 = 1; w2 < NW; ++w2) {
+                const float4 a = sacc[w2][j][lane];
+                r.x += a.x;
+                r.y += a.y;
+                r.z += a.z;
+                r.w += a.w;
+            }
             const uint32_t i = lane + 32u * j;
             if (i < nvec) {
-                const float4 r = make_float4(acc[j].x * inv, acc[j].y * inv, acc[j].z * inv, acc[j].w * inv);
+                r = make_float4(r.x * inv, r.y * inv, r.z * inv, r.w * inv);
                 op[i] = r;
                 reinterpret_cast<float4 *>(sout)[i] = r;
             }
@@ -150,6 +171,8 @@ int tc_attn_merge_partials(const float *pAcc, const float *pM, const float *pL, 
     TC_REQUIRE(hd >= 32 && hd <= 256 && (hd % 32u) == 0, TC_EUNSUPPORTED,
                "tc_attn_merge_partials: hd=%u must be a multiple of 32 in [32, 256]", hd);
     TC_REQUIRE(numChunks >= 1 && nHeads >= 1, TC_EINVAL, "tc_attn_merge_partials: empty shape");
+    TC_REQUIRE(numChunks <= tc::kMergeMaxChunks, TC_EUNSUPPORTED, "tc_attn_merge_partials: %u chunks (max %d)",
+               numChunks, tc::kMergeMaxChunks);
     TC_REQUIRE(seqLen <= 65535, TC_EUNSUPPORTED, "tc_attn_merge_partials: seqLen %u > 65535", seqLen);
     if (seqLen == 0) return TC_OK;
     return tc::launchMerge(pAcc, pM, pL, out, seqLen, nHeads, numChunks, numChunks, hd, nullptr, 0, 1, q81Out,
