@@ -191,7 +191,8 @@ def workload_config(name, gpus):
             "sharding": "by sequence, one replica of the workload per GPU, no collective" if gpus > 1 else "single GPU",
             "l2": f"inputs larger than L2: a step streams {layers} distinct KV pools "
                   f"({layers * batch * algorithmic_bytes(nKV, hd, ctx) / 1e6:.0f} MB)",
-            "launch": "cuda_graph"}
+            "launch": "cuda_graph; kernels chained by programmatic dependent launch (old KV rows stream in "
+                      "while the previous kernel drains; us_per_layer_plain_stream_order is the same step without it)"}
 
 
 # ---------------------------------------------------------------------------------
@@ -207,6 +208,8 @@ def main():
     ap.add_argument("--workload", default="decode32k", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true", help="plain stream order between the kernels of a step")
+    ap.add_argument("--partials-only", action="store_true", help="diagnostic: skip the merge launch")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -249,29 +252,35 @@ def main():
     lens = torch.full((batch,), ctx, dtype=torch.int32, device=dev)
     torch.cuda.synchronize()
 
-    def step():
+    lens_arg = None  # host lengths: every sequence holds exactly ctx rows
+
+    def step(pdl):
+        # rows [0, ctx-1) are old rows; the last row is the one a decode step appends
         for l in range(layers):
-            if batch == 1:
-                ops.decode_i8(q[l], k8[l, 0], v8[l, 0], ks[l, 0], vs[l, 0], out[l], ws, nH, nKV, hd, ctx - 1, chunks,
-                              chunk, inv)
-            else:
-                ops.decode_i8_batch(q[l], k8[l], v8[l], ks[l], vs[l], out[l], ws, lens, batch, nH, nKV, hd, ctx,
-                                    chunks, rows_per_seq=rows, invSqrt=inv)
+            ops.decode_i8_batch(q[l], k8[l], v8[l], ks[l], vs[l], out[l], ws, lens_arg, batch, nH, nKV, hd, ctx,
+                                chunks, rows_per_seq=rows, invSqrt=inv, pdl=pdl, prefetch_rows=ctx - 1,
+                                partials_only=args.partials_only)
 
     launches_per_step = layers * 2
-    step()
+    step(False)
+    step(True)
     torch.cuda.synchronize()
-    graph = None
-    if not args.no_graph:
-        s = torch.cuda.Stream()
-        s.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(s):
-            step()
-        torch.cuda.current_stream().wait_stream(s)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-    run = graph.replay if graph is not None else step
+
+    def capture(pdl):
+        if args.no_graph:
+            return lambda: step(pdl)
+        s_ = torch.cuda.Stream()
+        s_.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s_):
+            step(pdl)
+        torch.cuda.current_stream().wait_stream(s_)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            step(pdl)
+        return gr.replay
+
+    run_plain = capture(False)
+    run = capture(True) if not args.no_pdl else run_plain
 
     def barrier():
         if world > 1:
@@ -300,6 +309,16 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     ms_per_step = ms / args.steps
+    # the same step without programmatic dependent launch (no overlap between kernels)
+    for _ in range(3):
+        run_plain()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        run_plain()
+    e1.record()
+    barrier()
+    ms_plain_per_step = e0.elapsed_time(e1) / args.steps
     bytes_per_step_gpu = layers * batch * algorithmic_bytes(nKV, hd, ctx)
     value = world * bytes_per_step_gpu / (ms_per_step * 1e-3) / 1e9
     us_per_layer = ms_per_step * 1e3 / layers
@@ -323,12 +342,8 @@ def main():
             dv.copy_(hv[l], non_blocking=True)
             for b in range(batch):
                 ops.kv_quantize_i8(dk[b], dv[b], k8[l, b], v8[l, b], ks[l, b], vs[l, b], 1, nKV, hd, dst_base=ctx - 1)
-            if batch == 1:
-                ops.decode_i8(dq, k8[l, 0], v8[l, 0], ks[l, 0], vs[l, 0], dout, ws, nH, nKV, hd, ctx - 1, chunks,
-                              chunk, inv)
-            else:
-                ops.decode_i8_batch(dq, k8[l], v8[l], ks[l], vs[l], dout, ws, lens, batch, nH, nKV, hd, ctx, chunks,
-                                    rows_per_seq=rows, invSqrt=inv)
+            ops.decode_i8_batch(dq, k8[l], v8[l], ks[l], vs[l], dout, ws, lens_arg, batch, nH, nKV, hd, ctx, chunks,
+                                rows_per_seq=rows, invSqrt=inv, pdl=not args.no_pdl, prefetch_rows=ctx - 1)
             hout[l].copy_(dout, non_blocking=True)
         torch.cuda.synchronize()
 
@@ -361,7 +376,9 @@ def main():
     line = {
         "metric": "decode_attn_kv_gbs_ctx32k" if args.workload == "decode32k" else f"decode_attn_kv_gbs_{args.workload}",
         "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "us_per_layer": us_per_layer, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": ms_per_step, "us_per_layer": us_per_layer,
+        "us_per_layer_plain_stream_order": ms_plain_per_step * 1e3 / layers,
+        "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 KV, f32 q/out (fp16 hi+lo tensor-core products, f32 accumulate)",
         "data": "synthetic", "config": workload_config(args.workload, world),
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",

@@ -142,7 +142,8 @@ int tc_attn_decode_i8(const float *q, const int8_t *k8, const int8_t *v8,
  * int8 pool (the serving mix: one decode step of many sessions).  Sequence b
  * occupies pool rows [rowBase[b], rowBase[b] + lens[b]); rowBase == NULL means
  * b * rowsPerSeq.  lens / rowBase are DEVICE arrays (uint32 / uint64); maxLen is
- * the host's upper bound on lens[] and sizes the grid.  q/out: [batch][nHeads][hd].
+ * the host's upper bound on lens[] and sizes the grid; lens == NULL means every
+ * sequence is exactly maxLen rows long.  q/out: [batch][nHeads][hd].
  * partialsOnly != 0 skips the merge and leaves (m, l, acc) per chunk in
  * pAcc/pM/pL -- the form a context-axis split across GPUs exchanges;
  * *chunksUsed (HOST, nullable) receives the chunk slots written per head. */
@@ -162,7 +163,19 @@ typedef struct tc_decode_i8_batch {
     float invSqrt;
     int partialsOnly;
     uint32_t *chunksUsed; /* HOST out, nullable */
+    /* flags & TC_DECODE_PDL: launch with programmatic dependent launch, i.e. the
+     * kernels may begin while the kernels ahead of them in the stream drain.
+     * Whatever a kernel in flight may still write is read only after those
+     * kernels have completed: q, the lengths, and every K/V row >= prefetchRows.
+     * Rows [0, prefetchRows) of each sequence -- rows no kernel in flight writes,
+     * e.g. everything before the token being appended -- are streamed in early,
+     * but only with host lengths (lens == NULL: every sequence is maxLen rows
+     * long) and rowBase == NULL.  flags == 0 keeps plain stream order. */
+    uint32_t flags;
+    uint32_t prefetchRows;
 } tc_decode_i8_batch;
+
+enum { TC_DECODE_PDL = 1u };
 
 int tc_attn_decode_i8_batch(const tc_decode_i8_batch *d, tc_stream stream);
 

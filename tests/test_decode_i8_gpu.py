@@ -159,3 +159,41 @@ def test_partials_contract_and_merge_entry_point():
                         numChunks, partials_only=True)
     torch.cuda.synchronize()
     assert all(torch.equal(a, b) for a, b in zip(ws, ws2))
+
+
+def test_dependent_launch_chain_and_host_lengths():
+    """Three 'layers' back to back with programmatic dependent launch (KV rows of a
+    layer stream in while the previous layer's kernels drain) give the same
+    bits as plain stream order; lens=None means every sequence is maxLen long."""
+    nH, nKV, hd, ctx, B, layers, numChunks = 28, 4, 128, 3000, 2, 3, 64
+    rows = ctx + 16
+    rng = np.random.default_rng(17)
+    inv = 1.0 / math.sqrt(hd)
+    q = rng.standard_normal((layers, B, nH, hd), dtype=np.float32)
+    pools, want = [], np.zeros((layers, B, nH, hd), np.float32)
+    for l in range(layers):
+        k8 = np.zeros((B, rows, nKV, hd), np.int8)
+        v8 = np.zeros_like(k8)
+        ks = np.full((B, rows, nKV), np.nan, np.float32)
+        vs = np.full_like(ks, np.nan)
+        for b in range(B):
+            a, c, d, e = oracle.quant_kv8(rng.standard_normal((ctx, nKV, hd), dtype=np.float32),
+                                          rng.standard_normal((ctx, nKV, hd), dtype=np.float32), nKV, hd)
+            k8[b, :ctx], v8[b, :ctx], ks[b, :ctx], vs[b, :ctx] = a, c, d, e
+            want[l, b] = oracle.attention_i8(q[l, b:b + 1], a, c, d, e, 1, nH, nKV, hd, ctx - 1, inv)[0]
+        pools.append(tuple(dev(x) for x in (k8, v8, ks, vs)))
+    qd = dev(q)
+    ws = ops.workspace(B, nH, hd, numChunks)
+    outs = {}
+    for pdl in (False, True):
+        out = torch.full((layers, B, nH, hd), float("nan"), device="cuda")
+        for rep in range(2):
+            for l in range(layers):
+                k8, v8, ks, vs = pools[l]
+                ops.decode_i8_batch(qd[l], k8, v8, ks, vs, out[l], ws, None, B, nH, nKV, hd, ctx, numChunks,
+                                    rows_per_seq=rows, invSqrt=inv, pdl=pdl, prefetch_rows=ctx - 1)
+        torch.cuda.synchronize()
+        assert ops.device_status() == 0
+        assert_close(host(out), want, what=f"pdl={pdl}")
+        outs[pdl] = out
+    assert torch.equal(outs[False], outs[True])

@@ -21,6 +21,7 @@ TC_EWORKSPACE = 5
 TC_EDEVICE = 6
 TC_KV_F32 = 0
 TC_KV_I8 = 1
+TC_DECODE_PDL = 1
 
 
 class TcError(RuntimeError):
@@ -117,6 +118,8 @@ class DecodeI8Batch(C.Structure):
         ("invSqrt", C.c_float),
         ("partialsOnly", C.c_int),
         ("chunksUsed", C.POINTER(C.c_uint32)),
+        ("flags", C.c_uint32),
+        ("prefetchRows", C.c_uint32),
     ]
 
 

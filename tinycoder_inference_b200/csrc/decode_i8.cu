@@ -32,7 +32,7 @@ namespace tc {
 
 int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out, uint32_t seqLen,
                 uint32_t nHeads, uint32_t numChunks, uint32_t activeHost, uint32_t hd, const uint32_t *devLens,
-                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, cudaStream_t st);
+                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st);
 
 struct DecodeI8Params {
     const float *q;
@@ -45,22 +45,28 @@ struct DecodeI8Params {
     uint32_t lenHost, lenAdd;
     uint32_t nHeads, nKV, group;
     uint32_t chunkTokens, numChunks;
+    uint32_t prefetchRows;  // rows [0, prefetchRows) of a sequence may be read before the dependency wait
     float invSqrt;
     int directOut;
     unsigned int *err;
 };
 
 constexpr int kHD = 128;
-
-template <int HPC, int NW, int NSTAGE>
+// MT = 16-row MMA tiles one consumer warp folds per stage: 2 amortises the softmax
+// bookkeeping over 32 tokens (large problems), 1 halves the work quantum so that a
+// small problem still spreads evenly over 148 SMs x 8 warps.
+template <int HPC, int NW, int NSTAGE, int MT>
 struct DecodeI8Smem {
-    static constexpr int T = NW * 16 / HPC;              // tokens per stage
-    static constexpr int kTileBytes = NW * 16 * kHD;     // K (or V) bytes per stage, all HPC heads
-    static constexpr int kScaleBytes = NW * 16 * 4;
+    static constexpr int kTokPerWarp = 16 * MT;
+    static constexpr int kRows = NW * kTokPerWarp;       // (token, head) rows per stage
+    static constexpr int T = kRows / HPC;                 // tokens per stage
+    static constexpr int kTileBytes = kRows * kHD;        // K (or V) bytes per stage, all HPC heads
+    static constexpr int kScaleBytes = kRows * 4;
     static constexpr int kStageBytes = 2 * kTileBytes + 2 * kScaleBytes;
     static constexpr int kBarOffset = NSTAGE * kStageBytes;
     static constexpr int kTotal = kBarOffset + 2 * NSTAGE * 8 + 1024;  // + alignment slack
     static_assert(kStageBytes % 1024 == 0, "stage must keep 1024-byte alignment for the 128B swizzle");
+    static_assert(T <= 256, "TMA box rows");
 };
 
 __device__ __forceinline__ bool mbarWaitClock(uint64_t *bar, uint32_t parity, unsigned int *err,
@@ -77,28 +83,28 @@ __device__ __forceinline__ bool mbarWaitClock(uint64_t *bar, uint32_t parity, un
     return false;
 }
 
-template <int HPC, int NW, int NSTAGE, int MINB>
-__global__ void __launch_bounds__((NW + 1) * 32, MINB)
+// How far the running reference point of the softmax may lag behind the true
+// maximum (log2 units) before the accumulators are rescaled.  p stays <= 2^8.
+constexpr float kLazyLog2 = 8.0f;
+
+template <int HPC, int NW, int NSTAGE, int MT>
+__global__ void __launch_bounds__((NW + 1) * 32, 1)
 decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                const DecodeI8Params p) {
-    using L = DecodeI8Smem<HPC, NW, NSTAGE>;
+    using L = DecodeI8Smem<HPC, NW, NSTAGE, MT>;
     constexpr int T = L::T;
+    constexpr int kTokPerWarp = L::kTokPerWarp;
+    constexpr int NR = 2 * MT;  // 8-token row groups of a warp's tile
     constexpr int NSUB = NW / HPC;  // consumer warps per kv head
+    constexpr float k2p24 = 16777216.0f;
 
     const uint32_t chunk = blockIdx.x, hg = blockIdx.y, b = blockIdx.z;
-    const uint32_t len = p.devLens ? p.devLens[b] + p.lenAdd : p.lenHost;
-    const uint32_t t0 = chunk * p.chunkTokens;
-    if (t0 >= len) return;  // inactive chunk: the merge derives the active count from len
-    const uint32_t t1 = min(len, t0 + p.chunkTokens);
-    const uint32_t nTiles = (t1 - t0 + T - 1) / T;
-    const uint64_t rowBase = p.devRowBase ? p.devRowBase[b] : static_cast<uint64_t>(b) * p.rowsPerSeq;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
 
     extern __shared__ uint8_t smemRaw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
     uint64_t *fullBar = reinterpret_cast<uint64_t *>(smem + L::kBarOffset);
     uint64_t *emptyBar = fullBar + NSTAGE;
-
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
@@ -110,17 +116,39 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         tmaPrefetchDesc(&tmV);
     }
     __syncthreads();
+    gridDepLaunch();  // the dependent grid (the merge) may be scheduled as soon as room frees up
+
+    // The length may live in device memory written by an earlier kernel; only a
+    // host-known length lets the producer start before the dependency wait.
+    uint32_t len = p.lenHost;
+    const bool earlyOk = p.devLens == nullptr && p.devRowBase == nullptr && p.prefetchRows != 0;
+    if (!earlyOk) {
+        gridDepWait();
+        if (p.devLens) len = p.devLens[b] + p.lenAdd;
+    }
+    const uint32_t t0 = chunk * p.chunkTokens;
+    if (t0 >= len) return;  // inactive chunk: the merge derives the active count from len
+    const uint32_t t1 = min(len, t0 + p.chunkTokens);
+    const uint32_t nTiles = (t1 - t0 + T - 1) / T;
+    const uint64_t rowBase = p.devRowBase ? p.devRowBase[b] : static_cast<uint64_t>(b) * p.rowsPerSeq;
 
     if (warp == NW) {
         // ------------------------------ producer ------------------------------
         const uint32_t kvHead0 = hg * HPC;
+        bool waited = !earlyOk;
         for (uint32_t it = 0; it < nTiles; ++it) {
             const uint32_t s = it % NSTAGE;
             if (it >= NSTAGE) {
                 if (!mbarWaitClock(&emptyBar[s], ((it / NSTAGE) - 1) & 1, p.err, kDevErrEmptyWait)) break;
             }
+            const uint32_t tok = t0 + it * T;
+            if (!waited && tok + T > p.prefetchRows) {
+                // this tile may hold rows appended by the kernel we depend on
+                gridDepWait();
+                waited = true;
+            }
             uint8_t *st = smem + s * L::kStageBytes;
-            const uint64_t row = rowBase + t0 + static_cast<uint64_t>(it) * T;
+            const uint64_t row = rowBase + tok;
             if (lane == 0) {
                 mbarExpectTx(&fullBar[s], 2 * L::kTileBytes);
 #pragma unroll
@@ -131,9 +159,9 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 }
             }
             float *sK = reinterpret_cast<float *>(st + 2 * L::kTileBytes);
-            float *sV = sK + NW * 16;
+            float *sV = sK + L::kRows;
 #pragma unroll
-            for (int idx = lane; idx < HPC * T; idx += 32) {
+            for (int idx = lane; idx < L::kRows; idx += 32) {
                 const int h = idx / T, tt = idx % T;
                 uint64_t r = row + tt;
                 r = r < p.totalRows ? r : p.totalRows - 1;
@@ -146,6 +174,7 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
 
     // -------------------------------- consumers --------------------------------
+    if (earlyOk) gridDepWait();  // q comes from a kernel that may still be running
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t hL = warp % HPC, sub = warp / HPC;
     const uint32_t kvHead = hg * HPC + hL;
@@ -154,7 +183,7 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     // normalised, split into fp16 hi + lo, laid out as the B operand whose k
     // slots follow the byte order ldmatrix hands out (dims 16c + 4t + {0..3}).
     uint32_t qhi[8][2], qlo[8][2];
-    float headScale;
+    float headScale, headOff;
     {
         float4 qv[8];
         float amax = 0.0f;
@@ -173,6 +202,7 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const float down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);  // 2^-e
         const float up = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);    // 2^e
         headScale = p.invSqrt * up * kLog2e;
+        float qsum = 0.0f;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             float h0, l0, h1, l1, h2, l2, h3, l3;
@@ -184,14 +214,23 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             qhi[c][1] = packHalf2(h2, h3);
             qlo[c][0] = packHalf2(l0, l1);
             qlo[c][1] = packHalf2(l2, l3);
+            // the column sum the MMA really sees: the fp16-rounded parts
+            const __half2 a = *reinterpret_cast<__half2 *>(&qlo[c][0]), bb = *reinterpret_cast<__half2 *>(&qlo[c][1]);
+            qsum += (h0 + __low2float(a)) + (h1 + __high2float(a)) + (h2 + __low2float(bb)) + (h3 + __high2float(bb));
         }
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+        headOff = 128.0f * qsum;  // K bytes enter the MMA as x + 128
     }
-    // score columns of this thread are heads 2t and 2t+1: fetch their scales
+    // score columns of this thread are heads 2t and 2t+1: fetch their constants
     const float cs0 = __shfl_sync(0xffffffffu, headScale, (2 * t) * 4);
     const float cs1 = __shfl_sync(0xffffffffu, headScale, (2 * t + 1) * 4);
+    const float off0 = __shfl_sync(0xffffffffu, headOff, (2 * t) * 4);
+    const float off1 = __shfl_sync(0xffffffffu, headOff, (2 * t + 1) * 4);
 
     float m0 = kNegBig, m1 = kNegBig, l0 = 0.0f, l1 = 0.0f;
-    uint32_t Ebits = 0;  // running power-of-two scale of the V row scales (0 = unset)
+    float ps0 = 0.0f, ps1 = 0.0f;  // sum of p*sv as fed to the PV MMA (V bytes enter as x + 128)
+    uint32_t Ebits = 0;            // running power-of-two scale of the V row scales (0 = unset)
     float invE = 0.0f;
     float o[8][4];
 #pragma unroll
@@ -199,65 +238,89 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
     const uint32_t lr = (lane & 7u) + ((lane >> 3) & 1u) * 8u;  // ldmatrix row this lane addresses
     const uint32_t lco = lane >> 4;                             // and which chunk of the pair
-    bool ok = true;
+    const uint32_t lmOff = lr * 128;
 
     for (uint32_t it = 0; it < nTiles; ++it) {
         const uint32_t s = it % NSTAGE;
-        if (!mbarWaitClock(&fullBar[s], (it / NSTAGE) & 1, p.err, kDevErrFullWait)) {
-            ok = false;
-            break;
-        }
+        if (!mbarWaitClock(&fullBar[s], (it / NSTAGE) & 1, p.err, kDevErrFullWait)) break;
         uint8_t *st = smem + s * L::kStageBytes;
-        const float *sK = reinterpret_cast<const float *>(st + 2 * L::kTileBytes) + hL * T + sub * 16;
-        const float *sV = sK + NW * 16;
-        const uint32_t tok0 = t0 + it * T + sub * 16 + g;
-        const bool v0 = tok0 < t1, v1 = tok0 + 8 < t1;
-        const float skA = sK[g], skB = sK[g + 8];
-        const float svA = v0 ? sV[g] : 0.0f, svB = v1 ? sV[g + 8] : 0.0f;
+        const uint32_t rowInTile = hL * T + sub * kTokPerWarp;
+        const float *sK = reinterpret_cast<const float *>(st + 2 * L::kTileBytes) + rowInTile;
+        const float *sV = sK + L::kRows;
+        const uint32_t tokBase = t0 + it * T + sub * kTokPerWarp + g;
+        bool vld[NR];
+        float skr[NR], svr[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {  // rows g, g+8, ... of this warp's tokens
+            vld[r] = tokBase + 8 * r < t1;
+            skr[r] = sK[g + 8 * r];
+            svr[r] = vld[r] ? sV[g + 8 * r] : 0.0f;
+        }
 
-        // ---- S^T = K . Q^T (16 tokens x 8 heads) ----
-        // two accumulators (hi and lo parts of q) keep the MMA dependency chains short
-        float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc2[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint32_t kTile = smemAddr(st + (hL * T + sub * 16) * kHD);
+        // ---- S^T = K . Q^T, two 16-token tiles x 8 heads ----
+        float sh[MT][4], sl[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sh[mt][i] = sl[mt][i] = 0.0f;
+        const uint32_t kTile = smemAddr(st + rowInTile * kHD);
 #pragma unroll
         for (int cp = 0; cp < 4; ++cp) {
-            uint32_t r0, r1, r2, r3;
-            const uint32_t chunkIdx = 2 * cp + lco;
-            ldmatrixX4(r0, r1, r2, r3, kTile + lr * 128 + ((chunkIdx ^ (lr & 7u)) << 4));
-            r0 ^= 0x80808080u;
-            r1 ^= 0x80808080u;
-            r2 ^= 0x80808080u;
-            r3 ^= 0x80808080u;
-            {
-                const uint32_t a0 = biasedPairLo(r0), a1 = biasedPairLo(r1), a2 = biasedPairHi(r0),
-                               a3 = biasedPairHi(r1);
-                mmaF16(sc, a0, a1, a2, a3, qhi[2 * cp][0], qhi[2 * cp][1]);
-                mmaF16(sc2, a0, a1, a2, a3, qlo[2 * cp][0], qlo[2 * cp][1]);
-            }
-            {
-                const uint32_t a0 = biasedPairLo(r2), a1 = biasedPairLo(r3), a2 = biasedPairHi(r2),
-                               a3 = biasedPairHi(r3);
-                mmaF16(sc, a0, a1, a2, a3, qhi[2 * cp + 1][0], qhi[2 * cp + 1][1]);
-                mmaF16(sc2, a0, a1, a2, a3, qlo[2 * cp + 1][0], qlo[2 * cp + 1][1]);
+            const uint32_t sw = ((2 * cp + lco) ^ (lr & 7u)) << 4;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint32_t r0, r1, r2, r3;
+                ldmatrixX4(r0, r1, r2, r3, kTile + mt * 2048 + lmOff + sw);
+                r0 ^= 0x80808080u;
+                r1 ^= 0x80808080u;
+                r2 ^= 0x80808080u;
+                r3 ^= 0x80808080u;
+                {
+                    const uint32_t a0 = subnormalPair<0x4140>(r0), a1 = subnormalPair<0x4140>(r1),
+                                   a2 = subnormalPair<0x4342>(r0), a3 = subnormalPair<0x4342>(r1);
+                    mmaF16(sh[mt], a0, a1, a2, a3, qhi[2 * cp][0], qhi[2 * cp][1]);
+                    mmaF16(sl[mt], a0, a1, a2, a3, qlo[2 * cp][0], qlo[2 * cp][1]);
+                }
+                {
+                    const uint32_t a0 = subnormalPair<0x4140>(r2), a1 = subnormalPair<0x4140>(r3),
+                                   a2 = subnormalPair<0x4342>(r2), a3 = subnormalPair<0x4342>(r3);
+                    mmaF16(sh[mt], a0, a1, a2, a3, qhi[2 * cp + 1][0], qhi[2 * cp + 1][1]);
+                    mmaF16(sl[mt], a0, a1, a2, a3, qlo[2 * cp + 1][0], qlo[2 * cp + 1][1]);
+                }
             }
         }
+        // log2-domain scores: undo the 2^-24 of the subnormal operand and the +128 offset,
+        // apply the row's K scale; rows past the range are masked out
+        float sc[NR][2];  // [row r][head 2t / 2t+1]
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sc[i] += sc2[i];
-        // log2-domain scores; rows past the range are masked out
-        const float ninf = -INFINITY;
-        const float s00 = v0 ? sc[0] * (skA * cs0) : ninf;
-        const float s01 = v0 ? sc[1] * (skA * cs1) : ninf;
-        const float s10 = v1 ? sc[2] * (skB * cs0) : ninf;
-        const float s11 = v1 ? sc[3] * (skB * cs1) : ninf;
-        float mx0 = fmaxf(s00, s10), mx1 = fmaxf(s01, s11);
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int r = 2 * mt + hf;
+                const float d0 = fmaf(sh[mt][2 * hf] + sl[mt][2 * hf], k2p24, -off0);
+                const float d1 = fmaf(sh[mt][2 * hf + 1] + sl[mt][2 * hf + 1], k2p24, -off1);
+                sc[r][0] = vld[r] ? d0 * (skr[r] * cs0) : -INFINITY;
+                sc[r][1] = vld[r] ? d1 * (skr[r] * cs1) : -INFINITY;
+            }
+        }
+        float mx0 = fmaxf(sc[0][0], sc[1][0]), mx1 = fmaxf(sc[0][1], sc[1][1]);
+        float svmax = fmaxf(svr[0], svr[1]);
+#pragma unroll
+        for (int r = 2; r < NR; ++r) {
+            mx0 = fmaxf(mx0, sc[r][0]);
+            mx1 = fmaxf(mx1, sc[r][1]);
+            svmax = fmaxf(svmax, svr[r]);
+        }
 #pragma unroll
         for (int off = 4; off <= 16; off <<= 1) {
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
         }
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        // lazy reference point: move it only when the maximum ran ahead by 2^8
+        const float mn0 = mx0 > m0 + kLazyLog2 ? mx0 : m0;
+        const float mn1 = mx1 > m1 + kLazyLog2 ? mx1 : m1;
         // running power-of-two bound of the V scales (keeps p*sv inside fp16)
-        uint32_t eb = __reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(svA, svB))) & 0x7f800000u;
+        uint32_t eb = __reduce_max_sync(0xffffffffu, __float_as_uint(svmax)) & 0x7f800000u;
         eb = min(eb, 253u << 23);
         float fE = 1.0f;
         if (eb > Ebits) {
@@ -266,11 +329,9 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             Ebits = eb;
             invE = newInv;
         }
-        const float a0s = fastExp2(m0 - mn0), a1s = fastExp2(m1 - mn1);
-        const float al0 = a0s * fE, al1 = a1s * fE;
-        m0 = mn0;
-        m1 = mn1;
-        if (__any_sync(0xffffffffu, al0 != 1.0f || al1 != 1.0f)) {
+        if (__any_sync(0xffffffffu, mn0 != m0 || mn1 != m1 || fE != 1.0f)) {
+            const float a0s = fastExp2(m0 - mn0), a1s = fastExp2(m1 - mn1);
+            const float al0 = a0s * fE, al1 = a1s * fE;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 o[i][0] *= al0;
@@ -278,76 +339,92 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 o[i][2] *= al0;
                 o[i][3] *= al1;
             }
+            l0 *= a0s;
+            l1 *= a1s;
+            ps0 *= al0;
+            ps1 *= al1;
+            m0 = mn0;
+            m1 = mn1;
         }
-        const float p00 = fastExp2(s00 - mn0), p01 = fastExp2(s01 - mn1);
-        const float p10 = fastExp2(s10 - mn0), p11 = fastExp2(s11 - mn1);
-        l0 = l0 * a0s + (p00 + p10);
-        l1 = l1 * a1s + (p01 + p11);
-        // p * sv (scaled into fp16 range), hi + lo, then transposed to the B layout
-        uint32_t bh0, bh1, bl0, bl1;
-        {
-            const float wA = svA * invE, wB = svB * invE;
-            float h00, q00, h01, q01, h10, q10, h11, q11;
-            splitHalf(p00 * wA, h00, q00);
-            splitHalf(p01 * wA, h01, q01);
-            splitHalf(p10 * wB, h10, q10);
-            splitHalf(p11 * wB, h11, q11);
-            bh0 = movmatrixTrans(packHalf2(h00, h01));
-            bh1 = movmatrixTrans(packHalf2(h10, h11));
-            bl0 = movmatrixTrans(packHalf2(q00, q01));
-            bl1 = movmatrixTrans(packHalf2(q10, q11));
-        }
-        // ---- O^T += V^T . P^T (128 dims x 8 heads) ----
-        const uint8_t *vTile = st + L::kTileBytes + (hL * T + sub * 16) * kHD;
-        const uint32_t ra = 2 * t, rb = 2 * t + 1;  // token rows 2t, 2t+1 (and +8); (row & 7) is the swizzle key
+        // p, then p * sv scaled into fp16 range, hi + lo, transposed to the B layout
+        uint32_t bh[MT][2], bl[MT][2];
 #pragma unroll
-        for (int blk = 0; blk < 4; ++blk) {
-            const uint32_t ch = 2 * blk + (g >> 2), off = 4 * (g & 3u);
-            uint32_t w0 = *reinterpret_cast<const uint32_t *>(vTile + ra * 128 + ((ch ^ ra) << 4) + off);
-            uint32_t w1 = *reinterpret_cast<const uint32_t *>(vTile + rb * 128 + ((ch ^ rb) << 4) + off);
-            uint32_t w2 = *reinterpret_cast<const uint32_t *>(vTile + (ra + 8) * 128 + ((ch ^ ra) << 4) + off);
-            uint32_t w3 = *reinterpret_cast<const uint32_t *>(vTile + (rb + 8) * 128 + ((ch ^ rb) << 4) + off);
-            w0 ^= 0x80808080u;
-            w1 ^= 0x80808080u;
-            w2 ^= 0x80808080u;
-            w3 ^= 0x80808080u;
-            const uint32_t X = __byte_perm(w0, w1, 0x5140), Y = __byte_perm(w0, w1, 0x7362);
-            const uint32_t X2 = __byte_perm(w2, w3, 0x5140), Y2 = __byte_perm(w2, w3, 0x7362);
-            {
-                const uint32_t a0 = biasedPairLo(X), a1 = biasedPairHi(X), a2 = biasedPairLo(X2),
-                               a3 = biasedPairHi(X2);
-                mmaF16(o[2 * blk], a0, a1, a2, a3, bh0, bh1);
-                mmaF16(o[2 * blk], a0, a1, a2, a3, bl0, bl1);
+        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int r = 2 * mt + hf;
+                const float p0 = fastExp2(sc[r][0] - m0), p1 = fastExp2(sc[r][1] - m1);
+                l0 += p0;
+                l1 += p1;
+                const float w = svr[r] * invE;
+                const float x0 = p0 * w, x1 = p1 * w;
+                const uint32_t hi = packHalf2(x0, x1);
+                const __half2 hh = *reinterpret_cast<const __half2 *>(&hi);
+                const float r0 = x0 - __low2float(hh), r1 = x1 - __high2float(hh);
+                const uint32_t lo = packHalf2(r0, r1);
+                const __half2 ll = *reinterpret_cast<const __half2 *>(&lo);
+                ps0 += __low2float(hh) + __low2float(ll);
+                ps1 += __high2float(hh) + __high2float(ll);
+                bh[mt][hf] = movmatrixTrans(hi);
+                bl[mt][hf] = movmatrixTrans(lo);
             }
-            {
-                const uint32_t a0 = biasedPairLo(Y), a1 = biasedPairHi(Y), a2 = biasedPairLo(Y2),
-                               a3 = biasedPairHi(Y2);
-                mmaF16(o[2 * blk + 1], a0, a1, a2, a3, bh0, bh1);
-                mmaF16(o[2 * blk + 1], a0, a1, a2, a3, bl0, bl1);
+        }
+        // ---- O^T += V^T . P^T (128 dims x 8 heads), V bytes read transposed ----
+        const uint32_t vTile = smemAddr(st + L::kTileBytes + rowInTile * kHD);
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) {
+            const uint32_t sw = ((2 * cp + lco) ^ (lr & 7u)) << 4;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint32_t r0, r1, r2, r3;
+                ldmatrixX4Trans(r0, r1, r2, r3, vTile + mt * 2048 + lmOff + sw);
+                r0 ^= 0x80808080u;
+                r1 ^= 0x80808080u;
+                r2 ^= 0x80808080u;
+                r3 ^= 0x80808080u;
+                {
+                    // rows g / g+8 of this MMA tile are dims 16c+2g / 16c+2g+1, c = 2cp
+                    const uint32_t a0 = subnormalPair<0x4240>(r0), a1 = subnormalPair<0x4341>(r0),
+                                   a2 = subnormalPair<0x4240>(r1), a3 = subnormalPair<0x4341>(r1);
+                    mmaF16(o[2 * cp], a0, a1, a2, a3, bh[mt][0], bh[mt][1]);
+                    mmaF16(o[2 * cp], a0, a1, a2, a3, bl[mt][0], bl[mt][1]);
+                }
+                {
+                    const uint32_t a0 = subnormalPair<0x4240>(r2), a1 = subnormalPair<0x4341>(r2),
+                                   a2 = subnormalPair<0x4240>(r3), a3 = subnormalPair<0x4341>(r3);
+                    mmaF16(o[2 * cp + 1], a0, a1, a2, a3, bh[mt][0], bh[mt][1]);
+                    mmaF16(o[2 * cp + 1], a0, a1, a2, a3, bl[mt][0], bl[mt][1]);
+                }
             }
         }
         __syncwarp();
         if (lane == 0) mbarArrive(&emptyBar[s]);
     }
-    (void) ok;
 
     // ---- fold the consumer warps of each kv head, write the chunk partial ----
 #pragma unroll
     for (int off = 4; off <= 16; off <<= 1) {
         l0 += __shfl_xor_sync(0xffffffffu, l0, off);
         l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+        ps0 += __shfl_xor_sync(0xffffffffu, ps0, off);
+        ps1 += __shfl_xor_sync(0xffffffffu, ps1, off);
     }
     namedBarSync(1, NW * 32);  // every consumer is done reading the ring
     float *scr = reinterpret_cast<float *>(smem);
-    float *wO = scr + warp * (8 * kHD + 16);  // [8 heads][128], then m[8], l[8]
-    const float E = __uint_as_float(Ebits);
+    constexpr int kWarpScr = 8 * kHD + 16;
+    float *wO = scr + warp * kWarpScr;  // [8 heads][128], then m[8], l[8]
+    {
+        // true accumulator = 2^24 * raw - 128 * sum(p*sv), then back from the E-scaled domain
+        const float E = __uint_as_float(Ebits);
+        const float c0 = 128.0f * ps0, c1 = 128.0f * ps1;
 #pragma unroll
-    for (int blk = 0; blk < 4; ++blk) {
-        const int d = 32 * blk + 4 * g;
-        *reinterpret_cast<float4 *>(wO + (2 * t) * kHD + d) =
-                make_float4(o[2 * blk][0] * E, o[2 * blk][2] * E, o[2 * blk + 1][0] * E, o[2 * blk + 1][2] * E);
-        *reinterpret_cast<float4 *>(wO + (2 * t + 1) * kHD + d) =
-                make_float4(o[2 * blk][1] * E, o[2 * blk][3] * E, o[2 * blk + 1][1] * E, o[2 * blk + 1][3] * E);
+        for (int c = 0; c < 8; ++c) {
+            const int d = 16 * c + 2 * g;
+            *reinterpret_cast<float2 *>(wO + (2 * t) * kHD + d) =
+                    make_float2(fmaf(o[c][0], k2p24, -c0) * E, fmaf(o[c][2], k2p24, -c0) * E);
+            *reinterpret_cast<float2 *>(wO + (2 * t + 1) * kHD + d) =
+                    make_float2(fmaf(o[c][1], k2p24, -c1) * E, fmaf(o[c][3], k2p24, -c1) * E);
+        }
     }
     if (g == 0) {
         wO[8 * kHD + 2 * t] = m0;
@@ -362,12 +439,12 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         if (j >= p.group) continue;
         float M = kNegBig;
 #pragma unroll
-        for (int sb = 0; sb < NSUB; ++sb) M = fmaxf(M, scr[(sb * HPC + h) * (8 * kHD + 16) + 8 * kHD + j]);
+        for (int sb = 0; sb < NSUB; ++sb) M = fmaxf(M, scr[(sb * HPC + h) * kWarpScr + 8 * kHD + j]);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         float lsum = 0.0f;
 #pragma unroll
         for (int sb = 0; sb < NSUB; ++sb) {
-            const float *w = scr + (sb * HPC + h) * (8 * kHD + 16);
+            const float *w = scr + (sb * HPC + h) * kWarpScr;
             const float wgt = fastExp2(w[8 * kHD + j] - M);
             lsum += wgt * w[8 * kHD + 8 + j];
             const float4 a = *reinterpret_cast<const float4 *>(w + j * kHD + 4 * d4);
@@ -399,11 +476,11 @@ struct DecodePlan {
 
 // One wave of CTAs over the SMs when the batch is small, a few waves when many
 // ragged sequences need the hardware scheduler to even things out.
-static DecodePlan planDecode(uint32_t batch, uint32_t nKV, uint32_t maxLen, uint32_t slots, int nw) {
+static DecodePlan planDecode(uint32_t batch, uint32_t nKV, uint32_t maxLen, uint32_t slots, int nw, uint32_t mt) {
     DecodePlan pl;
     pl.hpc = (nKV % 4u == 0) ? 4u : (nKV % 2u == 0 ? 2u : 1u);
     pl.headGroups = nKV / pl.hpc;
-    pl.tileTokens = static_cast<uint32_t>(nw) * 16u / pl.hpc;
+    pl.tileTokens = static_cast<uint32_t>(nw) * 16u * mt / pl.hpc;
     const uint32_t tilesMax = (maxLen + pl.tileTokens - 1) / pl.tileTokens;
     const uint32_t sms = static_cast<uint32_t>(numSMs());
     const uint32_t waves = batch > 1 ? 2u : 1u;
@@ -419,12 +496,12 @@ static DecodePlan planDecode(uint32_t batch, uint32_t nKV, uint32_t maxLen, uint
     return pl;
 }
 
-template <int HPC>
+template <int HPC, int MT>
 static int launchDecodeI8(const CUtensorMap &tmK, const CUtensorMap &tmV, const DecodeI8Params &prm,
-                          const DecodePlan &pl, uint32_t batch, cudaStream_t st) {
-    constexpr int NW = 8, NSTAGE = 4, MINB = 1;
-    using L = DecodeI8Smem<HPC, NW, NSTAGE>;
-    auto kern = decodeI8Kernel<HPC, NW, NSTAGE, MINB>;
+                          const DecodePlan &pl, uint32_t batch, bool pdl, cudaStream_t st) {
+    constexpr int NW = 8, NSTAGE = MT == 2 ? 3 : 6;
+    using L = DecodeI8Smem<HPC, NW, NSTAGE, MT>;
+    auto kern = decodeI8Kernel<HPC, NW, NSTAGE, MT>;
     static bool attrDone[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -432,9 +509,17 @@ static int launchDecodeI8(const CUtensorMap &tmK, const CUtensorMap &tmV, const 
         TC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
         attrDone[dev] = true;
     }
-    dim3 grid(pl.chunksPerSeq, pl.headGroups, batch);
-    kern<<<grid, (NW + 1) * 32, L::kTotal, st>>>(tmK, tmV, prm);
-    TC_CUDA_OK(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.chunksPerSeq, pl.headGroups, batch);
+    cfg.blockDim = dim3((NW + 1) * 32);
+    cfg.dynamicSmemBytes = L::kTotal;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    TC_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tmK, tmV, prm));
     return TC_OK;
 }
 
@@ -453,7 +538,12 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
                  reinterpret_cast<uintptr_t>(d->q) | reinterpret_cast<uintptr_t>(d->out)) & 15u) == 0,
                TC_EINVAL, "decode_i8: q/out/k8/v8 need 16-byte alignment");
     TC_REQUIRE(d->numChunks >= 1, TC_EWORKSPACE, "decode_i8: no chunk slots");
-    const DecodePlan pl = planDecode(d->batch, d->nKV, d->maxLen, d->numChunks, 8);
+    // work quantum: 32 tokens per warp when every warp of the machine gets at least ~12
+    // of them, 16 otherwise (see DecodeI8Smem)
+    const uint64_t warpTiles32 = static_cast<uint64_t>(d->batch) * d->nKV * ((d->maxLen + 31) / 32);
+    const uint32_t mt = warpTiles32 >= 2ull * 8ull * static_cast<uint64_t>(numSMs()) ? 2u : 1u;
+    const DecodePlan pl = planDecode(d->batch, d->nKV, d->maxLen, d->numChunks, 8, mt);
+    const bool pdl = (d->flags & TC_DECODE_PDL) != 0;
     const bool direct = pl.chunksPerSeq == 1 && !d->partialsOnly;
     if (!direct)
         TC_REQUIRE(d->pAcc && d->pM && d->pL, TC_EWORKSPACE, "decode_i8: partial buffers are required");
@@ -499,20 +589,27 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     prm.group = group;
     prm.chunkTokens = pl.chunkTokens;
     prm.numChunks = d->numChunks;
+    prm.prefetchRows = pdl ? d->prefetchRows : 0;
     prm.invSqrt = d->invSqrt;
     prm.directOut = direct ? 1 : 0;
     prm.err = devErrorWord();
     TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "decode_i8: no device error word");
 
-    if (pl.hpc == 4) rc = launchDecodeI8<4>(tmK, tmV, prm, pl, d->batch, st);
-    else if (pl.hpc == 2) rc = launchDecodeI8<2>(tmK, tmV, prm, pl, d->batch, st);
-    else rc = launchDecodeI8<1>(tmK, tmV, prm, pl, d->batch, st);
+    if (mt == 2) {
+        if (pl.hpc == 4) rc = launchDecodeI8<4, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        else if (pl.hpc == 2) rc = launchDecodeI8<2, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        else rc = launchDecodeI8<1, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
+    } else {
+        if (pl.hpc == 4) rc = launchDecodeI8<4, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        else if (pl.hpc == 2) rc = launchDecodeI8<2, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        else rc = launchDecodeI8<1, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+    }
     if (rc != TC_OK) return rc;
     if (direct || d->partialsOnly) return TC_OK;
     // merge: the active chunk count of a sequence follows from its length (read on
     // the device when the length lives there); slots past it were never written.
     return launchMerge(d->pAcc, d->pM, d->pL, d->out, d->batch, d->nHeads, d->numChunks, pl.chunksPerSeq, kHD,
-                       d->lens, lenAdd, pl.chunkTokens, nullptr, st);
+                       d->lens, lenAdd, pl.chunkTokens, nullptr, pdl, st);
 }
 
 }  // namespace tc
@@ -521,8 +618,7 @@ extern "C" {
 
 int tc_attn_decode_i8_batch(const tc_decode_i8_batch *d, tc_stream stream) {
     TC_REQUIRE(d != nullptr, TC_EINVAL, "tc_attn_decode_i8_batch: null descriptor");
-    TC_REQUIRE(d->lens != nullptr, TC_EINVAL, "tc_attn_decode_i8_batch: lens (device) is required");
-    return tc::decodeI8Common(d, 0, 0, static_cast<cudaStream_t>(stream));
+    return tc::decodeI8Common(d, d->maxLen, 0, static_cast<cudaStream_t>(stream));
 }
 
 int tc_attn_decode_i8(const float *q, const int8_t *k8, const int8_t *v8, const float *ks, const float *vs,

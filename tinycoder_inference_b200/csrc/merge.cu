@@ -16,7 +16,7 @@
 
 namespace tc {
 
-constexpr int kMergeMaxChunks = 4096;
+constexpr int kMergeMaxChunks = 1024;
 
 // Phase 1: all 256 threads read (m, l) of the active chunks at once, the block
 // takes the max, and the per-chunk weights w_c = exp2((m_c - M) * log2e) (0 for
@@ -34,6 +34,10 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
     const uint32_t head = blockIdx.x, s = blockIdx.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint64_t base = (static_cast<uint64_t>(s) * nHeads + head) * numChunks;
+    // under programmatic dependent launch: let the next grid start its prologue, then
+    // wait until the grid that wrote the partials has finished (a no-op otherwise)
+    gridDepLaunch();
+    gridDepWait();
     // numChunks is the slot stride; only the first `active` slots were written
     uint32_t active = activeHost < numChunks ? activeHost : numChunks;
     if (devLens != nullptr) {
@@ -41,16 +45,39 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
         const uint32_t need = (len + chunkTokens - 1) / chunkTokens;
         active = need < numChunks ? need : numChunks;
     }
-    __shared__ float sw[kMergeMaxChunks];
+    __shared__ float sw[kMergeMaxChunks], sl[kMergeMaxChunks];
     __shared__ float sred[NW];
     __shared__ float4 sacc[NW][NV4][32];
     __shared__ float sout[NV4 * 128];
 
+    // Everything a thread needs from global memory is requested before anything is
+    // consumed: the (m, l) pair of the chunks it owns in phase 1 and the first batch
+    // of accumulator rows of phase 2 (their addresses do not depend on the weights),
+    // so the merge costs one round trip to L2 plus arithmetic, not one per chunk.
+    const uint32_t nvec = hd >> 2;
+    constexpr int kBatch = 16;
+    float4 a[kBatch][NV4];
+    auto loadBatch = [&](uint32_t c0) {
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const uint32_t c = c0 + u * NW;
+            const uint32_t cc = c < active ? c : (active ? active - 1 : 0);  // always a valid address
+            const float4 *pac = reinterpret_cast<const float4 *>(pAcc + (base + cc) * hd);
+#pragma unroll
+            for (int j = 0; j < NV4; ++j) {
+                const uint32_t i = lane + 32u * j;
+                a[u][j] = pac[i < nvec ? i : 0];
+            }
+        }
+    };
+    if (active) loadBatch(warp);
     // ---- phase 1: max, weights, normaliser ----
     float M = kNegBig;
     for (uint32_t c = threadIdx.x; c < active; c += 256) {
         const float m = pM[base + c];
+        const float lc = pL[base + c];
         sw[c] = m;
+        sl[c] = lc;
         M = fmaxf(M, m);
     }
 #pragma unroll
@@ -63,7 +90,7 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
     __syncthreads();
     float lsum = 0.0f;
     for (uint32_t c = threadIdx.x; c < active; c += 256) {
-        const float lc = pL[base + c];
+        const float lc = sl[c];
         const float w = lc > 0.0f ? exp2f((sw[c] - M) * kLog2e) : 0.0f;
         sw[c] = w;
         lsum = fmaf(w, lc > 0.0f ? lc : 0.0f, lsum);
@@ -71,29 +98,31 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
 #pragma unroll
     for (int o = 16; o; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
     if (lane == 0) sred[warp] = lsum;
-    __syncthreads();
+    __syncthreads();  // also publishes the weights in sw[]
     lsum = 0.0f;
 #pragma unroll
     for (int w2 = 0; w2 < NW; ++w2) lsum += sred[w2];
 
     // ---- phase 2: weighted sum of the accumulators ----
+    // A chunk with weight 0 (empty, possibly never written) is dropped by a select
+    // after the load, never multiplied in.
     float4 acc[NV4];
 #pragma unroll
     for (int j = 0; j < NV4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-    const uint32_t nvec = hd >> 2;
-#pragma unroll 4
-    for (uint32_t c = warp; c < active; c += NW) {
-        const float w = sw[c];
-        const float4 *pac = reinterpret_cast<const float4 *>(pAcc + (base + c) * hd);
+    for (uint32_t c0 = warp; c0 < active; c0 += NW * kBatch) {
+        if (c0 != warp) loadBatch(c0);
 #pragma unroll
-        for (int j = 0; j < NV4; ++j) {
-            const uint32_t i = lane + 32u * j;
-            if (i < nvec && w != 0.0f) {  // an empty chunk's accumulator may hold anything
-                const float4 a = pac[i];
-                acc[j].x = fmaf(w, a.x, acc[j].x);
-                acc[j].y = fmaf(w, a.y, acc[j].y);
-                acc[j].z = fmaf(w, a.z, acc[j].z);
-                acc[j].w = fmaf(w, a.w, acc[j].w);
+        for (int u = 0; u < kBatch; ++u) {
+            const uint32_t c = c0 + u * NW;
+            const float w = c < active ? sw[c < active ? c : 0] : 0.0f;
+#pragma unroll
+            for (int j = 0; j < NV4; ++j) {
+                const bool use = w != 0.0f && (lane + 32u * j) < nvec;
+                const float4 v = use ? a[u][j] : make_float4(0.f, 0.f, 0.f, 0.f);
+                acc[j].x = fmaf(w, v.x, acc[j].x);
+                acc[j].y = fmaf(w, v.y, acc[j].y);
+                acc[j].z = fmaf(w, v.z, acc[j].z);
+                acc[j].w = fmaf(w, v.w, acc[j].w);
             }
         }
     }
@@ -148,15 +177,22 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
 
 int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out, uint32_t seqLen,
                 uint32_t nHeads, uint32_t numChunks, uint32_t activeHost, uint32_t hd, const uint32_t *devLens,
-                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, cudaStream_t st) {
-    dim3 grid(nHeads, seqLen);
+                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nHeads, seqLen);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
     if (hd <= 128)
-        mergePartialsKernel<1><<<grid, 256, 0, st>>>(pAcc, pM, pL, out, nHeads, numChunks, activeHost, hd,
-                                                     devLens, lenAdd, chunkTokens, q81);
+        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, mergePartialsKernel<1>, pAcc, pM, pL, out, nHeads, numChunks,
+                                      activeHost, hd, devLens, lenAdd, chunkTokens, q81));
     else
-        mergePartialsKernel<2><<<grid, 256, 0, st>>>(pAcc, pM, pL, out, nHeads, numChunks, activeHost, hd,
-                                                     devLens, lenAdd, chunkTokens, q81);
-    TC_CUDA_OK(cudaGetLastError());
+        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, mergePartialsKernel<2>, pAcc, pM, pL, out, nHeads, numChunks,
+                                      activeHost, hd, devLens, lenAdd, chunkTokens, q81));
     return TC_OK;
 }
 
@@ -176,7 +212,7 @@ int tc_attn_merge_partials(const float *pAcc, const float *pM, const float *pL, 
     TC_REQUIRE(seqLen <= 65535, TC_EUNSUPPORTED, "tc_attn_merge_partials: seqLen %u > 65535", seqLen);
     if (seqLen == 0) return TC_OK;
     return tc::launchMerge(pAcc, pM, pL, out, seqLen, nHeads, numChunks, numChunks, hd, nullptr, 0, 1, q81Out,
-                           static_cast<cudaStream_t>(stream));
+                           false, static_cast<cudaStream_t>(stream));
 }
 
 int tc_attn_workspace_bytes(uint32_t batch, uint32_t nHeads, uint32_t hd, uint32_t numChunks, size_t *accBytes,

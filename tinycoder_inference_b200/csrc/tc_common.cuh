@@ -147,6 +147,12 @@ __device__ __forceinline__ void ldmatrixX4(uint32_t &r0, uint32_t &r1, uint32_t 
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                  : "r"(addr));
 }
+__device__ __forceinline__ void ldmatrixX4Trans(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3,
+                                                uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
 __device__ __forceinline__ uint32_t movmatrixTrans(uint32_t a) {
     uint32_t d;
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
@@ -190,6 +196,20 @@ __device__ __forceinline__ uint32_t biasedPairHi(uint32_t w) {
     __half2 r = __hsub2(*reinterpret_cast<__half2 *>(&h), __half2half2(__ushort_as_half(0x6480)));
     return *reinterpret_cast<uint32_t *>(&r);
 }
+
+// Cheaper exact form used by the decode kernel: a byte u placed in the low mantissa
+// bits of an fp16 with zero exponent IS the subnormal u * 2^-24, exactly.  With
+// u = x + 128 (w already xor-ed with 0x80) the operand carries a +128 offset that
+// the caller removes after the MMA with a per-column sum; one prmt per pair.
+template <uint32_t SEL>
+__device__ __forceinline__ uint32_t subnormalPair(uint32_t w) {
+    return __byte_perm(w, 0u, SEL);
+}
+
+// Programmatic dependent launch: wait for the grids this one depends on (and for
+// their memory to be visible) / let the dependent grid start its prologue.
+__device__ __forceinline__ void gridDepWait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void gridDepLaunch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t packHalf2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);

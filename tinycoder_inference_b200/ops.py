@@ -91,8 +91,10 @@ def decode_i8(q, k8, v8, ks, vs, out, ws, nHeads, nKV, hd, cachePos, numChunks, 
 
 
 def decode_i8_batch(q, k8, v8, ks, vs, out, ws, lens, batch, nHeads, nKV, hd, maxLen, numChunks,
-                    rows_per_seq=0, row_base=None, invSqrt=None, partials_only=False):
-    """`batch` sequences in one pool; returns the chunk slots used per head."""
+                    rows_per_seq=0, row_base=None, invSqrt=None, partials_only=False, pdl=False,
+                    prefetch_rows=0):
+    """`batch` sequences in one pool; returns the chunk slots used per head.
+    lens=None: every sequence is maxLen rows long (host length)."""
     if invSqrt is None:
         invSqrt = 1.0 / math.sqrt(hd)
     pAcc, pM, pL = ws
@@ -101,7 +103,9 @@ def decode_i8_batch(q, k8, v8, ks, vs, out, ws, lens, batch, nHeads, nKV, hd, ma
     d.q, d.out = q.data_ptr(), out.data_ptr()
     d.k8, d.v8, d.ks, d.vs = k8.data_ptr(), v8.data_ptr(), ks.data_ptr(), vs.data_ptr()
     d.pAcc, d.pM, d.pL = pAcc.data_ptr(), pM.data_ptr(), pL.data_ptr()
-    d.lens = lens.data_ptr()
+    d.lens = lens.data_ptr() if lens is not None else None
+    d.flags = capi.TC_DECODE_PDL if pdl else 0
+    d.prefetchRows = prefetch_rows
     d.rowBase = row_base.data_ptr() if row_base is not None else None
     d.rowsPerSeq = rows_per_seq
     d.totalRows = k8.numel() // (nKV * hd)
