@@ -27,12 +27,9 @@
 //     the caller's partial buffers in the reference's layout and are merged by
 //     the merge kernel (merge.cu).
 #include "tc_common.cuh"
+#include "decode_shared.cuh"
 
 namespace tc {
-
-int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out, uint32_t seqLen,
-                uint32_t nHeads, uint32_t numChunks, uint32_t activeHost, uint32_t hd, const uint32_t *devLens,
-                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st);
 
 struct DecodeI8Params {
     const float *q;
@@ -46,6 +43,11 @@ struct DecodeI8Params {
     uint32_t nHeads, nKV, group;
     uint32_t chunkTokens, numChunks;
     uint32_t prefetchRows;  // rows [0, prefetchRows) of a sequence may be read before the dependency wait
+    // rows mode (causal prefill over the store): the 8 MMA columns of a CTA are 8
+    // consecutive query rows of ONE q head instead of the q heads of one kv head;
+    // row s attends pool rows [0, cachePos + s].  grid = (1, nHeads, ceil(qRows / 8)).
+    uint32_t rowsMode, qRows, cachePos;
+    const uint32_t *devPos;
     float invSqrt;
     int directOut;
     unsigned int *err;
@@ -68,20 +70,6 @@ struct DecodeI8Smem {
     static_assert(kStageBytes % 1024 == 0, "stage must keep 1024-byte alignment for the 128B swizzle");
     static_assert(T <= 256, "TMA box rows");
 };
-
-__device__ __forceinline__ bool mbarWaitClock(uint64_t *bar, uint32_t parity, unsigned int *err,
-                                              uint32_t errBit) {
-    // ~2^31 cycles (about a second) before giving up.
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 256; ++i)
-            if (mbarTryWait(bar, parity)) return true;
-        if (clock64() - t0 > (1ll << 31)) break;
-    }
-    atomicOr(err, errBit);
-    return false;
-}
 
 // How far the running reference point of the softmax may lag behind the true
 // maximum (log2 units) before the accumulators are rescaled.  p stays <= 2^8.
@@ -121,20 +109,28 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     // The length may live in device memory written by an earlier kernel; only a
     // host-known length lets the producer start before the dependency wait.
     uint32_t len = p.lenHost;
-    const bool earlyOk = p.devLens == nullptr && p.devRowBase == nullptr && p.prefetchRows != 0;
+    const bool earlyOk = p.devLens == nullptr && p.devRowBase == nullptr && p.prefetchRows != 0 && !p.rowsMode;
     if (!earlyOk) {
         gridDepWait();
         if (p.devLens) len = p.devLens[b] + p.lenAdd;
+    }
+    uint32_t rowsPos = p.cachePos;  // rows mode: first query row sits at pool row rowsPos
+    if (p.rowsMode) {
+        if (p.devPos) rowsPos = p.devPos[0];
+        const uint32_t sEnd = min(p.qRows, b * 8u + 8u);  // b = row block
+        len = rowsPos + sEnd;                             // the block's last row sees [0, rowsPos + sEnd)
     }
     const uint32_t t0 = chunk * p.chunkTokens;
     if (t0 >= len) return;  // inactive chunk: the merge derives the active count from len
     const uint32_t t1 = min(len, t0 + p.chunkTokens);
     const uint32_t nTiles = (t1 - t0 + T - 1) / T;
-    const uint64_t rowBase = p.devRowBase ? p.devRowBase[b] : static_cast<uint64_t>(b) * p.rowsPerSeq;
+    const uint64_t rowBase = p.rowsMode ? 0ull
+                                        : (p.devRowBase ? p.devRowBase[b] : static_cast<uint64_t>(b) * p.rowsPerSeq);
+    // kv heads of this CTA: heads mode streams HPC of them, rows mode the one behind q head `hg`
+    const uint32_t kvHead0 = p.rowsMode ? hg / p.group : hg * HPC;
 
     if (warp == NW) {
         // ------------------------------ producer ------------------------------
-        const uint32_t kvHead0 = hg * HPC;
         bool waited = !earlyOk;
         for (uint32_t it = 0; it < nTiles; ++it) {
             const uint32_t s = it % NSTAGE;
@@ -177,7 +173,15 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (earlyOk) gridDepWait();  // q comes from a kernel that may still be running
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t hL = warp % HPC, sub = warp / HPC;
-    const uint32_t kvHead = hg * HPC + hL;
+    const uint32_t kvHead = kvHead0 + hL;
+    // What MMA column j (0..7) of this warp stands for.
+    auto colValid = [&](uint32_t j) { return p.rowsMode ? (b * 8u + j < p.qRows) : (j < p.group); };
+    auto colIndex = [&](uint32_t j) -> size_t {  // index of the column's q / out vector, in units of kHD
+        return p.rowsMode ? (static_cast<size_t>(b) * 8u + j) * p.nHeads + hg
+                          : static_cast<size_t>(b) * p.nHeads + kvHead * p.group + j;
+    };
+    // exclusive row bound of a column: everything in heads mode, causal in rows mode
+    auto colLen = [&](uint32_t j) { return p.rowsMode ? min(t1, rowsPos + b * 8u + j + 1u) : t1; };
 
     // q fragments for head column n = g of this kv head's group: power-of-two
     // normalised, split into fp16 hi + lo, laid out as the B operand whose k
@@ -187,8 +191,8 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     {
         float4 qv[8];
         float amax = 0.0f;
-        const bool valid = g < p.group;
-        const float *qp = p.q + (static_cast<size_t>(b) * p.nHeads + kvHead * p.group + (valid ? g : 0)) * kHD;
+        const bool valid = colValid(g);
+        const float *qp = p.q + colIndex(valid ? g : 0) * kHD;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
             qv[c] = valid ? __ldg(reinterpret_cast<const float4 *>(qp + 16 * c + 4 * t))
@@ -227,6 +231,7 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const float cs1 = __shfl_sync(0xffffffffu, headScale, (2 * t + 1) * 4);
     const float off0 = __shfl_sync(0xffffffffu, headOff, (2 * t) * 4);
     const float off1 = __shfl_sync(0xffffffffu, headOff, (2 * t + 1) * 4);
+    const uint32_t len0 = colLen(2 * t), len1 = colLen(2 * t + 1);
 
     float m0 = kNegBig, m1 = kNegBig, l0 = 0.0f, l1 = 0.0f;
     float ps0 = 0.0f, ps1 = 0.0f;  // sum of p*sv as fed to the PV MMA (V bytes enter as x + 128)
@@ -248,13 +253,14 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const float *sK = reinterpret_cast<const float *>(st + 2 * L::kTileBytes) + rowInTile;
         const float *sV = sK + L::kRows;
         const uint32_t tokBase = t0 + it * T + sub * kTokPerWarp + g;
-        bool vld[NR];
+        bool vl0[NR], vl1[NR];
         float skr[NR], svr[NR];
 #pragma unroll
         for (int r = 0; r < NR; ++r) {  // rows g, g+8, ... of this warp's tokens
-            vld[r] = tokBase + 8 * r < t1;
+            vl0[r] = tokBase + 8 * r < len0;
+            vl1[r] = tokBase + 8 * r < len1;
             skr[r] = sK[g + 8 * r];
-            svr[r] = vld[r] ? sV[g + 8 * r] : 0.0f;
+            svr[r] = tokBase + 8 * r < t1 ? sV[g + 8 * r] : 0.0f;
         }
 
         // ---- S^T = K . Q^T, two 16-token tiles x 8 heads ----
@@ -299,8 +305,8 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 const int r = 2 * mt + hf;
                 const float d0 = fmaf(sh[mt][2 * hf] + sl[mt][2 * hf], k2p24, -off0);
                 const float d1 = fmaf(sh[mt][2 * hf + 1] + sl[mt][2 * hf + 1], k2p24, -off1);
-                sc[r][0] = vld[r] ? d0 * (skr[r] * cs0) : -INFINITY;
-                sc[r][1] = vld[r] ? d1 * (skr[r] * cs1) : -INFINITY;
+                sc[r][0] = vl0[r] ? d0 * (skr[r] * cs0) : -INFINITY;
+                sc[r][1] = vl1[r] ? d1 * (skr[r] * cs1) : -INFINITY;
             }
         }
         float mx0 = fmaxf(sc[0][0], sc[1][0]), mx1 = fmaxf(sc[0][1], sc[1][1]);
@@ -436,7 +442,7 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     // NW*32 threads, HPC*8*32 float4 outputs
     for (uint32_t idx = threadIdx.x; idx < HPC * 8 * 32; idx += NW * 32) {
         const uint32_t d4 = idx & 31u, j = (idx >> 5) & 7u, h = idx >> 8;
-        if (j >= p.group) continue;
+        if (!colValid(j)) continue;
         float M = kNegBig;
 #pragma unroll
         for (int sb = 0; sb < NSUB; ++sb) M = fmaxf(M, scr[(sb * HPC + h) * kWarpScr + 8 * kHD + j]);
@@ -453,13 +459,15 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             acc.z = fmaf(wgt, a.z, acc.z);
             acc.w = fmaf(wgt, a.w, acc.w);
         }
-        const uint32_t qHead = (hg * HPC + h) * p.group + j;
+        // column -> output vector (same rule as colIndex, for kv head kvHead0 + h)
+        const size_t oidx = p.rowsMode ? (static_cast<size_t>(b) * 8u + j) * p.nHeads + hg
+                                       : static_cast<size_t>(b) * p.nHeads + (kvHead0 + h) * p.group + j;
         if (p.directOut) {
             const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
-            *reinterpret_cast<float4 *>(p.out + (static_cast<size_t>(b) * p.nHeads + qHead) * kHD + 4 * d4) =
+            *reinterpret_cast<float4 *>(p.out + oidx * kHD + 4 * d4) =
                     make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         } else {
-            const size_t pidx = (static_cast<size_t>(b) * p.nHeads + qHead) * p.numChunks + chunk;
+            const size_t pidx = oidx * p.numChunks + chunk;
             *reinterpret_cast<float4 *>(p.pAcc + pidx * kHD + 4 * d4) = acc;
             if (d4 == 0) {
                 // back to natural-log units: the merge contract is w = exp2((m - M) * log2e)
@@ -468,32 +476,6 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             }
         }
     }
-}
-
-struct DecodePlan {
-    uint32_t hpc, headGroups, chunkTokens, chunksPerSeq, tileTokens;
-};
-
-// One wave of CTAs over the SMs when the batch is small, a few waves when many
-// ragged sequences need the hardware scheduler to even things out.
-static DecodePlan planDecode(uint32_t batch, uint32_t nKV, uint32_t maxLen, uint32_t slots, int nw, uint32_t mt) {
-    DecodePlan pl;
-    pl.hpc = (nKV % 4u == 0) ? 4u : (nKV % 2u == 0 ? 2u : 1u);
-    pl.headGroups = nKV / pl.hpc;
-    pl.tileTokens = static_cast<uint32_t>(nw) * 16u * mt / pl.hpc;
-    const uint32_t tilesMax = (maxLen + pl.tileTokens - 1) / pl.tileTokens;
-    const uint32_t sms = static_cast<uint32_t>(numSMs());
-    const uint32_t waves = batch > 1 ? 2u : 1u;
-    uint32_t want = (sms * waves) / (batch * pl.headGroups);
-    want = want < 1u ? 1u : want;
-    want = want > slots ? slots : want;
-    want = want > tilesMax ? tilesMax : want;
-    want = want < 1u ? 1u : want;
-    const uint32_t tilesPerChunk = (tilesMax + want - 1) / want;
-    pl.chunkTokens = tilesPerChunk * pl.tileTokens;
-    pl.chunksPerSeq = (tilesMax + tilesPerChunk - 1) / tilesPerChunk;
-    if (pl.chunksPerSeq == 0) pl.chunksPerSeq = 1;
-    return pl;
 }
 
 template <int HPC, int MT>
@@ -542,7 +524,7 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     // of them, 16 otherwise (see DecodeI8Smem)
     const uint64_t warpTiles32 = static_cast<uint64_t>(d->batch) * d->nKV * ((d->maxLen + 31) / 32);
     const uint32_t mt = warpTiles32 >= 2ull * 8ull * static_cast<uint64_t>(numSMs()) ? 2u : 1u;
-    const DecodePlan pl = planDecode(d->batch, d->nKV, d->maxLen, d->numChunks, 8, mt);
+    const DecodePlan pl = planDecode(d->batch, d->nKV, d->maxLen, d->numChunks, 8u * 16u * mt);
     const bool pdl = (d->flags & TC_DECODE_PDL) != 0;
     const bool direct = pl.chunksPerSeq == 1 && !d->partialsOnly;
     if (!direct)
@@ -590,6 +572,10 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     prm.chunkTokens = pl.chunkTokens;
     prm.numChunks = d->numChunks;
     prm.prefetchRows = pdl ? d->prefetchRows : 0;
+    prm.rowsMode = 0;
+    prm.qRows = 0;
+    prm.cachePos = 0;
+    prm.devPos = nullptr;
     prm.invSqrt = d->invSqrt;
     prm.directOut = direct ? 1 : 0;
     prm.err = devErrorWord();
@@ -612,9 +598,91 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
                        d->lens, lenAdd, pl.chunkTokens, nullptr, pdl, st);
 }
 
+// Causal prefill over the int8 store: the decode kernel with query rows as MMA columns.
+static int prefillI8(const float *q, const int8_t *k8, const int8_t *v8, const float *ks, const float *vs,
+                     float *out, uint32_t seqLen, uint32_t nHeads, uint32_t nKV, uint32_t hd, uint32_t cachePos,
+                     const uint32_t *devPos, uint64_t totalRows, float invSqrt, cudaStream_t st) {
+    TC_REQUIRE(q && k8 && v8 && ks && vs && out, TC_EINVAL, "prefill_i8: null pointer");
+    TC_REQUIRE(hd == kHD, TC_EUNSUPPORTED, "prefill_i8: head_dim %u (built for 128)", hd);
+    TC_REQUIRE(nKV > 0 && nHeads % nKV == 0, TC_EINVAL, "prefill_i8: nHeads %u not a multiple of nKV %u", nHeads,
+               nKV);
+    TC_REQUIRE(totalRows >= 1 && totalRows < (1ull << 31), TC_EUNSUPPORTED, "prefill_i8: pool of %llu rows",
+               (unsigned long long) totalRows);
+    TC_REQUIRE(((reinterpret_cast<uintptr_t>(k8) | reinterpret_cast<uintptr_t>(v8) | reinterpret_cast<uintptr_t>(q) |
+                 reinterpret_cast<uintptr_t>(out)) & 15u) == 0,
+               TC_EINVAL, "prefill_i8: q/out/k8/v8 need 16-byte alignment");
+    if (seqLen == 0) return TC_OK;
+    if (devPos == nullptr && static_cast<uint64_t>(cachePos) + seqLen > totalRows) {
+        setError("prefill_i8: rows [%u, %llu) pass the pool of %llu rows", cachePos,
+                 (unsigned long long) cachePos + seqLen, (unsigned long long) totalRows);
+        return TC_ECONTEXT_FULL;
+    }
+    const uint32_t rowBlocks = (seqLen + 7) / 8;
+    TC_REQUIRE(rowBlocks <= 65535 && nHeads <= 65535, TC_EUNSUPPORTED, "prefill_i8: %u rows x %u heads", seqLen,
+               nHeads);
+    constexpr int NW = 8, MT = 2, NSTAGE = 3;
+    using L = DecodeI8Smem<1, NW, NSTAGE, MT>;
+    TensorMapKey key;
+    memset(&key, 0, sizeof(key));
+    key.rank = 3;
+    key.elemBytes = 1;
+    key.swizzle = 3;
+    key.dims[0] = kHD;
+    key.dims[1] = nKV;
+    key.dims[2] = totalRows;
+    key.strides[0] = kHD;
+    key.strides[1] = static_cast<uint64_t>(nKV) * kHD;
+    key.box[0] = kHD;
+    key.box[1] = 1;
+    key.box[2] = L::T;
+    CUtensorMap tmK, tmV;
+    key.base = k8;
+    int rc = getTensorMap(key, &tmK);
+    if (rc != TC_OK) return rc;
+    key.base = v8;
+    rc = getTensorMap(key, &tmV);
+    if (rc != TC_OK) return rc;
+    DecodeI8Params prm;
+    memset(&prm, 0, sizeof(prm));
+    prm.q = q;
+    prm.out = out;
+    prm.ks = ks;
+    prm.vs = vs;
+    prm.totalRows = totalRows;
+    prm.nHeads = nHeads;
+    prm.nKV = nKV;
+    prm.group = nHeads / nKV;
+    prm.chunkTokens = 0xffffff00u;  // one chunk: a block streams its whole causal prefix
+    prm.numChunks = 1;
+    prm.rowsMode = 1;
+    prm.qRows = seqLen;
+    prm.cachePos = cachePos;
+    prm.devPos = devPos;
+    prm.invSqrt = invSqrt;
+    prm.directOut = 1;
+    prm.err = devErrorWord();
+    TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "prefill_i8: no device error word");
+    DecodePlan pl;
+    pl.hpc = 1;
+    pl.headGroups = nHeads;
+    pl.chunksPerSeq = 1;
+    pl.chunkTokens = prm.chunkTokens;
+    pl.tileTokens = L::T;
+    // heaviest row blocks first would need a reversed grid; the hardware scheduler
+    // hands out blocks in z-major order, so late (long) blocks start last -- acceptable here
+    return launchDecodeI8<1, MT>(tmK, tmV, prm, pl, rowBlocks, false, st);
+}
+
 }  // namespace tc
 
 extern "C" {
+
+int tc_attn_prefill_i8(const float *q, const int8_t *k8, const int8_t *v8, const float *ks, const float *vs,
+                       float *out, uint32_t seqLen, uint32_t nHeads, uint32_t nKV, uint32_t hd, uint32_t cachePos,
+                       const uint32_t *devPos, uint64_t totalRows, float invSqrt, tc_stream stream) {
+    return tc::prefillI8(q, k8, v8, ks, vs, out, seqLen, nHeads, nKV, hd, cachePos, devPos, totalRows, invSqrt,
+                         static_cast<cudaStream_t>(stream));
+}
 
 int tc_attn_decode_i8_batch(const tc_decode_i8_batch *d, tc_stream stream) {
     TC_REQUIRE(d != nullptr, TC_EINVAL, "tc_attn_decode_i8_batch: null descriptor");

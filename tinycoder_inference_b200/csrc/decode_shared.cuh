@@ -1,0 +1,59 @@
+// decode_shared.cuh -- pieces shared by the split-KV decode kernels (int8 store and
+// f32/fp16 cache): the bounded mbarrier wait, the chunk plan, the merge launcher.
+#pragma once
+
+#include "tc_common.cuh"
+
+namespace tc {
+
+int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out, uint32_t seqLen,
+                uint32_t nHeads, uint32_t numChunks, uint32_t activeHost, uint32_t hd, const uint32_t *devLens,
+                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st);
+
+#ifdef __CUDACC__
+__device__ __forceinline__ bool mbarWaitClock(uint64_t *bar, uint32_t parity, unsigned int *err,
+                                              uint32_t errBit) {
+    // ~2^31 cycles (about a second) before giving up.
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbarTryWait(bar, parity)) return true;
+        if (clock64() - t0 > (1ll << 31)) break;
+    }
+    atomicOr(err, errBit);
+    return false;
+}
+
+#endif
+
+// rowsPerStage = (token, kv-head) rows one pipeline stage holds; a CTA streams
+// hpc kv heads, so a stage covers rowsPerStage / hpc tokens.
+struct DecodePlan {
+    uint32_t hpc, headGroups, chunkTokens, chunksPerSeq, tileTokens;
+};
+
+// One wave of CTAs over the SMs when the batch is small, a few waves when many
+// ragged sequences need the hardware scheduler to even things out.
+inline DecodePlan planDecode(uint32_t batch, uint32_t nKV, uint32_t maxLen, uint32_t slots, uint32_t rowsPerStage) {
+    DecodePlan pl;
+    pl.hpc = (nKV % 4u == 0) ? 4u : (nKV % 2u == 0 ? 2u : 1u);
+    pl.headGroups = nKV / pl.hpc;
+    pl.tileTokens = rowsPerStage / pl.hpc;
+    const uint32_t tilesMax = (maxLen + pl.tileTokens - 1) / pl.tileTokens;
+    const uint32_t sms = static_cast<uint32_t>(numSMs());
+    const uint32_t waves = batch > 1 ? 2u : 1u;
+    uint32_t want = (sms * waves) / (batch * pl.headGroups);
+    want = want < 1u ? 1u : want;
+    want = want > slots ? slots : want;
+    want = want > tilesMax ? tilesMax : want;
+    want = want < 1u ? 1u : want;
+    const uint32_t tilesPerChunk = (tilesMax + want - 1) / want;
+    pl.chunkTokens = tilesPerChunk * pl.tileTokens;
+    pl.chunksPerSeq = (tilesMax + tilesPerChunk - 1) / tilesPerChunk;
+    if (pl.chunksPerSeq == 0) pl.chunksPerSeq = 1;
+    return pl;
+}
+
+
+}  // namespace tc
