@@ -199,13 +199,151 @@ def workload_config(name, gpus):
 # GPU arm
 # ---------------------------------------------------------------------------------
 
+def run_prefill(args):
+    """Qwen2.5-7B-shaped causal prefill: 4096 rows, 28 q heads, 4 kv heads, head_dim 128.
+    A step = the fp16 twins, the tcgen05 attention kernel and the int8 mirror of all
+    4096 K/V rows, for `layers` layers with their own inputs (4 x 126 MB > L2)."""
+    import torch
+    import torch.distributed as dist
+
+    from tinycoder_inference_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    S, nH, nKV, hd, layers = 4096, 28, 4, 128, 4
+    inv = 1.0 / math.sqrt(hd)
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x7C0DE003 + rank)
+    q = torch.randn((layers, S, nH, hd), generator=g, device=dev)
+    k = torch.randn((layers, S, nKV, hd), generator=g, device=dev)
+    v = torch.randn((layers, S, nKV, hd), generator=g, device=dev)
+    # the reference rounds the operands to fp16; do it to the inputs so both arms see the same values
+    q, k, v = (x.half().float() for x in (q, k, v))
+    out = torch.empty_like(q)
+    k8 = torch.empty((layers, S + 16, nKV, hd), dtype=torch.int8, device=dev)
+    v8 = torch.empty_like(k8)
+    ks = torch.empty((layers, S + 16, nKV), device=dev)
+    vs = torch.empty_like(ks)
+    nbytes = ops.prefill_f16_scratch_bytes(S, nH, nKV, hd)
+    scratch = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
+    off = (-scratch.data_ptr()) % 1024
+    scratch = scratch[off:off + nbytes]
+
+    def step():
+        for l in range(layers):
+            ops.prefill_f16(q[l], k[l], v[l], out[l], scratch, S, nH, nKV, hd, invSqrt=inv)
+            ops.kv_quantize_i8(k[l], v[l], k8[l], v8[l], ks[l], vs[l], S, nKV, hd)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    props = torch.cuda.get_device_properties(local)
+    gpu_id = str(getattr(props, "uuid", local))
+    if "-" in gpu_id and not gpu_id.startswith("GPU-"):
+        gpu_id = "GPU-" + gpu_id
+    sampler = ClockSampler(gpu_id)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    # attention kernel alone (the dominant kernel), same inputs
+    ek0, ek1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kern_ms = 0.0
+    reps = max(3, min(args.steps, 20))
+    for r in range(reps):
+        l = r % layers
+        ops.prefill_f16(q[l], k[l], v[l], out[l], scratch, S, nH, nKV, hd, invSqrt=inv)
+    torch.cuda.synchronize()
+    ek0.record()
+    for r in range(reps):
+        l = r % layers
+        ops.prefill_f16(q[l], k[l], v[l], out[l], scratch, S, nH, nKV, hd, invSqrt=inv)
+    ek1.record()
+    torch.cuda.synchronize()
+    kern_ms = ek0.elapsed_time(ek1) / reps
+    # end to end with host buffers: q, k, v of a layer from pinned memory, the output back
+    hq, hk, hv = q[0].cpu().pin_memory(), k[0].cpu().pin_memory(), v[0].cpu().pin_memory()
+    hout = torch.empty_like(hq).pin_memory()
+    dq, dk, dv, dout = torch.empty_like(q[0]), torch.empty_like(k[0]), torch.empty_like(v[0]), torch.empty_like(q[0])
+
+    def e2e_step():
+        for l in range(layers):
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            ops.prefill_f16(dq, dk, dv, dout, scratch, S, nH, nKV, hd, invSqrt=inv)
+            ops.kv_quantize_i8(dk, dv, k8[l], v8[l], ks[l], vs[l], S, nKV, hd)
+            hout.copy_(dout, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    n_e2e = max(2, min(args.steps, 10))
+    for _ in range(n_e2e):
+        e2e_step()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / n_e2e
+    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    flags = ops.device_status()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    flops_layer = 2.0 * hd * nH * S * (S + 1)  # causal count: QK^T and PV over the lower triangle
+    pk = peaks()
+    tf = world * layers * flops_layer / (ms_per_step * 1e-3) / 1e12
+    tf_kernel = flops_layer / (kern_ms * 1e-3) / 1e12
+    line = {
+        "metric": "prefill_attn_tflops_s4096", "value": tf, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "us_per_layer": ms_per_step * 1e3 / layers,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16 operands, f32 accumulate (tcgen05), f32 softmax", "data": "synthetic",
+        "config": {"workload": f"prefill4k: causal prefill, {S} rows, {nH} q heads / {nKV} kv heads / head_dim {hd}, "
+                               f"{layers} layers per step, each with fp16 twins + attention + int8 mirror of all rows",
+                   "l2": f"inputs larger than L2: {layers} layers x 126 MB of q/k/v/out"},
+        "roofline": {"bound": "tensor", "achieved": tf_kernel, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": tf_kernel / pk["bf16_tflops"], "peak_source": pk["source"] + " (burst)", "traffic": None,
+                     "note": "attention launch alone (f32->fp16 twins + tcgen05 kernel), causal flop count"},
+        "e2e": {"value": world * layers * flops_layer / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": layers * (S * nH * hd + 2 * S * nKV * hd) * 4,
+                "d2h_bytes_per_step": layers * S * nH * hd * 4},
+        "gpu_launches": args.steps * layers * 5, "clocks": clocks, "device_error_flags": flags,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode32k", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="decode32k", choices=sorted(WORKLOADS) + ["prefill4k"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream order between the kernels of a step")
@@ -214,6 +352,9 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload == "prefill4k":
+        run_prefill(args)
         return
 
     import torch

@@ -5,7 +5,6 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
-#include <vector>
 
 #include "tc_common.cuh"
 
@@ -82,16 +81,20 @@ struct CacheEntry {
     CUtensorMap map;
 };
 
+// The cache is a fixed ring (no heap growth): entry points that promise not to
+// allocate go through here too.
 int getTensorMap(const TensorMapKey &key, CUtensorMap *out) {
     static std::mutex mu;
-    static std::vector<CacheEntry> cache;
+    constexpr int kSlots = 256;
+    static CacheEntry cache[kSlots];
+    static int used = 0, next = 0;
     int dev = 0;
     cudaGetDevice(&dev);
     {
         std::lock_guard<std::mutex> lk(mu);
-        for (const auto &e : cache) {
-            if (e.dev == dev && std::memcmp(&e.key, &key, sizeof(key)) == 0) {
-                *out = e.map;
+        for (int i = 0; i < used; ++i) {
+            if (cache[i].dev == dev && std::memcmp(&cache[i].key, &key, sizeof(key)) == 0) {
+                *out = cache[i].map;
                 return TC_OK;
             }
         }
@@ -121,13 +124,12 @@ int getTensorMap(const TensorMapKey &key, CUtensorMap *out) {
     TC_REQUIRE(r == CUDA_SUCCESS, TC_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int) r);
     {
         std::lock_guard<std::mutex> lk(mu);
-        if (cache.size() >= 256) cache.erase(cache.begin());
-        CacheEntry e;
+        CacheEntry &e = cache[next];
         e.dev = dev;
-        std::memset(&e.key, 0, sizeof(e.key));
         e.key = key;
         e.map = m;
-        cache.push_back(e);
+        next = (next + 1) % kSlots;
+        if (used < kSlots) ++used;
     }
     *out = m;
     return TC_OK;
