@@ -179,6 +179,26 @@ enum { TC_DECODE_PDL = 1u };
 
 int tc_attn_decode_i8_batch(const tc_decode_i8_batch *d, tc_stream stream);
 
+/* No counterpart in the reference.  The same int8 decode as tc_attn_decode_i8 for
+ * callers that cannot provide scratch memory because they cannot allocate any: a
+ * host that only passes device pointers from a memory plan fixed at load time, or a
+ * latency-critical serving loop that is not allowed to touch the device allocator
+ * once it is running.  The split-KV partials live in an array built into the library's device
+ * image -- about 5.3 MB on every GPU that loads the library, held until the
+ * process exits -- so the call takes only inputs and the output and performs no
+ * cudaMalloc / cudaFree / allocating library call.
+ * Limits: nHeads <= 64 and hd == 128 (TC_EWORKSPACE otherwise); host position only.
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call before any stream capture.
+ * All calls share the one array, which keeps the last call's partials: nothing in
+ * it needs clearing between calls, but two calls that overlap on the GPU (different
+ * streams) race on it -- serialise them. */
+int tc_attn_decode_i8_noalloc(const float *q, const int8_t *k8, const int8_t *v8,
+                              const float *ks, const float *vs, float *out,
+                              uint32_t nHeads, uint32_t nKV, uint32_t hd,
+                              uint32_t cachePos, uint64_t totalRows, float invSqrt,
+                              tc_stream stream);
+
 /* Replaces launchDecodeAttentionSplit (include/gpu/GpuAttentionKernels.hpp:
  * 1129-1230; launch GPUComputeForward.cu:3897-3902): split-KV decode over an
  * f32 (kvHalf == 0) or fp16 (kvHalf != 0) cache, seqLen query rows (the

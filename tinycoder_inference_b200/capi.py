@@ -140,6 +140,7 @@ SIGNATURES = {
     "tc_attn_decode_i8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u64,
                                _u32, _u32, _f, _vp]),
     "tc_attn_decode_i8_batch": (_i, [C.POINTER(DecodeI8Batch), _vp]),
+    "tc_attn_decode_i8_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u64, _f, _vp]),
     "tc_attn_decode_kv": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _u64, _u32,
                                _u32, _f, _i, _vp, _vp]),
     "tc_attn_merge_partials": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),

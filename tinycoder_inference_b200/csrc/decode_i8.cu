@@ -27,6 +27,8 @@
 //     the caller's partial buffers in the reference's layout and are merged by
 //     the merge kernel (merge.cu).
 #include "tc_common.cuh"
+#include <mutex>
+
 #include "decode_shared.cuh"
 
 namespace tc {
@@ -720,6 +722,80 @@ int tc_attn_decode_i8(const float *q, const int8_t *k8, const int8_t *v8, const 
     d.numChunks = numChunks;
     d.invSqrt = invSqrt;
     return tc::decodeI8Common(&d, cachePos + 1, devPos ? 1u : 0u, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------------------------
+// A decode entry point that allocates nothing
+// ---------------------------------------------------------------------------------
+// Some callers hold no allocator they may use at the moment attention runs: a host
+// that hands this library bare device pointers from a memory plan frozen at load
+// time, or a latency-critical serving loop that must not touch the device allocator
+// once it is running.  For them the split-KV partials (the only scratch this kernel needs)
+// live in a fixed array inside the library's own device image instead of in
+// caller-provided buffers.  Every GPU that loads the library carries the array
+// (kNoAllocBytes, about 5.3 MB) until the process exits.
+constexpr uint32_t kNoAllocMaxHeads = 64;    // q heads
+constexpr uint32_t kNoAllocChunks = 160;     // chunk slots per head (one per SM and a few spare)
+constexpr size_t kNoAllocAccFloats = static_cast<size_t>(kNoAllocMaxHeads) * kNoAllocChunks * tc::kHD;
+constexpr size_t kNoAllocMLFloats = static_cast<size_t>(kNoAllocMaxHeads) * kNoAllocChunks;
+constexpr size_t kNoAllocBytes = (kNoAllocAccFloats + 2 * kNoAllocMLFloats) * sizeof(float);
+static __device__ __align__(256) float g_noAllocScratch[kNoAllocAccFloats + 2 * kNoAllocMLFloats];
+
+// In host code the array's name is only a handle for the runtime, not a device
+// address, so the address is asked for once per device (with that device current)
+// and remembered.
+static int noAllocScratch(float **ptr) {
+    static std::mutex mu;
+    static float *addr[64] = {nullptr};
+    int dev = 0;
+    TC_CUDA_OK(cudaGetDevice(&dev));
+    TC_REQUIRE(dev >= 0 && dev < 64, TC_EUNSUPPORTED, "tc_attn_decode_i8_noalloc: device ordinal %d", dev);
+    std::lock_guard<std::mutex> lk(mu);
+    if (addr[dev] == nullptr) {
+        void *p = nullptr;
+        TC_CUDA_OK(cudaGetSymbolAddress(&p, g_noAllocScratch));
+        addr[dev] = static_cast<float *>(p);
+    }
+    *ptr = addr[dev];
+    return TC_OK;
+}
+
+int tc_attn_decode_i8_noalloc(const float *q, const int8_t *k8, const int8_t *v8, const float *ks, const float *vs,
+                              float *out, uint32_t nHeads, uint32_t nKV, uint32_t hd, uint32_t cachePos,
+                              uint64_t totalRows, float invSqrt, tc_stream stream) {
+    TC_REQUIRE(nHeads >= 1 && nHeads <= kNoAllocMaxHeads, TC_EWORKSPACE,
+               "tc_attn_decode_i8_noalloc: %u q heads, the built-in scratch holds at most %u", nHeads,
+               kNoAllocMaxHeads);
+    TC_REQUIRE(hd == static_cast<uint32_t>(tc::kHD), TC_EWORKSPACE,
+               "tc_attn_decode_i8_noalloc: head_dim %u, the built-in scratch is laid out for %d", hd, tc::kHD);
+    TC_REQUIRE(static_cast<uint64_t>(cachePos) + 1 <= totalRows, TC_ECONTEXT_FULL,
+               "tc_attn_decode_i8_noalloc: position %u is outside the pool of %llu rows", cachePos,
+               (unsigned long long) totalRows);
+    float *scratch = nullptr;
+    const int rc = noAllocScratch(&scratch);
+    if (rc != TC_OK) return rc;
+    tc_decode_i8_batch d;
+    memset(&d, 0, sizeof(d));
+    d.q = q;
+    d.out = out;
+    d.k8 = k8;
+    d.v8 = v8;
+    d.ks = ks;
+    d.vs = vs;
+    // the three partial arrays are carved out of the one array; nothing in them has to
+    // start at zero (the merge reads only the chunk slots this call wrote)
+    d.pAcc = scratch;
+    d.pM = scratch + kNoAllocAccFloats;
+    d.pL = scratch + kNoAllocAccFloats + kNoAllocMLFloats;
+    d.totalRows = totalRows;
+    d.batch = 1;
+    d.nHeads = nHeads;
+    d.nKV = nKV;
+    d.hd = hd;
+    d.maxLen = cachePos + 1;
+    d.numChunks = kNoAllocChunks;
+    d.invSqrt = invSqrt;
+    return tc::decodeI8Common(&d, cachePos + 1, 0u, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

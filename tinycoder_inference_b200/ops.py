@@ -90,6 +90,16 @@ def decode_i8(q, k8, v8, ks, vs, out, ws, nHeads, nKV, hd, cachePos, numChunks, 
                                 numChunks, chunkSize, invSqrt, _stream()))
 
 
+def decode_i8_noalloc(q, k8, v8, ks, vs, out, nHeads, nKV, hd, cachePos, invSqrt=None):
+    """tc_attn_decode_i8 without caller scratch: the partials live in an array inside the
+    library (for callers that cannot allocate device memory)."""
+    if invSqrt is None:
+        invSqrt = 1.0 / math.sqrt(hd)
+    total_rows = k8.numel() // (nKV * hd)
+    check(lib.tc_attn_decode_i8_noalloc(_ptr(q), _ptr(k8), _ptr(v8), _ptr(ks), _ptr(vs), _ptr(out), nHeads, nKV,
+                                        hd, cachePos, total_rows, invSqrt, _stream()))
+
+
 def decode_i8_batch(q, k8, v8, ks, vs, out, ws, lens, batch, nHeads, nKV, hd, maxLen, numChunks,
                     rows_per_seq=0, row_base=None, invSqrt=None, partials_only=False, pdl=False,
                     prefetch_rows=0):
