@@ -115,70 +115,108 @@ def algorithmic_bytes(nKV, hd, tokens):
 # CPU baseline / reference arm
 # ---------------------------------------------------------------------------------
 
+class CpuAttention:
+    """The reference CPU attention path on ONE layer of a decode workload (the CPU
+    engine keeps K/V in f32 only, so it attends over the dequantised f32 copy of the
+    int8 store), or on a slice of query rows of the prefill workload."""
+
+    def __init__(self, nH, nKV, hd, ctx, q_rows=1, threads=0):
+        import numpy as np
+
+        import oracle
+        from tinycoder_inference_b200 import synth
+
+        self.shape = (nH, nKV, hd, ctx, q_rows)
+        self.q = synth.normal(2, 1, (q_rows, nH, hd))
+        k = synth.normal(2, 2, (ctx, nKV, hd))
+        v = synth.normal(2, 3, (ctx, nKV, hd))
+        if q_rows == 1:
+            k8, v8, ks, vs = oracle.quant_kv8(k, v, nKV, hd)
+            k = (k8.astype(np.float32) * ks[:, :, None]).astype(np.float32)
+            v = (v8.astype(np.float32) * vs[:, :, None]).astype(np.float32)
+        self.k, self.v = k, v
+        self.use_ref = oracle.ref_available() and oracle.ref().has_avx512()
+        if self.use_ref:
+            self.ref = oracle.ref()
+            self.cores = self.ref.pool_init(threads)
+            self.kind = "reference"
+            self.how = (f"reference ThreadPool::parallelFor2D({q_rows} x {nKV} tasks) + AVX-512 dot/axpy leaves, "
+                        "restated attentionFused task loop")
+        else:
+            self.oracle = oracle
+            self.cores = 1
+            self.kind = "port"
+            self.how = "scalar C restatement of Model::attentionFused"
+
+    def run(self):
+        nH, nKV, hd, ctx, rows = self.shape
+        if self.use_ref:
+            return self.ref.attention_fused(self.q, self.k, self.v, ctx - rows, rows, nH, nKV, hd)
+        return self.oracle.attention_fused_cpu(self.q, self.k, self.v, rows, ctx - rows, nH, nKV, hd)
+
+    def time(self, reps):
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            self.run()
+        return (time.perf_counter() - t0) / reps
+
+
 def cpu_attention_sample(nH, nKV, hd, ctx, budget_s=12.0, threads=0):
-    """Times the reference CPU attention on ONE layer of the workload (the CPU
-    engine keeps K/V in f32 only, so it attends over the dequantised f32 copy of
-    the int8 store).  Returns (seconds per layer, cores, kind, sample text)."""
-    import numpy as np
-
-    import oracle
-    from tinycoder_inference_b200 import synth
-
-    q = synth.normal(2, 1, (1, nH, hd))
-    k = synth.normal(2, 2, (ctx, nKV, hd))
-    v = synth.normal(2, 3, (ctx, nKV, hd))
-    k8, v8, ks, vs = oracle.quant_kv8(k, v, nKV, hd)
-    kf = (k8.astype(np.float32) * ks[:, :, None]).astype(np.float32)
-    vf = (v8.astype(np.float32) * vs[:, :, None]).astype(np.float32)
-    use_ref = oracle.ref_available() and oracle.ref().has_avx512()
-    if use_ref:
-        ref = oracle.ref()
-        cores = ref.pool_init(threads)
-        run = lambda: ref.attention_fused(q, kf, vf, ctx - 1, 1, nH, nKV, hd)  # noqa: E731
-        kind = "reference"
-        how = ("reference ThreadPool::parallelFor2D(1 x %d kv heads) + AVX-512 dot/axpy leaves, restated "
-               "attentionFused task loop" % nKV)
-    else:
-        cores = 1
-        run = lambda: oracle.attention_fused_cpu(q, kf, vf, 1, ctx - 1, nH, nKV, hd)  # noqa: E731
-        kind = "port"
-        how = "scalar C restatement of Model::attentionFused"
-    run()
-    t0 = time.perf_counter()
-    reps = 0
-    while True:
-        run()
-        reps += 1
-        if time.perf_counter() - t0 > budget_s or reps >= 400:
-            break
-    per_layer = (time.perf_counter() - t0) / reps
-    sample = f"1 layer x {reps} repetitions, f32 copy of the int8 store, ctx {ctx}; {how}"
-    return per_layer, cores, kind, sample
+    """(seconds per layer, cores, kind, sample text) on a bounded sample."""
+    c = CpuAttention(nH, nKV, hd, ctx, 1, threads)
+    one = c.time(1)
+    reps = max(1, min(400, int(budget_s / max(one, 1e-6))))
+    per_layer = c.time(reps)
+    return per_layer, c.cores, c.kind, f"1 layer x {reps} repetitions, f32 copy of the int8 store, ctx {ctx}; {c.how}"
 
 
 def run_reference(args):
+    """The reference arm: the reference engine's CPU implementation of the path on the
+    host cores.  A step is a bounded sample: one layer of the decode workload, or the
+    last 32 query rows (full 4096-row causal prefix each) of the prefill workload."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    nH, nKV, hd, ctx, batch, layers = WORKLOADS[args.workload]
-    budget = max(2.0, min(20.0, 120.0 / max(1, args.steps + args.warmup)))
-    # a "step" of the CPU arm is a bounded sample: one layer, repeated
-    times = []
-    cores, kind, sample = 1, "port", ""
-    for i in range(args.warmup + args.steps):
-        per_layer, cores, kind, sample = cpu_attention_sample(nH, nKV, hd, ctx, budget_s=budget / 4)
-        if i >= args.warmup:
-            times.append(per_layer)
-    per_layer = sum(times) / len(times)
-    gbs = algorithmic_bytes(nKV, hd, ctx) / per_layer / 1e9
+    if args.workload == "prefill4k":
+        S, nH, nKV, hd, layers, rows = 4096, 28, 4, 128, 4, 32
+        c = CpuAttention(nH, nKV, hd, S, rows)
+        flops = sum(4.0 * hd * nH * (S - rows + r + 1) for r in range(rows))
+        metric, unit = "prefill_attn_tflops_s4096", "TFLOP/s"
+        per_unit = lambda t: flops / t / 1e12  # noqa: E731
+        sample = f"last {rows} query rows of one layer at the full causal prefix, f32; {c.how}"
+        cfg = {"workload": f"prefill4k: causal prefill, {S} rows, {nH} q heads / {nKV} kv heads / head_dim {hd} "
+                           "(CPU arm: a 32-row slice, f32)"}
+        ms_scale = (2.0 * hd * nH * S * (S + 1)) / flops * layers
+    else:
+        nH, nKV, hd, ctx, batch, layers = WORKLOADS[args.workload]
+        c = CpuAttention(nH, nKV, hd, ctx, 1)
+        nbytes = algorithmic_bytes(nKV, hd, ctx)
+        metric = ("decode_attn_kv_gbs_ctx32k" if args.workload == "decode32k"
+                  else f"decode_attn_kv_gbs_{args.workload}")
+        unit = "GB/s"
+        per_unit = lambda t: nbytes / t / 1e9  # noqa: E731
+        sample = f"one layer of one sequence per step, f32 copy of the int8 store, ctx {ctx}; {c.how}"
+        cfg = workload_config(args.workload, args.gpus)
+        ms_scale = layers * batch
+    one = c.time(1)
+    # keep the whole run within a few minutes whatever K and W are
+    per_step_reps = 1
+    total = (args.steps + args.warmup) * one
+    steps, warmup = args.steps, args.warmup
+    if total > 150.0:
+        warmup = min(warmup, 3)
+        steps = max(1, int(150.0 / one) - warmup)
+    for _ in range(warmup):
+        c.run()
+    per = c.time(steps * per_step_reps)
+    val = per_unit(per)
     line = {
-        "impl": "reference", "metric": "decode_attn_kv_gbs_ctx32k", "value": gbs, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": per_layer * layers * batch * 1e3, "us_per_layer": per_layer * 1e6,
+        "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": per * ms_scale * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.workload, args.gpus),
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
-        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": cfg,
+        "cpu_baseline": {"value": val, "unit": unit, "cores": c.cores, "kind": c.kind, "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)

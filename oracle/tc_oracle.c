@@ -15,11 +15,17 @@
  * Pinning status:
  *   - context planner: PINNED against the reference's own known answers
  *     (unit_tests/ContextPlanTest.cpp) and against the reference's compiled
- *     ContextPlan.cpp (oracle/_ref, see oracle/Makefile).
- *   - int8 quantiser, decode / prefill attention, KV append: the reference has no
- *     checkpoint-free test or golden vector for these ("parity unpinned" by the
- *     reference's tests); the contract is the kernel source restated here, cross-
- *     checked against a double-precision evaluation (orc_attention_f64).
+ *     ContextPlan.cpp (oracle/_ref/libtc_ref.so, tests/golden/planner_golden.json).
+ *   - int8 quantiser, int8 / f32 decode and causal attention, merge, Q8_1 fold,
+ *     RoPE / append, sigmoid gate, causal softmax rows: PINNED against outputs of the
+ *     reference's OWN CUDA kernels run on a B200 (oracle/ref_gpu_shim.cu ->
+ *     tests/golden/ref_gpu_golden.npz; tests/test_oracle_ref_gpu_golden.py):
+ *     bit-exact for bytes / integers / rotated values, a few ulp for softmax outputs
+ *     (device exp2f versus libm).  The reference has no checkpoint-free test of its
+ *     own for these, so the recorded kernel outputs are the anchor.
+ *   - the QK^T / PV products of the materialised fp16 prefill live in cuBLAS (not
+ *     part of the reference): orc_prefill_f16 states the contract (fp16 products,
+ *     f32 accumulation, fp16 probabilities) and is unpinned at kernel level.
  *
  * Build: see oracle/Makefile (gcc -O2 -mfma -ffp-contract=off; contraction is
  * switched off so that every fused multiply-add below is an explicit fmaf, as in

@@ -1,0 +1,82 @@
+"""The library's kernels against outputs recorded from the reference project's own
+CUDA kernels on a B200 (tests/golden/ref_gpu_golden.npz): same seeded inputs, the
+reference's result on one side, ours on the other -- no oracle in between."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tinycoder_inference_b200 import ops
+from tests.golden import ref_gpu_cases as cases
+from tests.util import assert_close, dev, host
+
+pytestmark = pytest.mark.gpu
+G = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_gpu_golden.npz"))
+C = cases.CASES
+
+
+@pytest.mark.parametrize("name,case_id", [("quant_hd128", 1), ("quant_hd256", 2)])
+def test_quantiser_equals_reference_kernel_bytes(name, case_id):
+    c = C[name]
+    k, v = cases.quant_case(case_id, c["tokens"], c["nKV"], c["hd"])
+    k8 = torch.zeros((c["tokens"], c["nKV"], c["hd"]), dtype=torch.int8, device="cuda")
+    v8 = torch.zeros_like(k8)
+    ks = torch.zeros((c["tokens"], c["nKV"]), device="cuda")
+    vs = torch.zeros_like(ks)
+    ops.kv_quantize_i8(dev(k), dev(v), k8, v8, ks, vs, c["tokens"], c["nKV"], c["hd"])
+    for key, t in (("k8", k8), ("v8", v8), ("ks", ks), ("vs", vs)):
+        assert np.array_equal(host(t), G[f"{name}.{key}"]), key
+
+
+@pytest.mark.parametrize("name,case_id", [("decode_f32_c1", 5), ("decode_f32_7b", 6)])
+def test_f32_decode_equals_reference_launcher(name, case_id):
+    c = C[name]
+    k, v = cases.store_case(case_id, c["ctx"], c["nKV"], c["hd"])
+    q = cases.q_case(case_id, 1, c["nH"], c["hd"])
+    out = torch.empty((1, c["nH"], c["hd"]), device="cuda")
+    q81 = torch.zeros(c["nH"] * (c["hd"] // 32) * 40, dtype=torch.uint8, device="cuda")
+    ops.decode_kv(dev(q), dev(k), dev(v), out, ops.workspace(1, c["nH"], c["hd"], c["chunks"]), 1, c["nH"], c["nKV"],
+                  c["hd"], c["ctx"] - 1, c["chunks"], c["chunk"], 1.0 / math.sqrt(c["hd"]), q81=q81)
+    assert_close(host(out), G[f"{name}.out"], what=name)
+    # the Q8_1 bytes follow our own f32 output exactly; against the reference's bytes allow the
+    # last-digit differences that a 1e-3 output tolerance implies: quantised values within one step
+    ours = host(q81).reshape(-1, 40)[:, 4:].view(np.int8).astype(np.int32)
+    theirs = G[f"{name}.q81"].reshape(-1, 40)[:, 4:].view(np.int8).astype(np.int32)
+    assert np.abs(ours - theirs).max() <= 1
+
+
+def test_causal_rows_equal_reference_kernel():
+    c = C["attention_f32"]
+    k, v = cases.store_case(7, c["cachePos"] + c["S"], c["nKV"], c["hd"])
+    q = cases.q_case(7, c["S"], c["nH"], c["hd"])
+    out = torch.empty((c["S"], c["nH"], c["hd"]), device="cuda")
+    ops.prefill_kv(dev(q), dev(k), dev(v), out, c["S"], c["nH"], c["nKV"], c["hd"], c["cachePos"])
+    assert_close(host(out), G["attention_f32.out"], what="kWarpAttention")
+
+
+def test_rope_and_append_equal_reference_kernels_bitwise():
+    c = C["rope_store"]
+    cosT, sinT = oracle.rope_tables(c["rows"], c["hd"], c["theta"])
+    kS, vS = cases.store_case(8, c["S"], c["nKV"], c["hd"])
+    q = dev(cases.q_case(8, c["S"], c["nH"], c["hd"]))
+    kD = torch.zeros((c["rows"], c["nKV"], c["hd"]), device="cuda")
+    vD = torch.zeros_like(kD)
+    ops.kv_append_rope(q, dev(kS), dev(vS), kD, vD, c["S"], c["nH"], c["nKV"], c["hd"], c["cachePos"], c["cachePos"],
+                       dev(cosT), dev(sinT))
+    assert np.array_equal(host(q), G["rope_store.q"])
+    assert np.array_equal(host(kD), G["rope_store.k"]) and np.array_equal(host(vD), G["rope_store.v"])
+
+
+def test_merge_and_gate_equal_reference_kernels():
+    c = C["combine_q81"]
+    acc, m, l = cases.partials_case(9, c["nH"], c["chunks"], c["hd"])
+    out = torch.empty((1, c["nH"], c["hd"]), device="cuda")
+    ops.merge_partials(dev(acc), dev(m), dev(l), out, 1, c["nH"], c["chunks"], c["hd"])
+    assert_close(host(out), G["combine_q81.out"], rtol=1e-5, atol=1e-6, what="merge")
+    c = C["sigmoid_gate"]
+    o = dev(cases.q_case(10, c["S"], c["nH"], c["hd"]))
+    ops.sigmoid_gate(o, dev(cases.q_case(11, c["S"], c["nH"], 2 * c["hd"]) * 4), c["S"], c["nH"], c["hd"])
+    assert_close(host(o), G["sigmoid_gate.out"], rtol=1e-5, atol=1e-6, what="gate")
