@@ -208,20 +208,29 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             tcFenceAfter();
             const bool diag = j == qt;
-            // pass 1: row maximum of the scaled scores
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (uint32_t c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmemLd32(tS[b] + laneBase + c * 32u, r);
-                tmemLdWait();
+            // the whole score row in registers: one TMEM pass per tile
+            uint32_t r[4][32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float s = __uint_as_float(r[i]) * p.scaleLog2;
-                    const bool valid = !diag || (j * kPfBN + c * 32u + i <= rq);
-                    mx = fmaxf(mx, valid ? s : -INFINITY);
-                }
+            for (int c = 0; c < 4; ++c) tmemLd32(tS[b] + laneBase + c * 32u, r[c]);
+            tmemLdWait();
+            if (diag) {
+                // causal edge: token j*128 + col is visible iff it is <= this row's position
+                const uint32_t lim = rq - j * kPfBN;  // last visible column (>= 0 on the diagonal tile)
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (static_cast<uint32_t>(c * 32 + i) > lim) r[c][i] = 0xff800000u;  // -inf
             }
+            float mxa = -INFINITY, mxb = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    mxa = fmaxf(mxa, __uint_as_float(r[c][i]));
+                    mxb = fmaxf(mxb, __uint_as_float(r[c][i + 1]));
+                }
+            const float mx = fmaxf(mxa, mxb) * p.scaleLog2;  // scale > 0: max commutes with it
             const float mNew = mx > m + kPfLazyLog2 ? mx : m;
             const float alpha = fastExp2(m - mNew);
             // O and the P buffer are free once the previous tile's PV has completed
@@ -234,35 +243,33 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (__any_sync(0xffffffffu, mNew != m)) {
 #pragma unroll 1
                     for (uint32_t c = 0; c < 4; ++c) {
-                        uint32_t r[32];
-                        tmemLd32(tO + laneBase + c * 32u, r);
+                        uint32_t o[32];
+                        tmemLd32(tO + laneBase + c * 32u, o);
                         tmemLdWait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmemSt32(tO + laneBase + c * 32u, r);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmemSt32(tO + laneBase + c * 32u, o);
                     }
                     tmemStWait();
                 }
             }
             m = mNew;
-            // pass 2: probabilities, fp16, into the A operand of the PV product
-            float sum = 0.0f;
-#pragma unroll 1
-            for (uint32_t c = 0; c < 4; ++c) {
-                uint32_t r[32], h[16];
-                tmemLd32(tS[b] + laneBase + c * 32u, r);
-                tmemLdWait();
+            // probabilities, fp16, into the A operand of the PV product
+            float suma = 0.0f, sumb = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t h[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const bool v0 = !diag || (j * kPfBN + c * 32u + 2 * i <= rq);
-                    const bool v1 = !diag || (j * kPfBN + c * 32u + 2 * i + 1 <= rq);
-                    const float p0 = v0 ? fastExp2(fmaf(__uint_as_float(r[2 * i]), p.scaleLog2, -m)) : 0.0f;
-                    const float p1 = v1 ? fastExp2(fmaf(__uint_as_float(r[2 * i + 1]), p.scaleLog2, -m)) : 0.0f;
-                    sum += p0 + p1;
+                    const float p0 = fastExp2(fmaf(__uint_as_float(r[c][2 * i]), p.scaleLog2, -m));
+                    const float p1 = fastExp2(fmaf(__uint_as_float(r[c][2 * i + 1]), p.scaleLog2, -m));
+                    suma += p0;
+                    sumb += p1;
                     h[i] = packHalf2(p0, p1);
                 }
                 tmemSt16(tP[b] + laneBase + c * 16u, h);
             }
+            const float sum = suma + sumb;
             l = l * alpha + sum;
             tmemStWait();
             tcFenceBefore();
