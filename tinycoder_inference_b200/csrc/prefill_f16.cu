@@ -10,21 +10,23 @@
 // scores, probabilities rounded to fp16 -- but flash-style, so the score matrix
 // never exists and the sequence length is not capped at 512.
 //
-// One CTA = one q head x 128 query rows.  Warp roles:
-//   warps 0-3  softmax: thread r owns query row r, reads its 128 scores from TMEM
-//              (tcgen05.ld), keeps (m, l), writes the fp16 probabilities back to TMEM
-//              (tcgen05.st) as the A operand of the PV product, rescales O in TMEM
-//              only when the row maximum ran ahead by 2^8 (lazy rescale);
-//   warp 4     TMA producer: Q once, then K / V tiles of 128 tokens into two-stage
-//              rings (cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA
+// One CTA = one q head x 256 query rows = two 128-row query tiles A and B.  Warp roles:
+//   warps 0-3 / 4-7  softmax of tile A / B: thread r owns query row r, reads its 128
+//              scores from TMEM in one pass (tcgen05.ld), keeps (m, l), writes the fp16
+//              probabilities over the first 64 columns of the same S region (tcgen05.st)
+//              as the A operand of the PV product, rescales O in TMEM only when the row
+//              maximum ran ahead by 2^8 (lazy rescale);
+//   warp 8     TMA producer: both Q tiles once, then K / V tiles of 128 tokens into
+//              two-stage rings (cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA
 //              shared-memory layout, so no register pass touches the operands);
-//   warp 5     MMA issuer: one elected thread issues tcgen05.mma -- S = Q K^T
-//              (M128 N128 K16 x8) into one of two S buffers so that the softmax of
-//              tile j overlaps the QK^T of tile j+1, then O += P V (A from TMEM, B = V
-//              MN-major from shared memory) -- and tcgen05.commit onto mbarriers.
+//   warp 9     MMA issuer: one thread issues tcgen05.mma -- S_X = Q_X K^T (M128 N128 K16
+//              x8), O_X += P_X V (A from TMEM, B = V MN-major from shared memory) -- in the
+//              order S_A, S_B, then per KV tile [O_A, S_A(next)], [O_B, S_B(next)], so the
+//              tensor pipe works for one tile while the other tile's softmax runs;
+//              tcgen05.commit onto mbarriers.
 // Causality: a query tile only visits KV tiles up to its own diagonal tile, which is
-// masked element-wise; heavy (late) query tiles are scheduled first.
-// TMEM: S0, S1 (128 columns each, f32), O (128), P0, P1 (64 each, packed fp16) = 512.
+// masked element-wise; heavy (late) query blocks are scheduled first.
+// TMEM: S_A, S_B (128 columns each, f32; P aliases their first 64), O_A, O_B (128 each) = 512.
 // Every wait is bounded; a wait that runs out records an error bit, the CTA drains and
 // frees its TMEM before it returns.
 #include <algorithm>
@@ -56,18 +58,18 @@ f32ToF16Kernel(const float4 *__restrict__ x, uint2 *__restrict__ y, size_t n4) {
 struct PrefillF16Params {
     float *out;        // [seqLen][nHeads][128] f32
     uint32_t seqLen, nHeads, nKV, group;
-    uint32_t nQTiles;
+    uint32_t nQTiles;  // 256-row query blocks
     float scaleLog2;   // invSqrt * log2(e)
     unsigned int *err;
 };
 
 struct PrefillF16Smem {
     static constexpr int kTile = kPfBM * kPfHD * 2;          // 32 KB: one 128x128 fp16 tile (two 64-column halves)
-    static constexpr int kQ = 0;
-    static constexpr int kK = kTile;
+    static constexpr int kQ = 0;                             // two query tiles
+    static constexpr int kK = 2 * kTile;
     static constexpr int kV = kK + kPfStages * kTile;
     static constexpr int kBars = kV + kPfStages * kTile;
-    static constexpr int kNumBars = 1 + 4 * kPfStages + 2 + 2 + 1;  // qFull, k/v full+empty, sFull[2], pFull[2], pvDone
+    static constexpr int kNumBars = 1 + 4 * kPfStages + 6;   // qFull, k/v full+empty, sFull[2], pFull[2], pvDone[2]
     static constexpr int kTmemSlot = kBars + kNumBars * 8;
     static constexpr int kTotal = kTmemSlot + 16 + 1024;
 };
@@ -84,7 +86,9 @@ __device__ __forceinline__ bool pfWait(uint64_t *bar, uint32_t parity, unsigned 
     return false;
 }
 
-__global__ void __launch_bounds__(192, 1)
+// 320 threads: warps 0-3 softmax of query tile A, warps 4-7 softmax of query tile B
+// (rows 128 further down), warp 8 TMA producer, warp 9 MMA issuer.
+__global__ void __launch_bounds__(320, 1)
 prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const PrefillF16Params p) {
     using L = PrefillF16Smem;
@@ -96,24 +100,27 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint32_t *tmemSlot = reinterpret_cast<uint32_t *>(smem + L::kTmemSlot);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    // heavy query tiles (long causal prefixes) first
-    const uint32_t qt = p.nQTiles - 1u - blockIdx.x / p.nHeads;
+    // heavy query blocks (long causal prefixes) first
+    const uint32_t qb = p.nQTiles - 1u - blockIdx.x / p.nHeads;  // 256-row query block
     const uint32_t head = blockIdx.x % p.nHeads;
     const uint32_t kvHead = head / p.group;
-    const uint32_t m0 = qt * kPfBM;
-    const uint32_t nTiles = qt + 1u;  // KV tiles 0..qt; tile qt holds the diagonal
+    const uint32_t m0 = qb * 2u * kPfBM;
+    // query tile X (0 = A, 1 = B) sits on KV tile 2*qb + X; B may lie wholly past the sequence
+    const bool activeB = m0 + kPfBM < p.seqLen;
+    const uint32_t qtA = 2u * qb, qtB = qtA + 1u;
+    const uint32_t nTiles = activeB ? qtB + 1u : qtA + 1u;
 
     if (threadIdx.x == 0) {
         mbarInit(qFull, 1);
-        for (int s = 0; s < kPfStages; ++s) {
+        for (int s = 0; s < 2; ++s) {
             mbarInit(&kFull[s], 1);
             mbarInit(&kEmpty[s], 1);
             mbarInit(&vFull[s], 1);
             mbarInit(&vEmpty[s], 1);
             mbarInit(&sFull[s], 1);
             mbarInit(&pFull[s], 128);
+            mbarInit(&pvDone[s], 1);
         }
-        mbarInit(pvDone, 1);
         fenceBarrierInit();
         tmaPrefetchDesc(&tmQ);
         tmaPrefetchDesc(&tmK);
@@ -127,16 +134,17 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncthreads();
     tcFenceAfter();
     const uint32_t tmemBase = *reinterpret_cast<volatile uint32_t *>(tmemSlot);
-    const uint32_t tS[2] = {tmemBase, tmemBase + 128u};
-    const uint32_t tO = tmemBase + 256u;
-    const uint32_t tP[2] = {tmemBase + 384u, tmemBase + 448u};
+    // S of tile X at columns 128X (its fp16 probabilities overwrite the first 64 of them), O at 256 + 128X
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            mbarExpectTx(qFull, L::kTile);
-            tmaLoad3D(smem + L::kQ, &tmQ, qFull, 0, head, m0);
-            tmaLoad3D(smem + L::kQ + L::kTile / 2, &tmQ, qFull, 64, head, m0);
+            mbarExpectTx(qFull, 2 * L::kTile);
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                tmaLoad3D(smem + L::kQ + x * L::kTile, &tmQ, qFull, 0, head, m0 + x * kPfBM);
+                tmaLoad3D(smem + L::kQ + x * L::kTile + L::kTile / 2, &tmQ, qFull, 64, head, m0 + x * kPfBM);
+            }
             for (uint32_t j = 0; j < nTiles; ++j) {
                 const uint32_t b = j & 1u;
                 if (j >= kPfStages && !pfWait(&kEmpty[b], ((j >> 1) - 1u) & 1u, p.err, kDevErrEmptyWait)) break;
@@ -151,76 +159,85 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 tmaLoad3D(vd + L::kTile / 2, &tmV, &vFull[b], 64, kvHead, j * kPfBN);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------- MMA issuer -------------------------------
+        // Order: S_A(0), S_B(0), then per KV tile j: [P_A(j)] O_A += P_A V, S_A(j+1); [P_B(j)] O_B += P_B V,
+        // S_B(j+1) -- while one tile's softmax runs, the tensor pipe works for the other tile.
         if (lane == 0) {
             constexpr uint32_t idQK = umaInstrDescF16(kPfBM, kPfBN, 0, 0);
             constexpr uint32_t idPV = umaInstrDescF16(kPfBM, kPfHD, 0, 1);
-            const uint32_t qAddr = smemAddr(smem + L::kQ);
-            auto issueQK = [&](uint32_t j) -> bool {
-                const uint32_t b = j & 1u;
-                if (!pfWait(&kFull[b], (j >> 1) & 1u, p.err, kDevErrFullWait)) return false;
-                tcFenceAfter();
-                const uint32_t kAddr = smemAddr(smem + L::kK + b * L::kTile);
+            auto tileOn = [&](uint32_t x, uint32_t j) { return x == 0 ? j <= qtA : (activeB && j <= qtB); };
+            auto issueQK = [&](uint32_t x, uint32_t j) {
+                const uint32_t qAddr = smemAddr(smem + L::kQ + x * L::kTile);
+                const uint32_t kAddr = smemAddr(smem + L::kK + (j & 1u) * L::kTile);
 #pragma unroll
                 for (uint32_t ks = 0; ks < 8; ++ks) {
-                    // K-major, 128-byte swizzle: 16 fp16 (32 bytes) per step inside a 64-column half
                     const uint32_t off = (ks >> 2) * (L::kTile / 2) + (ks & 3u) * 32u;
-                    umaMmaSS(tS[b], umaSmemDesc(qAddr + off, 16, 1024), umaSmemDesc(kAddr + off, 16, 1024), idQK,
-                             ks > 0 ? 1u : 0u);
+                    umaMmaSS(tmemBase + 128u * x, umaSmemDesc(qAddr + off, 16, 1024), umaSmemDesc(kAddr + off, 16, 1024),
+                             idQK, ks > 0 ? 1u : 0u);
                 }
-                umaCommit(&sFull[b]);
-                umaCommit(&kEmpty[b]);
-                return true;
+                umaCommit(&sFull[x]);
             };
-            bool ok = pfWait(qFull, 0, p.err, kDevErrFullWait);
-            if (ok) ok = issueQK(0);
+            bool ok = pfWait(qFull, 0, p.err, kDevErrFullWait) && pfWait(&kFull[0], 0, p.err, kDevErrFullWait);
+            if (ok) {
+                tcFenceAfter();
+                issueQK(0, 0);
+                if (tileOn(1, 0)) issueQK(1, 0);
+                umaCommit(&kEmpty[0]);
+            }
             for (uint32_t j = 0; ok && j < nTiles; ++j) {
                 const uint32_t b = j & 1u;
-                if (j + 1 < nTiles && !issueQK(j + 1)) break;  // S of the next tile while this tile's softmax runs
+                const bool more = j + 1 < nTiles;
                 if (!pfWait(&vFull[b], (j >> 1) & 1u, p.err, kDevErrFullWait)) break;
-                if (!pfWait(&pFull[b], (j >> 1) & 1u, p.err, kDevErrMmaWait)) break;
-                tcFenceAfter();
+                if (more && !pfWait(&kFull[b ^ 1u], ((j + 1) >> 1) & 1u, p.err, kDevErrFullWait)) break;
                 const uint32_t vAddr = smemAddr(smem + L::kV + b * L::kTile);
+                for (uint32_t x = 0; x < 2 && ok; ++x) {
+                    if (!tileOn(x, j)) continue;
+                    if (!pfWait(&pFull[x], j & 1u, p.err, kDevErrMmaWait)) {
+                        ok = false;
+                        break;
+                    }
+                    tcFenceAfter();
 #pragma unroll
-                for (uint32_t ks = 0; ks < 8; ++ks) {
-                    // A = P from TMEM (16 tokens = 8 packed columns per step); B = V, MN-major:
-                    // 64-dim halves 16 KB apart (leading offset), 8-token groups 1 KB apart (stride offset)
-                    umaMmaTS(tO, tP[b] + ks * 8u, umaSmemDesc(vAddr + ks * 2048u, L::kTile / 2, 1024), idPV,
-                             (j > 0 || ks > 0) ? 1u : 0u);
+                    for (uint32_t ks = 0; ks < 8; ++ks)
+                        umaMmaTS(tmemBase + 256u + 128u * x, tmemBase + 128u * x + ks * 8u,
+                                 umaSmemDesc(vAddr + ks * 2048u, L::kTile / 2, 1024), idPV, (j > 0 || ks > 0) ? 1u : 0u);
+                    umaCommit(&pvDone[x]);
+                    if (more && tileOn(x, j + 1)) issueQK(x, j + 1);  // overwrites P_x(j): issued after its PV
                 }
                 umaCommit(&vEmpty[b]);
-                umaCommit(pvDone);
+                if (more) umaCommit(&kEmpty[b ^ 1u]);
             }
         }
     } else {
         // --------------------------------- softmax ---------------------------------
-        const uint32_t row = warp * 32u + lane;          // row of the query tile = TMEM lane
-        const uint32_t laneBase = (warp * 32u) << 16;    // TMEM lane field
-        const uint32_t rq = m0 + row;                    // query position
+        const uint32_t x = warp >> 2;                         // which query tile this warpgroup owns
+        const uint32_t row = (warp & 3u) * 32u + lane;        // row of that tile = TMEM lane
+        const uint32_t laneBase = ((warp & 3u) * 32u) << 16;  // TMEM lane field
+        const uint32_t rq = m0 + x * kPfBM + row;             // query position
+        const uint32_t qt = x == 0 ? qtA : qtB;               // diagonal KV tile of this query tile
+        const uint32_t tS = tmemBase + 128u * x, tO = tmemBase + 256u + 128u * x;
         float m = kNegBig, l = 0.0f;
-        bool ok = true;
-        for (uint32_t j = 0; j < nTiles; ++j) {
-            const uint32_t b = j & 1u;
-            if (!pfWait(&sFull[b], (j >> 1) & 1u, p.err, kDevErrMmaWait)) {
+        bool ok = x == 0 || activeB;
+        const uint32_t myTiles = ok ? qt + 1u : 0u;
+        for (uint32_t j = 0; j < myTiles; ++j) {
+            if (!pfWait(&sFull[x], j & 1u, p.err, kDevErrMmaWait)) {
                 ok = false;
                 break;
             }
             tcFenceAfter();
-            const bool diag = j == qt;
             // the whole score row in registers: one TMEM pass per tile
             uint32_t r[4][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmemLd32(tS[b] + laneBase + c * 32u, r[c]);
+            for (int c = 0; c < 4; ++c) tmemLd32(tS + laneBase + c * 32u, r[c]);
             tmemLdWait();
-            if (diag) {
-                // causal edge: token j*128 + col is visible iff it is <= this row's position
-                const uint32_t lim = rq - j * kPfBN;  // last visible column (>= 0 on the diagonal tile)
+            if (j == qt) {
+                // causal edge: column c of the diagonal tile is visible iff c <= row
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (static_cast<uint32_t>(c * 32 + i) > lim) r[c][i] = 0xff800000u;  // -inf
+                        if (static_cast<uint32_t>(c * 32 + i) > row) r[c][i] = 0xff800000u;  // -inf
             }
             float mxa = -INFINITY, mxb = -INFINITY;
 #pragma unroll
@@ -233,9 +250,9 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float mx = fmaxf(mxa, mxb) * p.scaleLog2;  // scale > 0: max commutes with it
             const float mNew = mx > m + kPfLazyLog2 ? mx : m;
             const float alpha = fastExp2(m - mNew);
-            // O and the P buffer are free once the previous tile's PV has completed
+            // O is stable once the previous tile's PV has completed
             if (j > 0) {
-                if (!pfWait(pvDone, (j - 1u) & 1u, p.err, kDevErrMmaWait)) {
+                if (!pfWait(&pvDone[x], (j - 1u) & 1u, p.err, kDevErrMmaWait)) {
                     ok = false;
                     break;
                 }
@@ -254,7 +271,8 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
             }
             m = mNew;
-            // probabilities, fp16, into the A operand of the PV product
+            // probabilities as fp16 pairs, written over the first 64 columns of this tile's S:
+            // the A operand of the PV product (every score of the row is already in registers)
             float suma = 0.0f, sumb = 0.0f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -267,29 +285,28 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     sumb += p1;
                     h[i] = packHalf2(p0, p1);
                 }
-                tmemSt16(tP[b] + laneBase + c * 16u, h);
+                tmemSt16(tS + laneBase + c * 16u, h);
             }
-            const float sum = suma + sumb;
-            l = l * alpha + sum;
+            l = l * alpha + (suma + sumb);
             tmemStWait();
             tcFenceBefore();
-            mbarArrive(&pFull[b]);
+            mbarArrive(&pFull[x]);
         }
-        if (ok && pfWait(pvDone, (nTiles - 1u) & 1u, p.err, kDevErrMmaWait)) {
+        if (ok && myTiles && pfWait(&pvDone[x], (myTiles - 1u) & 1u, p.err, kDevErrMmaWait)) {
             tcFenceAfter();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             float *orow = p.out + (static_cast<size_t>(rq) * p.nHeads + head) * kPfHD;
 #pragma unroll 1
             for (uint32_t c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmemLd32(tO + laneBase + c * 32u, r);
+                uint32_t o[32];
+                tmemLd32(tO + laneBase + c * 32u, o);
                 tmemLdWait();
                 if (rq < p.seqLen) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         *reinterpret_cast<float4 *>(orow + c * 32 + 4 * i) =
-                                make_float4(__uint_as_float(r[4 * i]) * inv, __uint_as_float(r[4 * i + 1]) * inv,
-                                            __uint_as_float(r[4 * i + 2]) * inv, __uint_as_float(r[4 * i + 3]) * inv);
+                                make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
+                                            __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
                 }
             }
         }
@@ -354,7 +371,7 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
                prefillScratchBytes(seqLen, nHeads, nKV));
     TC_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 1023u) == 0, TC_EINVAL,
                "tc_attn_prefill_f16: scratch needs 1024-byte alignment");
-    const uint32_t nQTiles = (seqLen + kPfBM - 1) / kPfBM;
+    const uint32_t nQTiles = (seqLen + 2 * kPfBM - 1) / (2 * kPfBM);  // 256-row query blocks
     TC_REQUIRE(static_cast<uint64_t>(nQTiles) * nHeads < (1ull << 31), TC_EUNSUPPORTED,
                "tc_attn_prefill_f16: grid too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -398,7 +415,7 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
                                         PrefillF16Smem::kTotal));
         attrDone[dev] = true;
     }
-    prefillF16Kernel<<<nQTiles * nHeads, 192, PrefillF16Smem::kTotal, st>>>(tmQ, tmK, tmV, prm);
+    prefillF16Kernel<<<nQTiles * nHeads, 320, PrefillF16Smem::kTotal, st>>>(tmQ, tmK, tmV, prm);
     TC_CUDA_OK(cudaGetLastError());
     return TC_OK;
 }
