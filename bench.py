@@ -375,13 +375,119 @@ def run_prefill(args):
         dist.destroy_process_group()
 
 
+def run_sharded(args):
+    """Qwen2.5-32B-shaped long-context decode (40 q heads, 8 kv heads, head_dim 128, ctx
+    131072, int8 KV), ONE sequence split over the ranks -- strong scaling:
+      c4_heads    : kv-head groups (each rank holds nKV/N heads of every row; disjoint output
+                    slices, no collective on the data path);
+      c4_ctxsplit : the context axis (each rank holds all heads of ctx/N rows; split-KV
+                    partials are all-gathered over NCCL and merged on every rank).
+    8 layers are resident per rank and cycled (a step = 8 layers)."""
+    import torch
+    import torch.distributed as dist
+
+    from tinycoder_inference_b200 import ops, sharding
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    nH, nKV, hd, ctx, layers = 40, 8, 128, 131072, 8
+    inv = 1.0 / math.sqrt(hd)
+    by_ctx = args.workload == "c4_ctxsplit"
+    if by_ctx:
+        lo, hi = sharding.plan_context_ranges(ctx, world)[rank]
+        my_rows, my_kv, my_q = hi - lo, nKV, nH
+    else:
+        if nKV % world != 0:
+            raise SystemExit(f"c4_heads needs a rank count that divides {nKV} kv heads")
+        sh = sharding.plan_kv_head_shards(nH, nKV, world)[rank]
+        my_rows, my_kv, my_q = ctx, sh.kv_hi - sh.kv_lo, sh.q_hi - sh.q_lo
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x7C0DE004 + rank)
+    rows = my_rows + 16
+    k8 = torch.empty((layers, rows, my_kv, hd), dtype=torch.int8, device=dev)
+    v8 = torch.empty_like(k8)
+    ks = torch.zeros((layers, rows, my_kv), device=dev)
+    vs = torch.zeros_like(ks)
+    step_rows = 16384
+    for l in range(layers):
+        for r0 in range(0, my_rows, step_rows):
+            n = min(step_rows, my_rows - r0)
+            kf = torch.randn((n, my_kv, hd), generator=g, device=dev)
+            vf = torch.randn((n, my_kv, hd), generator=g, device=dev)
+            ops.kv_quantize_i8(kf, vf, k8[l], v8[l], ks[l], vs[l], n, my_kv, hd, dst_base=r0)
+    g2 = torch.Generator(device=dev)
+    g2.manual_seed(0x7C0DE005)                 # q is the same on every rank
+    q_all = torch.randn((layers, 1, nH, hd), generator=g2, device=dev)
+    q = q_all if by_ctx else q_all[:, :, sh.q_lo:sh.q_hi].contiguous()
+    out = torch.empty((layers, 1, my_q, hd), device=dev)
+    chunk, chunks = ops.split_geometry(ctx, nH, hd)
+    chunks = min(chunks, 128)
+    ws = ops.workspace(1, my_q, hd, chunks)
+    splitter = sharding.ContextSplitDecoder(my_q, my_kv, hd, my_rows, chunk_slots=64) if by_ctx else None
+
+    def step():
+        for l in range(layers):
+            if by_ctx:
+                splitter(q[l], k8[l], v8[l], ks[l], vs[l], out[l], my_rows, invSqrt=inv)
+            else:
+                ops.decode_i8_batch(q[l], k8[l], v8[l], ks[l], vs[l], out[l], ws, None, 1, my_q, my_kv, hd, my_rows,
+                                    chunks, invSqrt=inv, pdl=True, prefetch_rows=my_rows - 1)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    flags = ops.device_status()
+    if rank == 0:
+        total_bytes = layers * algorithmic_bytes(nKV, hd, ctx)       # the whole sequence, all ranks together
+        pk = peaks()
+        val = total_bytes / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": f"decode_attn_kv_gbs_{args.workload}", "value": val, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "us_per_layer": ms_per_step * 1e3 / layers, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8 KV, f32 q/out", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: 40 q heads / 8 kv heads / head_dim 128, int8 KV, one sequence of "
+                                   f"{ctx} rows, {layers} layers per step",
+                       "sharding": ("context axis: ctx/N rows per rank, partials all-gathered over NCCL and merged"
+                                    if by_ctx else "kv-head groups: nKV/N heads per rank, no data-path collective"),
+                       "l2": "inputs larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": val / world, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": val / world / pk["hbm_gbs"], "peak_source": pk["source"], "traffic": None,
+                         "note": "per-GPU share of the algorithmic bytes over the step time"},
+            "gpu_launches": args.steps * layers * 2, "device_error_flags": flags,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode32k", choices=sorted(WORKLOADS) + ["prefill4k"])
+    ap.add_argument("--workload", default="decode32k", choices=sorted(WORKLOADS) + ["prefill4k", "c4_heads", "c4_ctxsplit"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream order between the kernels of a step")
@@ -393,6 +499,9 @@ def main():
         return
     if args.workload == "prefill4k":
         run_prefill(args)
+        return
+    if args.workload in ("c4_heads", "c4_ctxsplit"):
+        run_sharded(args)
         return
 
     import torch

@@ -222,6 +222,15 @@ int tc_attn_merge_partials(const float *pAcc, const float *pM, const float *pL,
                            uint32_t numChunks, uint32_t hd, uint8_t *q81Out,
                            tc_stream stream);
 
+/* The merge step of a context-axis split across GPUs (new capability: the reference is
+ * single-device).  `gathered` holds, rank after rank, the block every rank produced with
+ * partialsOnly: [acc [nHeads][chunksPerRank][hd] | m [nHeads][chunksPerRank] |
+ * l [nHeads][chunksPerRank]] (one all-gather of the rank's contiguous workspace).  Slots a
+ * rank did not write must hold l == 0.  Same rule as tc_attn_merge_partials; out [nHeads][hd]. */
+int tc_attn_merge_gathered(const float *gathered, float *out, uint32_t nHeads,
+                           uint32_t ranks, uint32_t chunksPerRank, uint32_t hd,
+                           tc_stream stream);
+
 /* ------------------------------------------------------------------------- */
 /* prefill attention                                                           */
 /* ------------------------------------------------------------------------- */

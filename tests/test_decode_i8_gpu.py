@@ -197,3 +197,54 @@ def test_dependent_launch_chain_and_host_lengths():
         assert_close(host(out), want, what=f"pdl={pdl}")
         outs[pdl] = out
     assert torch.equal(outs[False], outs[True])
+
+
+def test_context_split_partials_merge_on_one_gpu():
+    """The context-axis split as two 'ranks' on one device: each half of the rows yields
+    partials-only output, the partials are concatenated as the all-gather would and merged."""
+    nH, nKV, hd, ctx, C = 28, 4, 128, 5000, 16
+    rng = np.random.default_rng(31)
+    q = rng.standard_normal((1, nH, hd), dtype=np.float32)
+    k8, v8, ks, vs = make_i8_store(rng.standard_normal((ctx, nKV, hd), dtype=np.float32),
+                                   rng.standard_normal((ctx, nKV, hd), dtype=np.float32), nKV, hd)
+    inv = 1.0 / math.sqrt(hd)
+    want = oracle.attention_i8(q, k8, v8, ks, vs, 1, nH, nKV, hd, ctx - 1, inv)
+    from tinycoder_inference_b200 import sharding
+    parts = []
+    for lo, hi in sharding.plan_context_ranges(ctx, 2):
+        acc, m, l = ops.workspace(1, nH, hd, C)
+        acc.zero_()
+        m.fill_(-1e30)
+        l.zero_()
+        out = torch.empty((1, nH, hd), device="cuda")
+        ops.decode_i8_batch(dev(q), dev(k8[lo:hi]), dev(v8[lo:hi]), dev(ks[lo:hi]), dev(vs[lo:hi]), out, (acc, m, l),
+                            None, 1, nH, nKV, hd, hi - lo, C, invSqrt=inv, partials_only=True)
+        parts.append((acc.view(nH, C, hd), m.view(nH, C), l.view(nH, C)))
+    gacc = torch.cat([p[0] for p in parts], dim=1).contiguous()
+    gm = torch.cat([p[1] for p in parts], dim=1).contiguous()
+    gl = torch.cat([p[2] for p in parts], dim=1).contiguous()
+    out = torch.empty((1, nH, hd), device="cuda")
+    ops.merge_partials(gacc, gm, gl, out, 1, nH, 2 * C, hd)
+    assert_close(host(out), want, what="context split, two ranges")
+    # the same partials as ONE all-gathered buffer of per-rank [acc | m | l] blocks
+    gathered = torch.cat([torch.cat([a.reshape(-1), m.reshape(-1), l.reshape(-1)]) for a, m, l in parts]).contiguous()
+    out2 = torch.full((1, nH, hd), float("nan"), device="cuda")
+    ops.merge_gathered(gathered, out2, nH, 2, C, hd)
+    assert np.array_equal(host(out2), host(out)), "rank-strided merge differs from the concatenated one"
+
+
+@pytest.mark.gpu
+def test_context_split_decoder_single_rank_matches_oracle():
+    nH, nKV, hd, ctx = 16, 2, 128, 3000
+    rng = np.random.default_rng(32)
+    q = rng.standard_normal((1, nH, hd), dtype=np.float32)
+    k8, v8, ks, vs = make_i8_store(rng.standard_normal((ctx, nKV, hd), dtype=np.float32),
+                                   rng.standard_normal((ctx, nKV, hd), dtype=np.float32), nKV, hd)
+    inv = 1.0 / math.sqrt(hd)
+    want = oracle.attention_i8(q, k8, v8, ks, vs, 1, nH, nKV, hd, ctx - 1, inv)
+    from tinycoder_inference_b200 import sharding
+    dec = sharding.ContextSplitDecoder(nH, nKV, hd, ctx, chunk_slots=32)
+    out = torch.empty((1, nH, hd), device="cuda")
+    for _ in range(2):     # second call reuses the buffers
+        dec(dev(q), dev(k8), dev(v8), dev(ks), dev(vs), out, ctx, invSqrt=inv)
+    assert_close(host(out), want, what="ContextSplitDecoder, world 1")

@@ -8,7 +8,8 @@ namespace tc {
 
 int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out, uint32_t seqLen,
                 uint32_t nHeads, uint32_t numChunks, uint32_t activeHost, uint32_t hd, const uint32_t *devLens,
-                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st);
+                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st,
+                uint32_t chunksPerRank = 0, uint64_t rankStride = 0);
 
 #ifdef __CUDACC__
 __device__ __forceinline__ bool mbarWaitClock(uint64_t *bar, uint32_t parity, unsigned int *err,

@@ -29,11 +29,21 @@ __global__ void __launch_bounds__(256)
 mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM, const float *__restrict__ pL,
                     float *__restrict__ out, uint32_t nHeads, uint32_t numChunks, uint32_t activeHost,
                     uint32_t hd, const uint32_t *__restrict__ devLens, uint32_t lenAdd, uint32_t chunkTokens,
-                    uint8_t *__restrict__ q81) {
+                    uint8_t *__restrict__ q81, uint32_t chunksPerRank, uint64_t rankStride) {
     constexpr int NW = 8;
     const uint32_t head = blockIdx.x, s = blockIdx.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint64_t base = (static_cast<uint64_t>(s) * nHeads + head) * numChunks;
+    // Slot c of this (token, head): plain layout [token][head][numChunks], or -- for partials
+    // gathered from several ranks -- rank c / chunksPerRank, whose block (rankStride floats
+    // further on in each of the three arrays) holds [token][head][chunksPerRank].
+    const uint64_t headRow = static_cast<uint64_t>(s) * nHeads + head;
+    auto mlOff = [&](uint32_t c) -> uint64_t {
+        return static_cast<uint64_t>(c / chunksPerRank) * rankStride + headRow * chunksPerRank + c % chunksPerRank;
+    };
+    auto accOff = [&](uint32_t c) -> uint64_t {
+        return static_cast<uint64_t>(c / chunksPerRank) * rankStride +
+               (headRow * chunksPerRank + c % chunksPerRank) * hd;
+    };
     // under programmatic dependent launch: let the next grid start its prologue, then
     // wait until the grid that wrote the partials has finished (a no-op otherwise)
     gridDepLaunch();
@@ -62,7 +72,7 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
         for (int u = 0; u < kBatch; ++u) {
             const uint32_t c = c0 + u * NW;
             const uint32_t cc = c < active ? c : (active ? active - 1 : 0);  // always a valid address
-            const float4 *pac = reinterpret_cast<const float4 *>(pAcc + (base + cc) * hd);
+            const float4 *pac = reinterpret_cast<const float4 *>(pAcc + accOff(cc));
 #pragma unroll
             for (int j = 0; j < NV4; ++j) {
                 const uint32_t i = lane + 32u * j;
@@ -74,8 +84,8 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
     // ---- phase 1: max, weights, normaliser ----
     float M = kNegBig;
     for (uint32_t c = threadIdx.x; c < active; c += 256) {
-        const float m = pM[base + c];
-        const float lc = pL[base + c];
+        const float m = pM[mlOff(c)];
+        const float lc = pL[mlOff(c)];
         sw[c] = m;
         sl[c] = lc;
         M = fmaxf(M, m);
@@ -177,7 +187,9 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
 
 int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out, uint32_t seqLen,
                 uint32_t nHeads, uint32_t numChunks, uint32_t activeHost, uint32_t hd, const uint32_t *devLens,
-                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st) {
+                uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st,
+                uint32_t chunksPerRank, uint64_t rankStride) {
+    if (chunksPerRank == 0) chunksPerRank = numChunks;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(nHeads, seqLen);
     cfg.blockDim = dim3(256);
@@ -189,10 +201,10 @@ int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out,
     cfg.numAttrs = pdl ? 1 : 0;
     if (hd <= 128)
         TC_CUDA_OK(cudaLaunchKernelEx(&cfg, mergePartialsKernel<1>, pAcc, pM, pL, out, nHeads, numChunks,
-                                      activeHost, hd, devLens, lenAdd, chunkTokens, q81));
+                                      activeHost, hd, devLens, lenAdd, chunkTokens, q81, chunksPerRank, rankStride));
     else
         TC_CUDA_OK(cudaLaunchKernelEx(&cfg, mergePartialsKernel<2>, pAcc, pM, pL, out, nHeads, numChunks,
-                                      activeHost, hd, devLens, lenAdd, chunkTokens, q81));
+                                      activeHost, hd, devLens, lenAdd, chunkTokens, q81, chunksPerRank, rankStride));
     return TC_OK;
 }
 
@@ -212,7 +224,21 @@ int tc_attn_merge_partials(const float *pAcc, const float *pM, const float *pL, 
     TC_REQUIRE(seqLen <= 65535, TC_EUNSUPPORTED, "tc_attn_merge_partials: seqLen %u > 65535", seqLen);
     if (seqLen == 0) return TC_OK;
     return tc::launchMerge(pAcc, pM, pL, out, seqLen, nHeads, numChunks, numChunks, hd, nullptr, 0, 1, q81Out,
-                           false, static_cast<cudaStream_t>(stream));
+                           false, static_cast<cudaStream_t>(stream), 0, 0);
+}
+
+int tc_attn_merge_gathered(const float *gathered, float *out, uint32_t nHeads, uint32_t ranks,
+                           uint32_t chunksPerRank, uint32_t hd, tc_stream stream) {
+    TC_REQUIRE(gathered && out, TC_EINVAL, "tc_attn_merge_gathered: null pointer");
+    TC_REQUIRE(hd >= 32 && hd <= 256 && (hd % 32u) == 0, TC_EUNSUPPORTED, "tc_attn_merge_gathered: hd=%u", hd);
+    TC_REQUIRE(ranks >= 1 && chunksPerRank >= 1 && nHeads >= 1, TC_EINVAL, "tc_attn_merge_gathered: empty shape");
+    TC_REQUIRE(static_cast<uint64_t>(ranks) * chunksPerRank <= tc::kMergeMaxChunks, TC_EUNSUPPORTED,
+               "tc_attn_merge_gathered: %u x %u partials (max %d)", ranks, chunksPerRank, tc::kMergeMaxChunks);
+    const uint64_t ml = static_cast<uint64_t>(nHeads) * chunksPerRank;
+    const uint64_t block = ml * hd + 2 * ml;  // one rank's [acc | m | l]
+    return tc::launchMerge(gathered, gathered + ml * hd, gathered + ml * hd + ml, out, 1, nHeads,
+                           ranks * chunksPerRank, ranks * chunksPerRank, hd, nullptr, 0, 1, nullptr, false,
+                           static_cast<cudaStream_t>(stream), chunksPerRank, block);
 }
 
 int tc_attn_workspace_bytes(uint32_t batch, uint32_t nHeads, uint32_t hd, uint32_t numChunks, size_t *accBytes,

@@ -145,6 +145,11 @@ def merge_partials(pAcc, pM, pL, out, seqLen, nHeads, numChunks, hd, q81=None):
                                      _ptr(q81), _stream()))
 
 
+def merge_gathered(gathered, out, nHeads, ranks, chunksPerRank, hd):
+    """Merge the all-gathered [acc | m | l] blocks of `ranks` context shards."""
+    check(lib.tc_attn_merge_gathered(_ptr(gathered), _ptr(out), nHeads, ranks, chunksPerRank, hd, _stream()))
+
+
 # ---- prefill ------------------------------------------------------------------
 
 def prefill_f16_scratch_bytes(seqLen, nHeads, nKV, hd) -> int:

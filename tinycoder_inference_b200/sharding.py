@@ -116,6 +116,47 @@ def gather_partials(acc, m, l, group=None):
     return tuple(outs)
 
 
+class ContextSplitDecoder:
+    """One decode token attended over a context that is split by rows across the ranks of
+    `group`.  Every rank holds rows [0, local_len) of ITS range in its own pool, runs the
+    split-KV kernel in partials-only form into one contiguous block [acc | m | l], the blocks
+    are all-gathered (one NCCL call, a few tens of KB) and merged on every rank.
+
+    Buffers are allocated once; a step is three enqueues (decode, all-gather, merge) and can be
+    captured in a CUDA graph."""
+
+    def __init__(self, nHeads, nKV, hd, max_local_len, group=None, chunk_slots=16):
+        import torch
+        import torch.distributed as dist
+
+        self.nH, self.nKV, self.hd, self.group = nHeads, nKV, hd, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.C = chunk_slots
+        ml = nHeads * self.C
+        self.block = torch.zeros(ml * hd + 2 * ml, dtype=torch.float32, device="cuda")
+        self.acc = self.block[:ml * hd]
+        self.m = self.block[ml * hd:ml * hd + ml]
+        self.l = self.block[ml * hd + ml:]
+        self.gathered = torch.zeros(self.world * self.block.numel(), dtype=torch.float32, device="cuda")
+        self.max_local_len = max_local_len
+
+    def __call__(self, q, k8, v8, ks, vs, out, local_len, invSqrt=None):
+        import torch.distributed as dist
+
+        from . import ops
+
+        self.l.zero_()   # chunk slots this rank does not write must read as empty
+        if local_len > 0:
+            ops.decode_i8_batch(q, k8, v8, ks, vs, out, (self.acc, self.m, self.l), None, 1, self.nH, self.nKV,
+                                self.hd, local_len, self.C, invSqrt=invSqrt, partials_only=True)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered, self.block, group=self.group)
+            src = self.gathered
+        else:
+            src = self.block
+        ops.merge_gathered(src, out, self.nH, self.world, self.C, self.hd)
+
+
 def decode_i8_context_split(q, k8, v8, ks, vs, out, nHeads, nKV, hd, local_len, numChunks, invSqrt=None,
                             group=None):
     """One decode token attended over a context that is split by rows across the
