@@ -49,6 +49,17 @@ def test_head_layouts(nH, nKV):
     _run_single(nH, nKV, 128, 777, numChunks=64, seed=nH * 10 + nKV)
 
 
+@pytest.mark.parametrize("nH,nKV,ctx", [(8, 2, 700), (16, 4, 1), (16, 4, 17), (24, 4, 4097), (32, 8, 2500),
+                                         (6, 1, 333), (16, 2, 20000)])
+def test_head_dim_256(nH, nKV, ctx):
+    """The reference's own int8 shape (its int8 kernels are fixed at head_dim 256)."""
+    _run_single(nH, nKV, 256, ctx, numChunks=64, seed=nH + ctx)
+
+
+def test_head_dim_256_device_position_and_slack_rows():
+    _run_single(16, 4, 256, 1500, numChunks=32, seed=77, extra_rows=64, dev_pos=True)
+
+
 @pytest.mark.parametrize("numChunks", [1, 2, 3, 512])
 def test_chunk_slot_capacity(numChunks):
     _run_single(28, 4, 128, 5000, numChunks=numChunks, seed=numChunks)

@@ -12,10 +12,10 @@ from tests.util import assert_close, dev, host, make_i8_store
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("S,nH,nKV,cachePos", [(37, 28, 4, 0), (8, 28, 4, 100), (1, 28, 4, 55), (300, 12, 2, 17),
-                                              (64, 40, 8, 0), (9, 8, 8, 1000)])
-def test_causal_rows_over_int8_store(S, nH, nKV, cachePos):
-    hd = 128
+@pytest.mark.parametrize("S,nH,nKV,cachePos,hd", [(37, 28, 4, 0, 128), (8, 28, 4, 100, 128), (1, 28, 4, 55, 128),
+                                                 (300, 12, 2, 17, 128), (64, 40, 8, 0, 128), (9, 8, 8, 1000, 128),
+                                                 (5, 4, 2, 40, 256), (70, 16, 4, 0, 256), (13, 8, 2, 600, 256)])
+def test_causal_rows_over_int8_store(S, nH, nKV, cachePos, hd):
     rng = np.random.default_rng(S * 7 + cachePos)
     rows = cachePos + S
     q = rng.standard_normal((S, nH, hd), dtype=np.float32)

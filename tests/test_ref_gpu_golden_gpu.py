@@ -48,6 +48,32 @@ def test_f32_decode_equals_reference_launcher(name, case_id):
     assert np.abs(ours - theirs).max() <= 1
 
 
+def test_int8_decode_equals_reference_kernels():
+    """kQ35WarpAttention8Split + kAttnCombinePartial and the eager kQ35WarpAttention8 at the
+    reference's own shape (head_dim 256), store built by the pinned quantiser."""
+    c = C["decode_i8"]
+    k, v = cases.store_case(3, c["ctx"], c["nKV"], c["hd"])
+    q = cases.q_case(3, 1, c["nH"], c["hd"])
+    k8, v8, ks, vs = oracle.quant_kv8(k, v, c["nKV"], c["hd"])
+    out = torch.empty((1, c["nH"], c["hd"]), device="cuda")
+    ops.decode_i8(dev(q), dev(k8), dev(v8), dev(ks), dev(vs), out, ops.workspace(1, c["nH"], c["hd"], c["chunks"]),
+                  c["nH"], c["nKV"], c["hd"], c["ctx"] - 1, c["chunks"], c["chunk"], 1.0 / math.sqrt(c["hd"]))
+    assert_close(host(out), G["decode_i8.split_out"], what="int8 split decode")
+    assert_close(host(out), G["decode_i8.eager_out"], what="int8 eager decode")
+
+
+def test_int8_prefill_equals_reference_kernel():
+    c = C["prefill_i8"]
+    rows = c["cachePos"] + c["S"]
+    k, v = cases.store_case(4, rows, c["nKV"], c["hd"])
+    q = cases.q_case(4, c["S"], c["nH"], c["hd"])
+    k8, v8, ks, vs = oracle.quant_kv8(k, v, c["nKV"], c["hd"])
+    out = torch.empty((c["S"], c["nH"], c["hd"]), device="cuda")
+    ops.prefill_i8(dev(q), dev(k8), dev(v8), dev(ks), dev(vs), out, c["S"], c["nH"], c["nKV"], c["hd"], c["cachePos"],
+                   invSqrt=1.0 / math.sqrt(c["hd"]))
+    assert_close(host(out), G["prefill_i8.out"], what="kQ35WarpAttention8Prefill")
+
+
 def test_causal_rows_equal_reference_kernel():
     c = C["attention_f32"]
     k, v = cases.store_case(7, c["cachePos"] + c["S"], c["nKV"], c["hd"])

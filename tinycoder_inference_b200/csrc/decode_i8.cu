@@ -59,12 +59,17 @@ constexpr int kHD = 128;
 // MT = 16-row MMA tiles one consumer warp folds per stage: 2 amortises the softmax
 // bookkeeping over 32 tokens (large problems), 1 halves the work quantum so that a
 // small problem still spreads evenly over 148 SMs x 8 warps.
-template <int HPC, int NW, int NSTAGE, int MT>
+//
+// A stage holds K then V; each is stored as HD/128 half-tiles of [rows][128 bytes]
+// (the 128-byte swizzle spans exactly one half-row), half-tile h covering dims
+// [128h, 128h + 128).
+template <int HD, int HPC, int NW, int NSTAGE, int MT>
 struct DecodeI8Smem {
     static constexpr int kTokPerWarp = 16 * MT;
     static constexpr int kRows = NW * kTokPerWarp;       // (token, head) rows per stage
     static constexpr int T = kRows / HPC;                 // tokens per stage
-    static constexpr int kTileBytes = kRows * kHD;        // K (or V) bytes per stage, all HPC heads
+    static constexpr int kHalfBytes = kRows * 128;        // one half-tile, all HPC heads
+    static constexpr int kTileBytes = kRows * HD;         // K (or V) bytes per stage, all HPC heads
     static constexpr int kScaleBytes = kRows * 4;
     static constexpr int kStageBytes = 2 * kTileBytes + 2 * kScaleBytes;
     static constexpr int kBarOffset = NSTAGE * kStageBytes;
@@ -77,12 +82,13 @@ struct DecodeI8Smem {
 // maximum (log2 units) before the accumulators are rescaled.  p stays <= 2^8.
 constexpr float kLazyLog2 = 8.0f;
 
-template <int HPC, int NW, int NSTAGE, int MT>
+template <int HD, int HPC, int NW, int NSTAGE, int MT>
 __global__ void __launch_bounds__((NW + 1) * 32, 1)
 decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                const DecodeI8Params p) {
-    using L = DecodeI8Smem<HPC, NW, NSTAGE, MT>;
+    using L = DecodeI8Smem<HD, HPC, NW, NSTAGE, MT>;
     constexpr int T = L::T;
+    constexpr int NC = HD / 16;  // 16-dim groups of a head vector
     constexpr int kTokPerWarp = L::kTokPerWarp;
     constexpr int NR = 2 * MT;  // 8-token row groups of a warp's tile
     constexpr int NSUB = NW / HPC;  // consumer warps per kv head
@@ -151,9 +157,13 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 mbarExpectTx(&fullBar[s], 2 * L::kTileBytes);
 #pragma unroll
                 for (int h = 0; h < HPC; ++h) {
-                    tmaLoad3D(st + h * T * kHD, &tmK, &fullBar[s], 0, kvHead0 + h, static_cast<int>(row));
-                    tmaLoad3D(st + L::kTileBytes + h * T * kHD, &tmV, &fullBar[s], 0, kvHead0 + h,
-                              static_cast<int>(row));
+#pragma unroll
+                    for (int hf = 0; hf < HD / 128; ++hf) {
+                        uint8_t *dst = st + hf * L::kHalfBytes + h * T * 128;
+                        tmaLoad3D(dst, &tmK, &fullBar[s], hf * 128, kvHead0 + h, static_cast<int>(row));
+                        tmaLoad3D(dst + L::kTileBytes, &tmV, &fullBar[s], hf * 128, kvHead0 + h,
+                                  static_cast<int>(row));
+                    }
                 }
             }
             float *sK = reinterpret_cast<float *>(st + 2 * L::kTileBytes);
@@ -178,7 +188,7 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const uint32_t kvHead = kvHead0 + hL;
     // What MMA column j (0..7) of this warp stands for.
     auto colValid = [&](uint32_t j) { return p.rowsMode ? (b * 8u + j < p.qRows) : (j < p.group); };
-    auto colIndex = [&](uint32_t j) -> size_t {  // index of the column's q / out vector, in units of kHD
+    auto colIndex = [&](uint32_t j) -> size_t {  // index of the column's q / out vector, in units of HD
         return p.rowsMode ? (static_cast<size_t>(b) * 8u + j) * p.nHeads + hg
                           : static_cast<size_t>(b) * p.nHeads + kvHead * p.group + j;
     };
@@ -188,15 +198,15 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     // q fragments for head column n = g of this kv head's group: power-of-two
     // normalised, split into fp16 hi + lo, laid out as the B operand whose k
     // slots follow the byte order ldmatrix hands out (dims 16c + 4t + {0..3}).
-    uint32_t qhi[8][2], qlo[8][2];
+    uint32_t qhi[NC][2], qlo[NC][2];
     float headScale, headOff;
     {
-        float4 qv[8];
+        float4 qv[NC];
         float amax = 0.0f;
         const bool valid = colValid(g);
-        const float *qp = p.q + colIndex(valid ? g : 0) * kHD;
+        const float *qp = p.q + colIndex(valid ? g : 0) * HD;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < NC; ++c) {
             qv[c] = valid ? __ldg(reinterpret_cast<const float4 *>(qp + 16 * c + 4 * t))
                           : make_float4(0.f, 0.f, 0.f, 0.f);
             amax = fmaxf(amax, fmaxf(fmaxf(fabsf(qv[c].x), fabsf(qv[c].y)), fmaxf(fabsf(qv[c].z), fabsf(qv[c].w))));
@@ -210,7 +220,7 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         headScale = p.invSqrt * up * kLog2e;
         float qsum = 0.0f;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < NC; ++c) {
             float h0, l0, h1, l1, h2, l2, h3, l3;
             splitHalf(qv[c].x * down, h0, l0);
             splitHalf(qv[c].y * down, h1, l1);
@@ -239,9 +249,9 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     float ps0 = 0.0f, ps1 = 0.0f;  // sum of p*sv as fed to the PV MMA (V bytes enter as x + 128)
     uint32_t Ebits = 0;            // running power-of-two scale of the V row scales (0 = unset)
     float invE = 0.0f;
-    float o[8][4];
+    float o[NC][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    for (int i = 0; i < NC; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 
     const uint32_t lr = (lane & 7u) + ((lane >> 3) & 1u) * 8u;  // ldmatrix row this lane addresses
     const uint32_t lco = lane >> 4;                             // and which chunk of the pair
@@ -271,10 +281,10 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) sh[mt][i] = sl[mt][i] = 0.0f;
-        const uint32_t kTile = smemAddr(st + rowInTile * kHD);
+        const uint32_t kTile = smemAddr(st + rowInTile * 128);
 #pragma unroll
-        for (int cp = 0; cp < 4; ++cp) {
-            const uint32_t sw = ((2 * cp + lco) ^ (lr & 7u)) << 4;
+        for (int cp = 0; cp < NC / 2; ++cp) {
+            const uint32_t sw = (((2 * (cp & 3) + lco) ^ (lr & 7u)) << 4) + (cp >> 2) * L::kHalfBytes;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 uint32_t r0, r1, r2, r3;
@@ -341,7 +351,7 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             const float a0s = fastExp2(m0 - mn0), a1s = fastExp2(m1 - mn1);
             const float al0 = a0s * fE, al1 = a1s * fE;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < NC; ++i) {
                 o[i][0] *= al0;
                 o[i][1] *= al1;
                 o[i][2] *= al0;
@@ -377,11 +387,11 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 bl[mt][hf] = movmatrixTrans(lo);
             }
         }
-        // ---- O^T += V^T . P^T (128 dims x 8 heads), V bytes read transposed ----
-        const uint32_t vTile = smemAddr(st + L::kTileBytes + rowInTile * kHD);
+        // ---- O^T += V^T . P^T (HD dims x 8 heads), V bytes read transposed ----
+        const uint32_t vTile = smemAddr(st + L::kTileBytes + rowInTile * 128);
 #pragma unroll
-        for (int cp = 0; cp < 4; ++cp) {
-            const uint32_t sw = ((2 * cp + lco) ^ (lr & 7u)) << 4;
+        for (int cp = 0; cp < NC / 2; ++cp) {
+            const uint32_t sw = (((2 * (cp & 3) + lco) ^ (lr & 7u)) << 4) + (cp >> 2) * L::kHalfBytes;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 uint32_t r0, r1, r2, r3;
@@ -419,43 +429,44 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
     namedBarSync(1, NW * 32);  // every consumer is done reading the ring
     float *scr = reinterpret_cast<float *>(smem);
-    constexpr int kWarpScr = 8 * kHD + 16;
-    float *wO = scr + warp * kWarpScr;  // [8 heads][128], then m[8], l[8]
+    constexpr int kWarpScr = 8 * HD + 16;
+    float *wO = scr + warp * kWarpScr;  // [8 heads][HD], then m[8], l[8]
     {
         // true accumulator = 2^24 * raw - 128 * sum(p*sv), then back from the E-scaled domain
         const float E = __uint_as_float(Ebits);
         const float c0 = 128.0f * ps0, c1 = 128.0f * ps1;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < NC; ++c) {
             const int d = 16 * c + 2 * g;
-            *reinterpret_cast<float2 *>(wO + (2 * t) * kHD + d) =
+            *reinterpret_cast<float2 *>(wO + (2 * t) * HD + d) =
                     make_float2(fmaf(o[c][0], k2p24, -c0) * E, fmaf(o[c][2], k2p24, -c0) * E);
-            *reinterpret_cast<float2 *>(wO + (2 * t + 1) * kHD + d) =
+            *reinterpret_cast<float2 *>(wO + (2 * t + 1) * HD + d) =
                     make_float2(fmaf(o[c][1], k2p24, -c1) * E, fmaf(o[c][3], k2p24, -c1) * E);
         }
     }
     if (g == 0) {
-        wO[8 * kHD + 2 * t] = m0;
-        wO[8 * kHD + 2 * t + 1] = m1;
-        wO[8 * kHD + 8 + 2 * t] = l0;
-        wO[8 * kHD + 8 + 2 * t + 1] = l1;
+        wO[8 * HD + 2 * t] = m0;
+        wO[8 * HD + 2 * t + 1] = m1;
+        wO[8 * HD + 8 + 2 * t] = l0;
+        wO[8 * HD + 8 + 2 * t + 1] = l1;
     }
     namedBarSync(1, NW * 32);
-    // NW*32 threads, HPC*8*32 float4 outputs
-    for (uint32_t idx = threadIdx.x; idx < HPC * 8 * 32; idx += NW * 32) {
-        const uint32_t d4 = idx & 31u, j = (idx >> 5) & 7u, h = idx >> 8;
+    // NW*32 threads, HPC*8*(HD/4) float4 outputs
+    constexpr uint32_t V4 = HD / 4;
+    for (uint32_t idx = threadIdx.x; idx < HPC * 8 * V4; idx += NW * 32) {
+        const uint32_t d4 = idx % V4, j = (idx / V4) & 7u, h = idx / (8 * V4);
         if (!colValid(j)) continue;
         float M = kNegBig;
 #pragma unroll
-        for (int sb = 0; sb < NSUB; ++sb) M = fmaxf(M, scr[(sb * HPC + h) * kWarpScr + 8 * kHD + j]);
+        for (int sb = 0; sb < NSUB; ++sb) M = fmaxf(M, scr[(sb * HPC + h) * kWarpScr + 8 * HD + j]);
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         float lsum = 0.0f;
 #pragma unroll
         for (int sb = 0; sb < NSUB; ++sb) {
             const float *w = scr + (sb * HPC + h) * kWarpScr;
-            const float wgt = fastExp2(w[8 * kHD + j] - M);
-            lsum += wgt * w[8 * kHD + 8 + j];
-            const float4 a = *reinterpret_cast<const float4 *>(w + j * kHD + 4 * d4);
+            const float wgt = fastExp2(w[8 * HD + j] - M);
+            lsum += wgt * w[8 * HD + 8 + j];
+            const float4 a = *reinterpret_cast<const float4 *>(w + j * HD + 4 * d4);
             acc.x = fmaf(wgt, a.x, acc.x);
             acc.y = fmaf(wgt, a.y, acc.y);
             acc.z = fmaf(wgt, a.z, acc.z);
@@ -466,11 +477,11 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                                        : static_cast<size_t>(b) * p.nHeads + (kvHead0 + h) * p.group + j;
         if (p.directOut) {
             const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
-            *reinterpret_cast<float4 *>(p.out + oidx * kHD + 4 * d4) =
+            *reinterpret_cast<float4 *>(p.out + oidx * HD + 4 * d4) =
                     make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         } else {
             const size_t pidx = oidx * p.numChunks + chunk;
-            *reinterpret_cast<float4 *>(p.pAcc + pidx * kHD + 4 * d4) = acc;
+            *reinterpret_cast<float4 *>(p.pAcc + pidx * HD + 4 * d4) = acc;
             if (d4 == 0) {
                 // back to natural-log units: the merge contract is w = exp2((m - M) * log2e)
                 p.pM[pidx] = M > -1e29f ? M * 0.6931471805599453f : kNegBig;
@@ -480,12 +491,13 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
 }
 
-template <int HPC, int MT>
+template <int HD, int HPC, int MT>
 static int launchDecodeI8(const CUtensorMap &tmK, const CUtensorMap &tmV, const DecodeI8Params &prm,
                           const DecodePlan &pl, uint32_t batch, bool pdl, cudaStream_t st) {
-    constexpr int NW = 8, NSTAGE = MT == 2 ? 3 : 6;
-    using L = DecodeI8Smem<HPC, NW, NSTAGE, MT>;
-    auto kern = decodeI8Kernel<HPC, NW, NSTAGE, MT>;
+    constexpr int NW = 8, NSTAGE = (MT == 2 || HD == 256) ? 3 : 6;
+    using L = DecodeI8Smem<HD, HPC, NW, NSTAGE, MT>;
+    static_assert(L::kTotal <= 227 * 1024, "stage ring exceeds the shared memory of an SM");
+    auto kern = decodeI8Kernel<HD, HPC, NW, NSTAGE, MT>;
     static bool attrDone[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -509,7 +521,9 @@ static int launchDecodeI8(const CUtensorMap &tmK, const CUtensorMap &tmV, const 
 
 static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_t lenAdd, cudaStream_t st) {
     TC_REQUIRE(d->q && d->out && d->k8 && d->v8 && d->ks && d->vs, TC_EINVAL, "decode_i8: null pointer");
-    TC_REQUIRE(d->hd == kHD, TC_EUNSUPPORTED, "decode_i8: head_dim %u (built for 128)", d->hd);
+    TC_REQUIRE(d->hd == 128 || d->hd == 256, TC_EUNSUPPORTED, "decode_i8: head_dim %u (built for 128 and 256)",
+               d->hd);
+    const uint32_t hd = d->hd;
     TC_REQUIRE(d->nKV > 0 && d->nHeads % d->nKV == 0, TC_EINVAL, "decode_i8: nHeads %u not a multiple of nKV %u",
                d->nHeads, d->nKV);
     const uint32_t group = d->nHeads / d->nKV;
@@ -525,7 +539,8 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     // work quantum: 32 tokens per warp when every warp of the machine gets at least ~12
     // of them, 16 otherwise (see DecodeI8Smem)
     const uint64_t warpTiles32 = static_cast<uint64_t>(d->batch) * d->nKV * ((d->maxLen + 31) / 32);
-    const uint32_t mt = warpTiles32 >= 2ull * 8ull * static_cast<uint64_t>(numSMs()) ? 2u : 1u;
+    // (head_dim 256: a 32-token tile of K and V no longer leaves room for a second stage)
+    const uint32_t mt = hd == 128 && warpTiles32 >= 2ull * 8ull * static_cast<uint64_t>(numSMs()) ? 2u : 1u;
     const DecodePlan pl = planDecode(d->batch, d->nKV, d->maxLen, d->numChunks, 8u * 16u * mt);
     const bool pdl = (d->flags & TC_DECODE_PDL) != 0;
     const bool direct = pl.chunksPerSeq == 1 && !d->partialsOnly;
@@ -538,12 +553,12 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     key.rank = 3;
     key.elemBytes = 1;
     key.swizzle = 3;
-    key.dims[0] = kHD;
+    key.dims[0] = hd;
     key.dims[1] = d->nKV;
     key.dims[2] = d->totalRows;
-    key.strides[0] = kHD;
-    key.strides[1] = static_cast<uint64_t>(d->nKV) * kHD;
-    key.box[0] = kHD;
+    key.strides[0] = hd;
+    key.strides[1] = static_cast<uint64_t>(d->nKV) * hd;
+    key.box[0] = 128;  // one swizzle span; a 256-dim row is fetched as two boxes
     key.box[1] = 1;
     key.box[2] = pl.tileTokens;
     CUtensorMap tmK, tmV;
@@ -583,20 +598,24 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     prm.err = devErrorWord();
     TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "decode_i8: no device error word");
 
-    if (mt == 2) {
-        if (pl.hpc == 4) rc = launchDecodeI8<4, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
-        else if (pl.hpc == 2) rc = launchDecodeI8<2, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
-        else rc = launchDecodeI8<1, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
+    if (hd == 256) {
+        if (pl.hpc == 4) rc = launchDecodeI8<256, 4, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        else if (pl.hpc == 2) rc = launchDecodeI8<256, 2, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        else rc = launchDecodeI8<256, 1, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+    } else if (mt == 2) {
+        if (pl.hpc == 4) rc = launchDecodeI8<128, 4, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        else if (pl.hpc == 2) rc = launchDecodeI8<128, 2, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        else rc = launchDecodeI8<128, 1, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
     } else {
-        if (pl.hpc == 4) rc = launchDecodeI8<4, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-        else if (pl.hpc == 2) rc = launchDecodeI8<2, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-        else rc = launchDecodeI8<1, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        if (pl.hpc == 4) rc = launchDecodeI8<128, 4, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        else if (pl.hpc == 2) rc = launchDecodeI8<128, 2, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        else rc = launchDecodeI8<128, 1, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
     }
     if (rc != TC_OK) return rc;
     if (direct || d->partialsOnly) return TC_OK;
     // merge: the active chunk count of a sequence follows from its length (read on
     // the device when the length lives there); slots past it were never written.
-    return launchMerge(d->pAcc, d->pM, d->pL, d->out, d->batch, d->nHeads, d->numChunks, pl.chunksPerSeq, kHD,
+    return launchMerge(d->pAcc, d->pM, d->pL, d->out, d->batch, d->nHeads, d->numChunks, pl.chunksPerSeq, hd,
                        d->lens, lenAdd, pl.chunkTokens, nullptr, pdl, st);
 }
 
@@ -605,7 +624,7 @@ static int prefillI8(const float *q, const int8_t *k8, const int8_t *v8, const f
                      float *out, uint32_t seqLen, uint32_t nHeads, uint32_t nKV, uint32_t hd, uint32_t cachePos,
                      const uint32_t *devPos, uint64_t totalRows, float invSqrt, cudaStream_t st) {
     TC_REQUIRE(q && k8 && v8 && ks && vs && out, TC_EINVAL, "prefill_i8: null pointer");
-    TC_REQUIRE(hd == kHD, TC_EUNSUPPORTED, "prefill_i8: head_dim %u (built for 128)", hd);
+    TC_REQUIRE(hd == 128 || hd == 256, TC_EUNSUPPORTED, "prefill_i8: head_dim %u (built for 128 and 256)", hd);
     TC_REQUIRE(nKV > 0 && nHeads % nKV == 0, TC_EINVAL, "prefill_i8: nHeads %u not a multiple of nKV %u", nHeads,
                nKV);
     TC_REQUIRE(totalRows >= 1 && totalRows < (1ull << 31), TC_EUNSUPPORTED, "prefill_i8: pool of %llu rows",
@@ -622,21 +641,21 @@ static int prefillI8(const float *q, const int8_t *k8, const int8_t *v8, const f
     const uint32_t rowBlocks = (seqLen + 7) / 8;
     TC_REQUIRE(rowBlocks <= 65535 && nHeads <= 65535, TC_EUNSUPPORTED, "prefill_i8: %u rows x %u heads", seqLen,
                nHeads);
-    constexpr int NW = 8, MT = 2, NSTAGE = 3;
-    using L = DecodeI8Smem<1, NW, NSTAGE, MT>;
+    // tokens per stage: 8 warps x 32 rows (head_dim 128) or x 16 rows (head_dim 256)
+    const uint32_t tileTokens = hd == 256 ? 128u : 256u;
     TensorMapKey key;
     memset(&key, 0, sizeof(key));
     key.rank = 3;
     key.elemBytes = 1;
     key.swizzle = 3;
-    key.dims[0] = kHD;
+    key.dims[0] = hd;
     key.dims[1] = nKV;
     key.dims[2] = totalRows;
-    key.strides[0] = kHD;
-    key.strides[1] = static_cast<uint64_t>(nKV) * kHD;
-    key.box[0] = kHD;
+    key.strides[0] = hd;
+    key.strides[1] = static_cast<uint64_t>(nKV) * hd;
+    key.box[0] = 128;
     key.box[1] = 1;
-    key.box[2] = L::T;
+    key.box[2] = tileTokens;
     CUtensorMap tmK, tmV;
     key.base = k8;
     int rc = getTensorMap(key, &tmK);
@@ -669,10 +688,11 @@ static int prefillI8(const float *q, const int8_t *k8, const int8_t *v8, const f
     pl.headGroups = nHeads;
     pl.chunksPerSeq = 1;
     pl.chunkTokens = prm.chunkTokens;
-    pl.tileTokens = L::T;
+    pl.tileTokens = tileTokens;
     // heaviest row blocks first would need a reversed grid; the hardware scheduler
     // hands out blocks in z-major order, so late (long) blocks start last -- acceptable here
-    return launchDecodeI8<1, MT>(tmK, tmV, prm, pl, rowBlocks, false, st);
+    if (hd == 256) return launchDecodeI8<256, 1, 1>(tmK, tmV, prm, pl, rowBlocks, false, st);
+    return launchDecodeI8<128, 1, 2>(tmK, tmV, prm, pl, rowBlocks, false, st);
 }
 
 }  // namespace tc
