@@ -81,6 +81,8 @@ struct DecodeI8Smem {
 // How far the running reference point of the softmax may lag behind the true
 // maximum (log2 units) before the accumulators are rescaled.  p stays <= 2^8.
 constexpr float kLazyLog2 = 8.0f;
+// Stages a producer may request before the grids it depends on have completed.
+constexpr uint32_t kEarlyStages = 1;
 
 template <int HD, int HPC, int NW, int NSTAGE, int MT>
 __global__ void __launch_bounds__((NW + 1) * 32, 1)
@@ -146,8 +148,11 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 if (!mbarWaitClock(&emptyBar[s], ((it / NSTAGE) - 1) & 1, p.err, kDevErrEmptyWait)) break;
             }
             const uint32_t tok = t0 + it * T;
-            if (!waited && tok + T > p.prefetchRows) {
-                // this tile may hold rows appended by the kernel we depend on
+            if (!waited && (tok + T > p.prefetchRows || it >= kEarlyStages)) {
+                // this tile may hold rows appended by the kernel we depend on -- or it is not
+                // the first one: the kernels ahead (the merge above all) are short and
+                // latency-bound, and a deeper prefetch would put a whole ring of KV loads
+                // in front of theirs in the memory system
                 gridDepWait();
                 waited = true;
             }

@@ -37,12 +37,17 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
     // gathered from several ranks -- rank c / chunksPerRank, whose block (rankStride floats
     // further on in each of the three arrays) holds [token][head][chunksPerRank].
     const uint64_t headRow = static_cast<uint64_t>(s) * nHeads + head;
+    // (the plain layout takes the branch without the divisions: they would sit in front of
+    // every load of a kernel whose whole cost is latency)
     auto mlOff = [&](uint32_t c) -> uint64_t {
-        return static_cast<uint64_t>(c / chunksPerRank) * rankStride + headRow * chunksPerRank + c % chunksPerRank;
+        if (rankStride == 0) return headRow * numChunks + c;
+        const uint32_t r = c / chunksPerRank;
+        return static_cast<uint64_t>(r) * rankStride + headRow * chunksPerRank + (c - r * chunksPerRank);
     };
     auto accOff = [&](uint32_t c) -> uint64_t {
-        return static_cast<uint64_t>(c / chunksPerRank) * rankStride +
-               (headRow * chunksPerRank + c % chunksPerRank) * hd;
+        if (rankStride == 0) return (headRow * numChunks + c) * hd;
+        const uint32_t r = c / chunksPerRank;
+        return static_cast<uint64_t>(r) * rankStride + (headRow * chunksPerRank + (c - r * chunksPerRank)) * hd;
     };
     // under programmatic dependent launch: let the next grid start its prologue, then
     // wait until the grid that wrote the partials has finished (a no-op otherwise)
