@@ -9,7 +9,8 @@ L2: no layer's KV survives in cache until the next step).  Metric: algorithmic K
 bytes (int8 rows + f32 scales, read once) per second.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
-                    [--workload decode32k|decode8k_b8|c4_32b_128k|ragged64|prefill4k]
+                    [--workload decode32k|decode32k_b8|decode8k_b8|decode8k_b1|c4_32b_128k|c4_heads|
+                                c4_ctxsplit|ragged64|prefill4k]
 
 N > 1 (torchrun): every rank runs the same per-GPU workload on its own sequences
 (sharding by sequence, no data-path collective) -- weak scaling; the time is the
@@ -39,6 +40,7 @@ WORKLOADS = {
     "decode32k": (28, 4, 128, 32768, 1, 28),
     "decode8k_b8": (28, 4, 128, 8192, 8, 28),
     "decode8k_b1": (28, 4, 128, 8192, 1, 28),
+    "decode32k_b8": (28, 4, 128, 32768, 8, 8),   # 8 of the 28 layers resident (8 x 277 MB)
     "c4_32b_128k": (40, 8, 128, 131072, 1, 8),  # 8 of the 64 layers resident (64 x 277 MB pools are cycled per 8)
 }
 
@@ -375,6 +377,174 @@ def run_prefill(args):
         dist.destroy_process_group()
 
 
+def quick_decode(name, dev, steps=20, warmup=5):
+    """Device-resident decode measurement of one workload (graph + dependent launch), for
+    the secondary figures of the default line."""
+    import torch
+
+    from tinycoder_inference_b200 import ops
+
+    nH, nKV, hd, ctx, batch, layers = WORKLOADS[name]
+    inv = 1.0 / math.sqrt(hd)
+    rows = ctx + 16
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x7C0DE012)
+    k8 = torch.empty((layers, batch, rows, nKV, hd), dtype=torch.int8, device=dev)
+    v8 = torch.empty_like(k8)
+    ks = torch.zeros((layers, batch, rows, nKV), device=dev)
+    vs = torch.zeros_like(ks)
+    for l in range(layers):
+        for b in range(batch):
+            kf = torch.randn((ctx, nKV, hd), generator=g, device=dev)
+            vf = torch.randn((ctx, nKV, hd), generator=g, device=dev)
+            ops.kv_quantize_i8(kf, vf, k8[l, b], v8[l, b], ks[l, b], vs[l, b], ctx, nKV, hd)
+    q = torch.randn((layers, batch, nH, hd), generator=g, device=dev)
+    out = torch.empty_like(q)
+    _, chunks = ops.split_geometry(ctx, nH, hd)
+    ws = ops.workspace(batch, nH, hd, chunks)
+
+    def step():
+        for l in range(layers):
+            ops.decode_i8_batch(q[l], k8[l], v8[l], ks[l], vs[l], out[l], ws, None, batch, nH, nKV, hd, ctx, chunks,
+                                rows_per_seq=rows, invSqrt=inv, pdl=True, prefetch_rows=ctx - 1)
+
+    step()
+    torch.cuda.synchronize()
+    s_ = torch.cuda.Stream()
+    s_.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s_):
+        step()
+    torch.cuda.current_stream().wait_stream(s_)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        step()
+    for _ in range(warmup):
+        gr.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        gr.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    gbs = layers * batch * algorithmic_bytes(nKV, hd, ctx) / (ms * 1e-3) / 1e9
+    pk = peaks()
+    return {"workload": workload_config(name, 1)["workload"], "us_per_layer": ms * 1e3 / layers, "value": gbs,
+            "unit": "GB/s", "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "steps": steps, "warmup": warmup}
+
+
+def run_ragged(args):
+    """Batched decode serving mix: 64 sequences with context lengths drawn uniformly from
+    [512, 32768] by seed (28 q heads, 4 kv heads, head_dim 128, int8 KV), one decode step =
+    28 layers.  The 64 sequences are dealt to the ranks so that the TOKEN counts balance
+    (longest first onto the lightest rank) -- strong scaling, no collective.  Every rank keeps
+    4 layer pools of its sequences resident and cycles them 7 times per step."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from tinycoder_inference_b200 import ops, sharding
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    nH, nKV, hd, nseq, layers, resident = 28, 4, 128, 64, 28, 4
+    inv = 1.0 / math.sqrt(hd)
+    rng = np.random.Generator(np.random.Philox(key=[0x7C0DE005, 0]))
+    lens_all = (512 + rng.integers(0, 32257, nseq, dtype=np.uint64)).astype(np.int64)   # 512 + (u64 mod 32257)
+    mine = sharding.plan_sequence_shards(lens_all.tolist(), world)[rank]
+    lens = lens_all[mine]
+    B = len(mine)
+    base = np.zeros(B, dtype=np.uint64)
+    base[1:] = np.cumsum(lens[:-1] + 16)      # 16 rows of slack behind every sequence
+    rows = int((lens + 16).sum())
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x7C0DE005 + rank)
+    k8 = torch.empty((resident, rows, nKV, hd), dtype=torch.int8, device=dev)
+    v8 = torch.empty_like(k8)
+    ks = torch.zeros((resident, rows, nKV), device=dev)
+    vs = torch.zeros_like(ks)
+    blk = 32768
+    for l in range(resident):
+        for r0 in range(0, rows, blk):
+            n = min(blk, rows - r0)
+            kf = torch.randn((n, nKV, hd), generator=g, device=dev)
+            vf = torch.randn((n, nKV, hd), generator=g, device=dev)
+            ops.kv_quantize_i8(kf, vf, k8[l], v8[l], ks[l], vs[l], n, nKV, hd, dst_base=r0)
+    q = torch.randn((resident, B, nH, hd), generator=g, device=dev)
+    out = torch.empty_like(q)
+    dlens = torch.tensor(lens, dtype=torch.int32, device=dev)
+    dbase = torch.tensor(base.astype(np.int64), dtype=torch.int64, device=dev)
+    maxlen = int(lens.max())
+    _, chunks = ops.split_geometry(maxlen, nH, hd)
+    chunks = min(chunks, 64)
+    ws = ops.workspace(B, nH, hd, chunks)
+
+    def step():
+        for l in range(layers):
+            r = l % resident
+            ops.decode_i8_batch(q[r], k8[r], v8[r], ks[r], vs[r], out[r], ws, dlens, B, nH, nKV, hd, maxlen, chunks,
+                                row_base=dbase, invSqrt=inv, pdl=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    step()
+    torch.cuda.synchronize()
+    s_ = torch.cuda.Stream()
+    s_.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s_):
+        step()
+    torch.cuda.current_stream().wait_stream(s_)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        step()
+    for _ in range(args.warmup):
+        gr.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        gr.replay()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    flags = ops.device_status()
+    if rank == 0:
+        tokens = int(lens_all.sum())
+        total_bytes = layers * algorithmic_bytes(nKV, hd, tokens)
+        val = total_bytes / (ms_per_step * 1e-3) / 1e9
+        pk = peaks()
+        line = {
+            "metric": "decode_attn_kv_gbs_ragged64", "value": val, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "us_per_layer": ms_per_step * 1e3 / layers, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8 KV, f32 q/out", "data": "synthetic",
+            "config": {"workload": f"ragged64: {nseq} sequences, context lengths uniform in [512, 32768] by seed "
+                                   f"({tokens} tokens), {nH} q heads / {nKV} kv heads / head_dim {hd}, int8 KV, "
+                                   f"{layers} layers per step ({resident} resident pools cycled)",
+                       "sharding": "whole sequences dealt to ranks by token count (longest first), no collective",
+                       "rank0_sequences": B, "l2": "inputs larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": val / world, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": val / world / pk["hbm_gbs"], "peak_source": pk["source"], "traffic": None,
+                         "note": "per-GPU share of the algorithmic bytes over the step time"},
+            "gpu_launches": args.steps * layers * 2, "device_error_flags": flags,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_sharded(args):
     """Qwen2.5-32B-shaped long-context decode (40 q heads, 8 kv heads, head_dim 128, ctx
     131072, int8 KV), ONE sequence split over the ranks -- strong scaling:
@@ -487,8 +657,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode32k", choices=sorted(WORKLOADS) + ["prefill4k", "c4_heads", "c4_ctxsplit"])
+    ap.add_argument("--workload", default="decode32k", choices=sorted(WORKLOADS) + ["prefill4k", "c4_heads", "c4_ctxsplit", "ragged64"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary batch-8 measurement of the default line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream order between the kernels of a step")
     ap.add_argument("--partials-only", action="store_true", help="diagnostic: skip the merge launch")
@@ -502,6 +673,9 @@ def main():
         return
     if args.workload in ("c4_heads", "c4_ctxsplit"):
         run_sharded(args)
+        return
+    if args.workload == "ragged64":
+        run_ragged(args)
         return
 
     import torch
@@ -679,6 +853,12 @@ def main():
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks, "device_error_flags": dev_flags,
     }
+    if world == 1 and args.workload == "decode32k" and not args.no_extras:
+        # the same shape and context with 8 sequences in the batch: enough rows in flight to be
+        # bandwidth-bound rather than latency-bound
+        del k8, v8, ks, vs
+        torch.cuda.empty_cache()
+        line["also"] = [quick_decode("decode32k_b8", dev)]
     if not args.no_cpu_baseline and world == 1:
         per_layer, cores, kind, sample = cpu_attention_sample(nH, nKV, hd, ctx)
         line["cpu_baseline"] = {"value": algorithmic_bytes(nKV, hd, ctx) / per_layer / 1e9, "unit": "GB/s",
