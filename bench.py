@@ -598,15 +598,41 @@ def run_sharded(args):
     chunk, chunks = ops.split_geometry(ctx, nH, hd)
     chunks = min(chunks, 128)
     ws = ops.workspace(1, my_q, hd, chunks)
-    splitter = sharding.ContextSplitDecoder(my_q, my_kv, hd, my_rows, chunk_slots=64) if by_ctx else None
+    splitter = sharding.ContextSplitDecoder(my_q, my_kv, hd, my_rows, chunk_slots=64,
+                                            exchange=args.exchange) if by_ctx else None
+    if by_ctx and world > 1 and args.exchange == "p2p":
+        # the library's own exchange must agree with the NCCL all-gather path before anything is timed
+        chk = sharding.ContextSplitDecoder(my_q, my_kv, hd, my_rows, chunk_slots=64, exchange="nccl")
+        o1, o2 = torch.empty_like(out[0]), torch.empty_like(out[0])
+        splitter(q[0], k8[0], v8[0], ks[0], vs[0], o1, my_rows, invSqrt=inv)
+        chk(q[0], k8[0], v8[0], ks[0], vs[0], o2, my_rows, invSqrt=inv)
+        torch.cuda.synchronize()
+        if not torch.allclose(o1, o2, rtol=1e-4, atol=1e-6):
+            raise SystemExit("context split: the two exchange paths disagree")
+        del chk
 
-    def step():
+    def step_plain():
         for l in range(layers):
             if by_ctx:
-                splitter(q[l], k8[l], v8[l], ks[l], vs[l], out[l], my_rows, invSqrt=inv)
+                splitter(q[l], k8[l], v8[l], ks[l], vs[l], out[l], my_rows, invSqrt=inv, pdl=True)
             else:
                 ops.decode_i8_batch(q[l], k8[l], v8[l], ks[l], vs[l], out[l], ws, None, 1, my_q, my_kv, hd, my_rows,
                                     chunks, invSqrt=inv, pdl=True, prefetch_rows=my_rows - 1)
+
+    step_plain()
+    torch.cuda.synchronize()
+    if args.no_graph or (by_ctx and args.exchange == "nccl"):
+        step = step_plain      # (the NCCL path is timed as plain launches)
+    else:
+        s_ = torch.cuda.Stream()
+        s_.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s_):
+            step_plain()
+        torch.cuda.current_stream().wait_stream(s_)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            step_plain()
+        step = gr.replay
 
     def barrier():
         if world > 1:
@@ -638,8 +664,14 @@ def run_sharded(args):
             "vs_baseline": None, "dtype": "int8 KV, f32 q/out", "data": "synthetic",
             "config": {"workload": f"{args.workload}: 40 q heads / 8 kv heads / head_dim 128, int8 KV, one sequence of "
                                    f"{ctx} rows, {layers} layers per step",
-                       "sharding": ("context axis: ctx/N rows per rank, partials all-gathered over NCCL and merged"
+                       "sharding": (("context axis: ctx/N rows per rank; "
+                                     + ("each rank's merged partial is stored into every peer over NVLink and merged "
+                                        "there, one kernel per rank (no collective library call)"
+                                        if args.exchange == "p2p" else
+                                        "partials all-gathered over NCCL and merged"))
                                     if by_ctx else "kv-head groups: nKV/N heads per rank, no data-path collective"),
+                       "launch": "plain launches" if args.no_graph or (by_ctx and args.exchange == "nccl")
+                                 else "cuda_graph",
                        "l2": "inputs larger than L2"},
             "roofline": {"bound": "hbm", "achieved": val / world, "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": val / world / pk["hbm_gbs"], "peak_source": pk["source"], "traffic": None,
@@ -658,6 +690,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode32k", choices=sorted(WORKLOADS) + ["prefill4k", "c4_heads", "c4_ctxsplit", "ragged64"])
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="c4_ctxsplit: partials exchanged by the library's own kernel over peer memory, or by NCCL")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary batch-8 measurement of the default line")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -231,6 +231,39 @@ int tc_attn_merge_gathered(const float *gathered, float *out, uint32_t nHeads,
                            uint32_t ranks, uint32_t chunksPerRank, uint32_t hd,
                            tc_stream stream);
 
+/* The same merge with the exchange inside the kernel (no collective library call).
+ * Every rank owns an exchange buffer of tc_attn_exchange_bytes() bytes that all ranks
+ * can store into (peer-mapped device memory: CUDA IPC, a symmetric-memory allocation,
+ * or plain device memory when all "ranks" share a GPU), zeroed once before first use;
+ * buffers[r] is rank r's buffer as addressed from the calling rank.  One launch per
+ * rank and step: it merges the rank's own chunk partials (layout [nHeads][numChunks],
+ * the first activeChunks slots written) into one partial per head, stores it into
+ * every rank's buffer, waits -- at most about a second, after which
+ * tc_device_status reports it -- for the partials of all ranks and writes out
+ * [nHeads][hd].  Every rank must issue the same sequence of calls on its buffer.
+ * flags & TC_DECODE_PDL as for tc_attn_decode_i8_batch. */
+typedef struct tc_peer_group {
+    void *buffers[16];
+    uint32_t world, rank;
+} tc_peer_group;
+
+int tc_attn_exchange_bytes(uint32_t nHeads, uint32_t hd, uint32_t world, size_t *bytes);
+
+int tc_attn_merge_exchange(const float *pAcc, const float *pM, const float *pL, float *out,
+                           uint32_t nHeads, uint32_t numChunks, uint32_t activeChunks,
+                           uint32_t hd, const tc_peer_group *g, uint32_t flags,
+                           tc_stream stream);
+
+/* All `ranks` of the protocol in ONE cooperative launch on one GPU (arrays of `ranks`
+ * host pointers): for hosts that keep several context shards on one device, and for
+ * testing the protocol without a second GPU.  Blocks of the launch wait for one
+ * another, hence cooperative: the call fails if the grid cannot be resident at once. */
+int tc_attn_merge_exchange_local(const float *const *pAcc, const float *const *pM,
+                                 const float *const *pL, float *const *out,
+                                 void *const *buffers, uint32_t ranks, uint32_t nHeads,
+                                 uint32_t numChunks, uint32_t activeChunks, uint32_t hd,
+                                 tc_stream stream);
+
 /* ------------------------------------------------------------------------- */
 /* prefill attention                                                           */
 /* ------------------------------------------------------------------------- */

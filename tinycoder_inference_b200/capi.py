@@ -94,6 +94,10 @@ class KvPoolGeometry(C.Structure):
     ]
 
 
+class PeerGroup(C.Structure):
+    _fields_ = [("buffers", C.c_void_p * 16), ("world", C.c_uint32), ("rank", C.c_uint32)]
+
+
 class DecodeI8Batch(C.Structure):
     _fields_ = [
         ("q", C.c_void_p),
@@ -145,6 +149,10 @@ SIGNATURES = {
                                _u32, _f, _i, _vp, _vp]),
     "tc_attn_merge_partials": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "tc_attn_merge_gathered": (_i, [_vp, _vp, _u32, _u32, _u32, _u32, _vp]),
+    "tc_attn_exchange_bytes": (_i, [_u32, _u32, _u32, _sz_p]),
+    "tc_attn_merge_exchange": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, C.POINTER(PeerGroup), _u32, _vp]),
+    "tc_attn_merge_exchange_local": (_i, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
+                                          C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _vp]),
     "tc_attn_prefill_f16_scratch_bytes": (_i, [_u32, _u32, _u32, _u32, _sz_p]),
     "tc_attn_prefill_f16": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_size_t, _u32, _u32, _u32, _u32, _f, _vp]),
     "tc_attn_prefill_kv": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _u64, _f, _i, _vp]),

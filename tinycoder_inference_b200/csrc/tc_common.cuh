@@ -22,6 +22,7 @@ enum : uint32_t {
     kDevErrEmptyWait = 2u,  // producer waited too long for a free stage
     kDevErrMmaWait = 4u,    // waited too long for a tcgen05 commit
     kDevErrTmemAlloc = 8u,
+    kDevErrMergeWait = 16u,  // a block waited too long for the partials of another rank
 };
 // The word lives in one translation unit; kernels receive its device address as
 // an argument (devErrorWord(), resolved once per device).

@@ -150,6 +150,33 @@ def merge_gathered(gathered, out, nHeads, ranks, chunksPerRank, hd):
     check(lib.tc_attn_merge_gathered(_ptr(gathered), _ptr(out), nHeads, ranks, chunksPerRank, hd, _stream()))
 
 
+def exchange_bytes(nHeads, hd, world):
+    n = C.c_size_t(0)
+    check(lib.tc_attn_exchange_bytes(nHeads, hd, world, C.byref(n)))
+    return n.value
+
+
+def merge_exchange(ws, out, nHeads, numChunks, activeChunks, hd, buffer_ptrs, rank, pdl=False):
+    """Merge this rank's chunk partials, exchange with the peers inside the kernel, write out.
+    buffer_ptrs: device addresses of every rank's exchange buffer as seen from this rank."""
+    g = capi.PeerGroup()
+    for r, ptr in enumerate(buffer_ptrs):
+        g.buffers[r] = ptr
+    g.world, g.rank = len(buffer_ptrs), rank
+    pAcc, pM, pL = ws
+    check(lib.tc_attn_merge_exchange(_ptr(pAcc), _ptr(pM), _ptr(pL), _ptr(out), nHeads, numChunks, activeChunks, hd,
+                                     C.byref(g), capi.TC_DECODE_PDL if pdl else 0, _stream()))
+
+
+def merge_exchange_local(wss, outs, buffers, nHeads, numChunks, activeChunks, hd):
+    """All ranks of the exchange protocol in one cooperative launch on this GPU."""
+    n = len(wss)
+    arr = lambda ts: (C.c_void_p * n)(*[t.data_ptr() for t in ts])  # noqa: E731
+    check(lib.tc_attn_merge_exchange_local(arr([w[0] for w in wss]), arr([w[1] for w in wss]),
+                                           arr([w[2] for w in wss]), arr(outs), arr(buffers), n, nHeads, numChunks,
+                                           activeChunks, hd, _stream()))
+
+
 # ---- prefill ------------------------------------------------------------------
 
 def prefill_f16_scratch_bytes(seqLen, nHeads, nKV, hd) -> int:

@@ -118,37 +118,68 @@ def gather_partials(acc, m, l, group=None):
 
 class ContextSplitDecoder:
     """One decode token attended over a context that is split by rows across the ranks of
-    `group`.  Every rank holds rows [0, local_len) of ITS range in its own pool, runs the
-    split-KV kernel in partials-only form into one contiguous block [acc | m | l], the blocks
-    are all-gathered (one NCCL call, a few tens of KB) and merged on every rank.
+    `group`.  Every rank holds rows [0, local_len) of ITS range in its own pool and runs the
+    split-KV kernel in partials-only form; then
 
-    Buffers are allocated once; a step is three enqueues (decode, all-gather, merge) and can be
-    captured in a CUDA graph."""
+    * exchange="p2p" (default when symmetric memory can be set up): one launch of the
+      exchange-merge kernel per rank -- it merges the rank's chunks, stores the result into
+      every peer's buffer over NVLink and merges what the peers stored here;
+    * exchange="nccl": the rank's [acc | m | l] block is all-gathered and merged by
+      tc_attn_merge_gathered.
 
-    def __init__(self, nHeads, nKV, hd, max_local_len, group=None, chunk_slots=16):
+    Buffers are allocated once; a step is two or three enqueues and can be captured in a
+    CUDA graph."""
+
+    def __init__(self, nHeads, nKV, hd, max_local_len, group=None, chunk_slots=64, exchange="p2p"):
         import torch
         import torch.distributed as dist
 
+        from . import ops
+
         self.nH, self.nKV, self.hd, self.group = nHeads, nKV, hd, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.C = chunk_slots
         ml = nHeads * self.C
         self.block = torch.zeros(ml * hd + 2 * ml, dtype=torch.float32, device="cuda")
         self.acc = self.block[:ml * hd]
         self.m = self.block[ml * hd:ml * hd + ml]
         self.l = self.block[ml * hd + ml:]
-        self.gathered = torch.zeros(self.world * self.block.numel(), dtype=torch.float32, device="cuda")
         self.max_local_len = max_local_len
+        self.exchange = exchange
+        if exchange == "p2p":
+            words = ops.exchange_bytes(nHeads, hd, self.world) // 4
+            if self.world > 1:
+                import torch.distributed._symmetric_memory as symm
 
-    def __call__(self, q, k8, v8, ks, vs, out, local_len, invSqrt=None):
+                self.xbuf = symm.empty(words, dtype=torch.float32, device=torch.device("cuda", torch.cuda.current_device()))
+                self.xbuf.zero_()
+                self.handle = symm.rendezvous(self.xbuf, group if group is not None else dist.group.WORLD)
+                self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+                torch.cuda.synchronize()
+                dist.barrier(group)
+            else:
+                self.xbuf = torch.zeros(words, dtype=torch.float32, device="cuda")
+                self.ptrs = [self.xbuf.data_ptr()]
+        else:
+            self.gathered = torch.zeros(self.world * self.block.numel(), dtype=torch.float32, device="cuda")
+
+    def __call__(self, q, k8, v8, ks, vs, out, local_len, invSqrt=None, pdl=False):
         import torch.distributed as dist
 
         from . import ops
 
-        self.l.zero_()   # chunk slots this rank does not write must read as empty
+        used = 0
+        if self.exchange != "p2p":
+            self.l.zero_()   # chunk slots this rank does not write must read as empty
         if local_len > 0:
-            ops.decode_i8_batch(q, k8, v8, ks, vs, out, (self.acc, self.m, self.l), None, 1, self.nH, self.nKV,
-                                self.hd, local_len, self.C, invSqrt=invSqrt, partials_only=True)
+            used = ops.decode_i8_batch(q, k8, v8, ks, vs, out, (self.acc, self.m, self.l), None, 1, self.nH,
+                                       self.nKV, self.hd, local_len, self.C, invSqrt=invSqrt, partials_only=True,
+                                       pdl=pdl, prefetch_rows=local_len - 1 if pdl else 0)
+        if self.exchange == "p2p":
+            ops.merge_exchange((self.acc, self.m, self.l), out, self.nH, self.C, used, self.hd, self.ptrs, self.rank,
+                               pdl=pdl)
+            return
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered, self.block, group=self.group)
             src = self.gathered
