@@ -77,12 +77,73 @@ def test_cpu_engine_path_agrees():
         assert_close(got, ref, what="GPU kernel vs reference leaves + pool")
 
 
-def test_fp16_cache_is_reported_unsupported():
-    q = torch.zeros((1, 14, 64), device="cuda")
-    k = torch.zeros((8, 2, 64), dtype=torch.float16, device="cuda")
-    with pytest.raises(capi.TcError) as e:
-        ops.decode_kv(q, k, k, q.clone(), ops.workspace(1, 14, 64, 4), 1, 14, 2, 64, 3, 4)
-    assert e.value.code == capi.TC_EUNSUPPORTED
+@pytest.mark.parametrize("nH,nKV,hd,ctx,numChunks", [(14, 2, 64, 2048, 64), (14, 2, 64, 1, 64), (14, 2, 64, 17, 64),
+                                                    (28, 4, 128, 1000, 128), (40, 8, 128, 5000, 32),
+                                                    (12, 2, 128, 129, 1), (7, 1, 64, 300, 16), (8, 8, 64, 63, 8)])
+def test_fp16_cache_decode(nH, nKV, hd, ctx, numChunks):
+    """The dense models' optional fp16 cache (KVT = __half in the reference): same rule, the
+    products see float(k), float(v).  Rows behind the position hold NaN."""
+    rng = np.random.default_rng(ctx * 3 + nH)
+    pad = 40
+    q = rng.standard_normal((1, nH, hd), dtype=np.float32)
+    k = rng.standard_normal((ctx + pad, nKV, hd), dtype=np.float32).astype(np.float16)
+    v = (rng.standard_normal((ctx + pad, nKV, hd), dtype=np.float32) * 3).astype(np.float16)
+    k[ctx:] = np.nan
+    v[ctx:] = np.nan
+    inv = 1.0 / math.sqrt(hd)
+    want = oracle.attention_kv(q, k[:ctx], v[:ctx], 1, nH, nKV, hd, ctx - 1, inv)
+    out = torch.full((1, nH, hd), float("nan"), device="cuda")
+    ws = ops.workspace(1, nH, hd, numChunks)
+    for w in ws:
+        w.fill_(float("nan"))
+    ops.decode_kv(dev(q), dev(k), dev(v), out, ws, 1, nH, nKV, hd, ctx - 1, numChunks, invSqrt=inv)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(host(out), want, what=f"fp16 cache decode {nH}/{nKV}/{hd} ctx {ctx}")
+    # device position (host value = upper bound) and the Q8_1 epilogue
+    pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda")
+    blocks = torch.zeros(nH * (hd // 32) * 40, dtype=torch.uint8, device="cuda")
+    out2 = torch.full((1, nH, hd), float("nan"), device="cuda")
+    ops.decode_kv(dev(q), dev(k), dev(v), out2, ws, 1, nH, nKV, hd, ctx - 1 + pad, numChunks, invSqrt=inv, dev_pos=pos,
+                  q81=blocks)
+    torch.cuda.synchronize()
+    assert_close(host(out2), want, what="fp16 cache decode, device position")
+    assert np.array_equal(host(blocks), oracle.q8_1_blocks(host(out2)))
+
+
+@pytest.mark.parametrize("S,nH,nKV,hd,cachePos", [(37, 14, 2, 64, 0), (8, 28, 4, 128, 100), (129, 12, 2, 128, 17)])
+def test_fp16_cache_causal_rows(S, nH, nKV, hd, cachePos):
+    rng = np.random.default_rng(S + cachePos + 1)
+    rows = cachePos + S
+    q = rng.standard_normal((S, nH, hd), dtype=np.float32)
+    k = rng.standard_normal((rows + 5, nKV, hd), dtype=np.float32).astype(np.float16)
+    v = rng.standard_normal((rows + 5, nKV, hd), dtype=np.float32).astype(np.float16)
+    k[rows:] = np.nan
+    v[rows:] = np.nan
+    inv = 1.0 / math.sqrt(hd)
+    want = oracle.attention_kv(q, k, v, S, nH, nKV, hd, cachePos, inv)
+    out = torch.full((S, nH, hd), float("nan"), device="cuda")
+    ops.prefill_kv(dev(q), dev(k), dev(v), out, S, nH, nKV, hd, cachePos, invSqrt=inv)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(host(out), want, what="fp16 cache causal rows")
+
+
+def test_append_then_attend_fp16_cache():
+    """tc_kv_append into an fp16 cache, then decode over it: the pair the dense engine runs per token."""
+    nH, nKV, hd, ctx = 14, 2, 64, 300
+    rng = np.random.default_rng(8)
+    kf = rng.standard_normal((ctx, nKV, hd), dtype=np.float32)
+    vf = rng.standard_normal((ctx, nKV, hd), dtype=np.float32)
+    q = rng.standard_normal((1, nH, hd), dtype=np.float32)
+    kc = torch.zeros((ctx + 8, nKV, hd), dtype=torch.float16, device="cuda")
+    vc = torch.zeros_like(kc)
+    ops.kv_append(dev(kf), dev(vf), kc, vc, ctx, nKV, hd, 0)
+    assert np.array_equal(host(kc)[:ctx], kf.astype(np.float16))     # round-to-nearest-even, as __float2half_rn
+    out = torch.empty((1, nH, hd), device="cuda")
+    ops.decode_kv(dev(q), kc, vc, out, ops.workspace(1, nH, hd, 32), 1, nH, nKV, hd, ctx - 1, 32)
+    want = oracle.attention_kv(q, kf.astype(np.float16), vf.astype(np.float16), 1, nH, nKV, hd, ctx - 1, 1.0 / math.sqrt(hd))
+    assert_close(host(out), want, what="append + decode, fp16 cache")
 
 
 @pytest.mark.parametrize("S,nH,nKV,hd,cachePos", [(37, 14, 2, 64, 0), (8, 28, 4, 128, 100), (1, 14, 2, 64, 55),

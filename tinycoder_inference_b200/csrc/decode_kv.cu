@@ -4,6 +4,7 @@
 // What it replaces: launchDecodeAttentionSplit / kWarpAttentionSplit +
 // kAttnCombinePartial(W4) and kWarpAttention / kWarpAttentionPos of the reference
 // (include/gpu/GpuAttentionKernels.hpp:211-272, 537-599, 625-766, 909-1230), and
+// (the fp16 cache, kvHalf, is served by the twin kernel in decode_kv16.cu) and
 // the f32 twins kQ35WarpAttention / kQ35StoreKV-fed split path of the hybrid
 // models (include/gpu/GpuQwen35Kernels.hpp:2437-2492): score = dot(q, k) *
 // invSqrt, online softmax with exp2, out = sum p v / sum p, all f32.
@@ -395,7 +396,7 @@ static int kvMaps(const void *kvK, const void *kvV, uint32_t nKV, uint32_t hd, u
 static int kvCommonChecks(const char *who, const float *q, const void *kvK, const void *kvV, float *out,
                           uint32_t nHeads, uint32_t nKV, uint32_t hd, uint64_t totalRows, int kvHalf) {
     TC_REQUIRE(q && kvK && kvV && out, TC_EINVAL, "%s: null pointer", who);
-    TC_REQUIRE(!kvHalf, TC_EUNSUPPORTED, "%s: the fp16 KV cache is not built yet", who);
+    (void) kvHalf;
     TC_REQUIRE(hd == 64 || hd == 128, TC_EUNSUPPORTED, "%s: head_dim %u (built for 64 and 128)", who, hd);
     TC_REQUIRE(nKV > 0 && nHeads % nKV == 0, TC_EINVAL, "%s: nHeads %u not a multiple of nKV %u", who, nHeads, nKV);
     TC_REQUIRE(nHeads / nKV <= 8, TC_EUNSUPPORTED, "%s: %u q heads per kv head (built for <= 8)", who, nHeads / nKV);
@@ -421,6 +422,8 @@ static int prefillKv(const float *q, const void *kvK, const void *kvV, float *ou
     }
     const uint32_t rowBlocks = (seqLen + 7) / 8;
     TC_REQUIRE(rowBlocks <= 65535 && nHeads <= 65535, TC_EUNSUPPORTED, "prefill_kv: %u rows x %u heads", seqLen, nHeads);
+    if (kvHalf)
+        return prefillKv16(q, kvK, kvV, out, seqLen, nHeads, nKV, hd, cachePos, devPos, totalRows, invSqrt, st);
     const uint32_t nw = hd == 64 ? 8u : 4u;
     CUtensorMap tmK, tmV;
     rc = kvMaps(kvK, kvV, nKV, hd, totalRows, nw * 16u, &tmK, &tmV);
@@ -477,6 +480,9 @@ int tc_attn_decode_kv(const float *q, const void *kvK, const void *kvV, float *a
                "tc_attn_decode_kv: position %u is outside the cache of %llu rows", pos,
                (unsigned long long) totalRows);
     TC_REQUIRE(numChunks >= 1, TC_EWORKSPACE, "tc_attn_decode_kv: no chunk slots");
+    if (kvHalf)
+        return decodeKv16(q, kvK, kvV, attnOut, pAcc, pM, pL, nHeads, nKV, hd, pos, devPos, totalRows, numChunks,
+                          invSqrt, q81Out, st);
     const uint32_t nw = hd == 64 ? 8u : 4u;
     DecodePlan pl = planDecode(1, nKV, pos + 1, numChunks, nw * 16u);
     const bool direct = pl.chunksPerSeq == 1 && q81Out == nullptr;

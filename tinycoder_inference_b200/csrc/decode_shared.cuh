@@ -11,6 +11,14 @@ int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out,
                 uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st,
                 uint32_t chunksPerRank = 0, uint64_t rankStride = 0);
 
+// fp16-cache twins of the f32 decode / causal kernels (decode_kv16.cu); arguments already validated
+int decodeKv16(const float *q, const void *kvK, const void *kvV, float *attnOut, float *pAcc, float *pM, float *pL,
+               uint32_t nHeads, uint32_t nKV, uint32_t hd, uint32_t pos, const uint32_t *devPos, uint64_t totalRows,
+               uint32_t numChunks, float invSqrt, uint8_t *q81Out, cudaStream_t st);
+int prefillKv16(const float *q, const void *kvK, const void *kvV, float *out, uint32_t seqLen, uint32_t nHeads,
+                uint32_t nKV, uint32_t hd, uint32_t cachePos, const uint32_t *devPos, uint64_t totalRows,
+                float invSqrt, cudaStream_t st);
+
 #ifdef __CUDACC__
 __device__ __forceinline__ bool mbarWaitClock(uint64_t *bar, uint32_t parity, unsigned int *err,
                                               uint32_t errBit) {
