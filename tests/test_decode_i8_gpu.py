@@ -44,7 +44,8 @@ def test_7b_shape_context_edges(ctx):
     _run_single(28, 4, 128, ctx, numChunks=256, seed=ctx)
 
 
-@pytest.mark.parametrize("nH,nKV", [(40, 8), (14, 2), (12, 2), (8, 8), (8, 1), (5, 1), (21, 3), (16, 4), (6, 6)])
+@pytest.mark.parametrize("nH,nKV", [(40, 8), (14, 2), (12, 2), (8, 8), (8, 1), (5, 1), (21, 3), (16, 4), (6, 6),
+                                    (32, 2), (24, 2), (9, 1), (40, 1)])
 def test_head_layouts(nH, nKV):
     _run_single(nH, nKV, 128, 777, numChunks=64, seed=nH * 10 + nKV)
 

@@ -54,7 +54,8 @@ def test_qwen05b_shape(ctx):
 
 
 @pytest.mark.parametrize("nH,nKV,hd,ctx", [(28, 4, 128, 1000), (40, 8, 128, 777), (12, 2, 128, 300), (8, 8, 64, 200),
-                                          (7, 1, 64, 90), (9, 3, 128, 33), (16, 4, 64, 4096)])
+                                          (7, 1, 64, 90), (9, 3, 128, 33), (16, 4, 64, 4096),
+                                          (32, 2, 64, 400), (18, 2, 128, 200), (9, 1, 64, 150)])
 def test_shapes(nH, nKV, hd, ctx):
     _decode(nH, nKV, hd, ctx, numChunks=128, seed=nH + ctx)
 
@@ -79,7 +80,8 @@ def test_cpu_engine_path_agrees():
 
 @pytest.mark.parametrize("nH,nKV,hd,ctx,numChunks", [(14, 2, 64, 2048, 64), (14, 2, 64, 1, 64), (14, 2, 64, 17, 64),
                                                     (28, 4, 128, 1000, 128), (40, 8, 128, 5000, 32),
-                                                    (12, 2, 128, 129, 1), (7, 1, 64, 300, 16), (8, 8, 64, 63, 8)])
+                                                    (12, 2, 128, 129, 1), (7, 1, 64, 300, 16), (8, 8, 64, 63, 8),
+                                                    (24, 2, 64, 500, 16), (20, 2, 128, 260, 32)])
 def test_fp16_cache_decode(nH, nKV, hd, ctx, numChunks):
     """The dense models' optional fp16 cache (KVT = __half in the reference): same rule, the
     products see float(k), float(v).  Rows behind the position hold NaN."""

@@ -43,6 +43,7 @@ struct DecodeI8Params {
     uint64_t rowsPerSeq, totalRows;
     uint32_t lenHost, lenAdd;
     uint32_t nHeads, nKV, group;
+    uint32_t colBase;  // heads mode: the 8 MMA columns are q heads colBase .. colBase + 7 of the kv head
     uint32_t chunkTokens, numChunks;
     uint32_t prefetchRows;  // rows [0, prefetchRows) of a sequence may be read before the dependency wait
     // rows mode (causal prefill over the store): the 8 MMA columns of a CTA are 8
@@ -192,10 +193,10 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const uint32_t hL = warp % HPC, sub = warp / HPC;
     const uint32_t kvHead = kvHead0 + hL;
     // What MMA column j (0..7) of this warp stands for.
-    auto colValid = [&](uint32_t j) { return p.rowsMode ? (b * 8u + j < p.qRows) : (j < p.group); };
+    auto colValid = [&](uint32_t j) { return p.rowsMode ? (b * 8u + j < p.qRows) : (p.colBase + j < p.group); };
     auto colIndex = [&](uint32_t j) -> size_t {  // index of the column's q / out vector, in units of HD
         return p.rowsMode ? (static_cast<size_t>(b) * 8u + j) * p.nHeads + hg
-                          : static_cast<size_t>(b) * p.nHeads + kvHead * p.group + j;
+                          : static_cast<size_t>(b) * p.nHeads + kvHead * p.group + p.colBase + j;
     };
     // exclusive row bound of a column: everything in heads mode, causal in rows mode
     auto colLen = [&](uint32_t j) { return p.rowsMode ? min(t1, rowsPos + b * 8u + j + 1u) : t1; };
@@ -479,7 +480,7 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         }
         // column -> output vector (same rule as colIndex, for kv head kvHead0 + h)
         const size_t oidx = p.rowsMode ? (static_cast<size_t>(b) * 8u + j) * p.nHeads + hg
-                                       : static_cast<size_t>(b) * p.nHeads + (kvHead0 + h) * p.group + j;
+                                       : static_cast<size_t>(b) * p.nHeads + (kvHead0 + h) * p.group + p.colBase + j;
         if (p.directOut) {
             const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
             *reinterpret_cast<float4 *>(p.out + oidx * HD + 4 * d4) =
@@ -532,7 +533,7 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     TC_REQUIRE(d->nKV > 0 && d->nHeads % d->nKV == 0, TC_EINVAL, "decode_i8: nHeads %u not a multiple of nKV %u",
                d->nHeads, d->nKV);
     const uint32_t group = d->nHeads / d->nKV;
-    TC_REQUIRE(group <= 8, TC_EUNSUPPORTED, "decode_i8: %u q heads per kv head (built for <= 8)", group);
+    TC_REQUIRE(group <= 64, TC_EUNSUPPORTED, "decode_i8: %u q heads per kv head (built for <= 64)", group);
     TC_REQUIRE(d->batch >= 1 && d->batch <= 65535, TC_EINVAL, "decode_i8: batch %u", d->batch);
     TC_REQUIRE(d->maxLen >= 1, TC_EINVAL, "decode_i8: empty context");
     TC_REQUIRE(d->totalRows >= 1 && d->totalRows < (1ull << 31), TC_EUNSUPPORTED,
@@ -603,18 +604,24 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     prm.err = devErrorWord();
     TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "decode_i8: no device error word");
 
-    if (hd == 256) {
-        if (pl.hpc == 4) rc = launchDecodeI8<256, 4, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-        else if (pl.hpc == 2) rc = launchDecodeI8<256, 2, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-        else rc = launchDecodeI8<256, 1, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-    } else if (mt == 2) {
-        if (pl.hpc == 4) rc = launchDecodeI8<128, 4, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
-        else if (pl.hpc == 2) rc = launchDecodeI8<128, 2, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
-        else rc = launchDecodeI8<128, 1, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
-    } else {
-        if (pl.hpc == 4) rc = launchDecodeI8<128, 4, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-        else if (pl.hpc == 2) rc = launchDecodeI8<128, 2, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-        else rc = launchDecodeI8<128, 1, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+    // a launch serves 8 q heads per kv head (the MMA columns); wider groups take one launch per
+    // block of 8 and stream the rows again
+    for (uint32_t cb = 0; cb < group; cb += 8) {
+        prm.colBase = cb;
+        if (hd == 256) {
+            if (pl.hpc == 4) rc = launchDecodeI8<256, 4, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+            else if (pl.hpc == 2) rc = launchDecodeI8<256, 2, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+            else rc = launchDecodeI8<256, 1, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        } else if (mt == 2) {
+            if (pl.hpc == 4) rc = launchDecodeI8<128, 4, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
+            else if (pl.hpc == 2) rc = launchDecodeI8<128, 2, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
+            else rc = launchDecodeI8<128, 1, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        } else {
+            if (pl.hpc == 4) rc = launchDecodeI8<128, 4, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+            else if (pl.hpc == 2) rc = launchDecodeI8<128, 2, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+            else rc = launchDecodeI8<128, 1, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+        }
+        if (rc != TC_OK) return rc;
     }
     if (rc != TC_OK) return rc;
     if (direct || d->partialsOnly) return TC_OK;

@@ -31,6 +31,7 @@ struct DecodeKvParams {
     uint64_t totalRows;
     uint32_t lenHost;        // rows to attend in heads mode when devPos == nullptr
     uint32_t nHeads, nKV, group;
+    uint32_t colBase;  // heads mode: the 8 MMA columns are q heads colBase .. colBase + 7 of the kv head
     uint32_t chunkTokens, numChunks;
     uint32_t rowsMode, qRows, cachePos;  // rows mode: see decode_i8.cu
     float invSqrt;
@@ -129,10 +130,10 @@ decodeKvKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t hL = warp % HPC, sub = warp / HPC;
     const uint32_t kvHead = kvHead0 + hL;
-    auto colValid = [&](uint32_t j) { return p.rowsMode ? (b * 8u + j < p.qRows) : (j < p.group); };
+    auto colValid = [&](uint32_t j) { return p.rowsMode ? (b * 8u + j < p.qRows) : (p.colBase + j < p.group); };
     auto colIndex = [&](uint32_t j) -> size_t {
         return p.rowsMode ? (static_cast<size_t>(b) * 8u + j) * p.nHeads + hg
-                          : static_cast<size_t>(b) * p.nHeads + kvHead * p.group + j;
+                          : static_cast<size_t>(b) * p.nHeads + kvHead * p.group + p.colBase + j;
     };
     auto colLen = [&](uint32_t j) { return p.rowsMode ? min(t1, rowsPos + b * 8u + j + 1u) : t1; };
 
@@ -329,7 +330,7 @@ decodeKvKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             acc.w = fmaf(wgt, a.w, acc.w);
         }
         const size_t oidx = p.rowsMode ? (static_cast<size_t>(b) * 8u + j) * p.nHeads + hg
-                                       : static_cast<size_t>(b) * p.nHeads + (kvHead0 + h) * p.group + j;
+                                       : static_cast<size_t>(b) * p.nHeads + (kvHead0 + h) * p.group + p.colBase + j;
         if (p.directOut) {
             const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
             *reinterpret_cast<float4 *>(p.out + oidx * HD + 4 * d4) =
@@ -399,7 +400,7 @@ static int kvCommonChecks(const char *who, const float *q, const void *kvK, cons
     (void) kvHalf;
     TC_REQUIRE(hd == 64 || hd == 128, TC_EUNSUPPORTED, "%s: head_dim %u (built for 64 and 128)", who, hd);
     TC_REQUIRE(nKV > 0 && nHeads % nKV == 0, TC_EINVAL, "%s: nHeads %u not a multiple of nKV %u", who, nHeads, nKV);
-    TC_REQUIRE(nHeads / nKV <= 8, TC_EUNSUPPORTED, "%s: %u q heads per kv head (built for <= 8)", who, nHeads / nKV);
+    TC_REQUIRE(nHeads / nKV <= 64, TC_EUNSUPPORTED, "%s: %u q heads per kv head (built for <= 64)", who, nHeads / nKV);
     TC_REQUIRE(totalRows >= 1 && totalRows < (1ull << 31), TC_EUNSUPPORTED, "%s: cache of %llu rows", who,
                (unsigned long long) totalRows);
     TC_REQUIRE(((reinterpret_cast<uintptr_t>(kvK) | reinterpret_cast<uintptr_t>(kvV) | reinterpret_cast<uintptr_t>(q) |
@@ -510,9 +511,13 @@ int tc_attn_decode_kv(const float *q, const void *kvK, const void *kvV, float *a
     prm.err = devErrorWord();
     TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "tc_attn_decode_kv: no device error word");
     dim3 grid(pl.chunksPerSeq, pl.headGroups, 1);
-    rc = hd == 64 ? launchKvHpc<64, 8>(pl.hpc, tmK, tmV, prm, grid, st)
-                  : launchKvHpc<128, 4>(pl.hpc, tmK, tmV, prm, grid, st);
-    if (rc != TC_OK || direct) return rc;
+    for (uint32_t cb = 0; cb < prm.group; cb += 8) {  // 8 q heads of a kv head per launch
+        prm.colBase = cb;
+        rc = hd == 64 ? launchKvHpc<64, 8>(pl.hpc, tmK, tmV, prm, grid, st)
+                      : launchKvHpc<128, 4>(pl.hpc, tmK, tmV, prm, grid, st);
+        if (rc != TC_OK) return rc;
+    }
+    if (direct) return TC_OK;
     return launchMerge(pAcc, pM, pL, attnOut, 1, nHeads, numChunks, pl.chunksPerSeq, hd, devPos, devPos ? 1u : 0u,
                        pl.chunkTokens, q81Out, false, st);
 }

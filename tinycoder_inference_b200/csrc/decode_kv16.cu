@@ -27,6 +27,7 @@ struct DecodeKv16Params {
     uint64_t totalRows;
     uint32_t lenHost;
     uint32_t nHeads, nKV, group;
+    uint32_t colBase;  // heads mode: the 8 MMA columns are q heads colBase .. colBase + 7 of the kv head
     uint32_t chunkTokens, numChunks;
     uint32_t rowsMode, qRows, cachePos;  // rows mode: see decode_i8.cu
     float invSqrt;
@@ -123,10 +124,10 @@ decodeKv16Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t hL = warp % HPC, sub = warp / HPC;
     const uint32_t kvHead = kvHead0 + hL;
-    auto colValid = [&](uint32_t j) { return p.rowsMode ? (b * 8u + j < p.qRows) : (j < p.group); };
+    auto colValid = [&](uint32_t j) { return p.rowsMode ? (b * 8u + j < p.qRows) : (p.colBase + j < p.group); };
     auto colIndex = [&](uint32_t j) -> size_t {
         return p.rowsMode ? (static_cast<size_t>(b) * 8u + j) * p.nHeads + hg
-                          : static_cast<size_t>(b) * p.nHeads + kvHead * p.group + j;
+                          : static_cast<size_t>(b) * p.nHeads + kvHead * p.group + p.colBase + j;
     };
     auto colLen = [&](uint32_t j) { return p.rowsMode ? min(t1, rowsPos + b * 8u + j + 1u) : t1; };
 
@@ -313,7 +314,7 @@ decodeKv16Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             acc.w = fmaf(wgt, a.w, acc.w);
         }
         const size_t oidx = p.rowsMode ? (static_cast<size_t>(b) * 8u + j) * p.nHeads + hg
-                                       : static_cast<size_t>(b) * p.nHeads + (kvHead0 + h) * p.group + j;
+                                       : static_cast<size_t>(b) * p.nHeads + (kvHead0 + h) * p.group + p.colBase + j;
         if (p.directOut) {
             const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
             *reinterpret_cast<float4 *>(p.out + oidx * HD + 4 * d4) =
@@ -407,9 +408,13 @@ int decodeKv16(const float *q, const void *kvK, const void *kvV, float *attnOut,
     prm.err = devErrorWord();
     TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "tc_attn_decode_kv: no device error word");
     dim3 grid(pl.chunksPerSeq, pl.headGroups, 1);
-    rc = hd == 64 ? launchKv16Hpc<64>(pl.hpc, tmK, tmV, prm, grid, st)
-                  : launchKv16Hpc<128>(pl.hpc, tmK, tmV, prm, grid, st);
-    if (rc != TC_OK || direct) return rc;
+    for (uint32_t cb = 0; cb < prm.group; cb += 8) {  // 8 q heads of a kv head per launch
+        prm.colBase = cb;
+        rc = hd == 64 ? launchKv16Hpc<64>(pl.hpc, tmK, tmV, prm, grid, st)
+                      : launchKv16Hpc<128>(pl.hpc, tmK, tmV, prm, grid, st);
+        if (rc != TC_OK) return rc;
+    }
+    if (direct) return TC_OK;
     return launchMerge(pAcc, pM, pL, attnOut, 1, nHeads, numChunks, pl.chunksPerSeq, hd, devPos, devPos ? 1u : 0u,
                        pl.chunkTokens, q81Out, false, st);
 }
