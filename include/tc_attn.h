@@ -306,6 +306,35 @@ int tc_attn_prefill_i8(const float *q, const int8_t *k8, const int8_t *v8,
                        uint64_t totalRows, float invSqrt, tc_stream stream);
 
 /* ------------------------------------------------------------------------- */
+/* the step in front of attention: Q/K RMSNorm + rotation, rotation tables      */
+/* ------------------------------------------------------------------------- */
+
+/* Replaces kQ35QNormRoPE + kQ35KNormRoPE (include/gpu/GpuQwen35Kernels.hpp:55-137;
+ * launched at src/cpp/core/cuda/forward/GPUComputeForward.cu:1330-1337) in one
+ * launch: per (token, head) slice rms = rsqrt(mean(x^2) + 1e-6), y = x*rms*w, the
+ * first nDims elements rotated NEOX-style (pairs j, j + nDims/2) by table row
+ * pos + s (devPos: position read on the device), the rest copied.  Q: rows
+ * qIn[s][h] of stride qInStride floats (2*hd in the gated models: q then gate)
+ * -> qOut[s][nHeads][hd], out of place.  K: [s][nKV][hd] in place.  Either side
+ * may be NULL.  cosT/sinT [tableRows][nDims/2].  Bit-identical to the reference
+ * kernels (same summation order, same intrinsics). */
+int tc_qk_norm_rope(const float *qIn, uint32_t qInStride, float *qOut, float *k,
+                    const float *wq, const float *wk, uint32_t hd, uint32_t nDims,
+                    uint32_t nHeads, uint32_t nKV, uint32_t seqLen, uint32_t pos,
+                    const uint32_t *devPos, const float *cosT, const float *sinT,
+                    uint32_t tableRows, tc_stream stream);
+
+/* HOST functions: the rotation tables the engine uploads once.
+ * tc_rope_tables: [rows][headDim/2], angle = float(p) / powf(theta, 2j/headDim)
+ *   (src/cpp/core/cuda/forward/GPUComputeUpload.cu:1149-1163; CPU twin
+ *   src/cpp/core/ModelPrimitives.cpp:112-127).
+ * tc_mrope_tables: [rows][nDims/2], angle = float(p) * t_j with t_0 = 1 and
+ *   t_{j+1} = t_j * powf(thetaBase, -2/nDims), the product taken in float
+ *   (GPUComputeUpload.cu:1178-1203). */
+int tc_rope_tables(float *cosT, float *sinT, uint32_t rows, uint32_t headDim, float theta);
+int tc_mrope_tables(float *cosT, float *sinT, uint32_t rows, uint32_t nDims, float thetaBase);
+
+/* ------------------------------------------------------------------------- */
 /* attention-output epilogues                                                  */
 /* ------------------------------------------------------------------------- */
 

@@ -282,6 +282,25 @@ def sigmoid_gate(attnOut, qGate, seqLen, nHeads, hd):
     return o
 
 
+def norm_rope(x, w, hd, nDims, heads, seqLen, pos, cosT, sinT, in_stride=None):
+    """kQ35QNormRoPE (in_stride = 2*hd, q then gate per head) / kQ35KNormRoPE (in_stride = hd)."""
+    in_stride = hd if in_stride is None else in_stride
+    xin = _c(x, np.float32)
+    out = np.zeros((seqLen, heads, hd), np.float32)
+    _lib.orc_norm_rope(_p(xin, _f32p), C.c_uint32(in_stride), _p(out, _f32p), _p(_c(w, np.float32), _f32p),
+                       C.c_uint32(hd), C.c_uint32(nDims), C.c_uint32(heads), C.c_uint32(seqLen), C.c_uint32(pos),
+                       _p(_c(cosT, np.float32), _f32p), _p(_c(sinT, np.float32), _f32p))
+    return out
+
+
+def mrope_tables(rows, nDims, thetaBase):
+    cosT = np.zeros((rows, nDims // 2), np.float32)
+    sinT = np.zeros((rows, nDims // 2), np.float32)
+    _lib.orc_mrope_tables(_p(cosT, _f32p), _p(sinT, _f32p), C.c_uint32(rows), C.c_uint32(nDims),
+                          C.c_float(thetaBase))
+    return cosT, sinT
+
+
 # ---- planner -----------------------------------------------------------------
 
 _lib.orc_kv_bytes_per_token.restype = C.c_uint64

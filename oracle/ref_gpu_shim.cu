@@ -109,6 +109,17 @@ int ref_gpu_softmax_causal(const float *scores, __half *pOut, uint32_t seqLen, u
     return done();
 }
 
+// kQ35QNormRoPE + kQ35KNormRoPE as launched at GPUComputeForward.cu:1330-1337
+int ref_gpu_qk_norm_rope(const float *qGate, float *qOut, float *k, const float *wq, const float *wk, uint32_t hd,
+                         uint32_t nDims, uint32_t nHeads, uint32_t nKV, uint32_t seqLen, uint32_t pos,
+                         const float *cosT, const float *sinT) {
+    kQ35QNormRoPE<<<dim3(seqLen, nHeads), 128, 128 * sizeof(float)>>>(qGate, qOut, wq, hd, nDims, nHeads, seqLen, pos,
+                                                                     nullptr, cosT, sinT);
+    kQ35KNormRoPE<<<dim3(seqLen, nKV), 128, 128 * sizeof(float)>>>(k, wk, hd, nDims, nKV, seqLen, pos, nullptr, cosT,
+                                                                  sinT);
+    return done();
+}
+
 }  // extern "C"
 
 }  // namespace tinycoder::gpu

@@ -693,6 +693,63 @@ void orc_sigmoid_gate(float *attnOut, const float *qGate, uint32_t seqLen,
             }
 }
 
+/* kQ35QNormRoPE / kQ35KNormRoPE (include/gpu/GpuQwen35Kernels.hpp:55-137): one
+ * 128-thread block per (token, head) slice.  Thread t folds x[t], x[t+128], ...
+ * with fmaf, the 128 partial sums are folded by a shared-memory tree (64, 32,
+ * ..., 1 apart); rms = rsqrtf(sum / hd + 1e-6f) -- 1/sqrtf here, the device
+ * intrinsic differs from it in the last bits; y = x * rms * w; the first nDims
+ * elements are rotated in NEOX pairs (j, j + nDims/2) by table row pos + s with
+ * the fmaf form, the rest copied.  in rows have stride inStride (2*hd for the
+ * gated q), out rows stride hd; in == out is allowed (the K kernel). */
+void orc_norm_rope(const float *in, uint32_t inStride, float *out, const float *w,
+                   uint32_t hd, uint32_t nDims, uint32_t heads, uint32_t seqLen,
+                   uint32_t pos, const float *cosT, const float *sinT) {
+    const uint32_t half = nDims / 2;
+    float *tmp = (float *) malloc(sizeof(float) * hd);
+    for (uint32_t s = 0; s < seqLen; ++s)
+        for (uint32_t h = 0; h < heads; ++h) {
+            const float *rp = in + ((uint64_t) s * heads + h) * inStride;
+            float *op = out + ((uint64_t) s * heads + h) * hd;
+            float part[128];
+            for (uint32_t t = 0; t < 128; ++t) {
+                float acc = 0.0f;
+                for (uint32_t j = t; j < hd; j += 128) acc = fmaf(rp[j], rp[j], acc);
+                part[t] = acc;
+            }
+            for (uint32_t st = 64; st > 0; st >>= 1)
+                for (uint32_t t = 0; t < st; ++t) part[t] += part[t + st];
+            const float rms = 1.0f / sqrtf(part[0] / (float) hd + 1e-6f);
+            const float *c = cosT + (uint64_t) (pos + s) * half;
+            const float *sn = sinT + (uint64_t) (pos + s) * half;
+            for (uint32_t j = 0; j < half; ++j) {
+                const float x0 = rp[j] * rms * w[j];
+                const float x1 = rp[j + half] * rms * w[j + half];
+                tmp[j] = fmaf(x0, c[j], -x1 * sn[j]);
+                tmp[j + half] = fmaf(x0, sn[j], x1 * c[j]);
+            }
+            for (uint32_t j = nDims; j < hd; ++j) tmp[j] = rp[j] * rms * w[j];
+            memcpy(op, tmp, sizeof(float) * hd);
+        }
+    free(tmp);
+}
+
+/* The MRoPE cache of the hybrid models
+ * (src/cpp/core/cuda/forward/GPUComputeUpload.cu:1178-1203): [rows][nDims/2],
+ * angle = float(p) * theta_j, theta_0 = 1, theta_{j+1} = theta_j * powf(base, -2/nDims). */
+void orc_mrope_tables(float *cosT, float *sinT, uint32_t rows, uint32_t nDims,
+                      float thetaBase) {
+    const uint32_t half = nDims / 2;
+    const float scale = powf(thetaBase, -2.0f / (float) nDims);
+    for (uint32_t p = 0; p < rows; ++p) {
+        float theta = 1.0f;
+        for (uint32_t j = 0; j < half; ++j) {
+            cosT[(uint64_t) p * half + j] = cosf((float) p * theta);
+            sinT[(uint64_t) p * half + j] = sinf((float) p * theta);
+            theta *= scale;
+        }
+    }
+}
+
 /* ------------------------------------------------------------------------- */
 /* context planner                                                            */
 /* ------------------------------------------------------------------------- */

@@ -4,6 +4,7 @@ Needs a GPU and oracle/_ref/libtc_ref_gpu.so (built by `make -C oracle refgpu` w
 the reference checkout is mounted; the built library travels with the tree):
 
     python tests/golden/make_ref_gpu_golden.py [out.npz]
+    python tests/golden/make_ref_gpu_golden.py f2 [out_f2.npz]      (ref_gpu_golden_f2.npz)
 
 The result is committed as tests/golden/ref_gpu_golden.npz; inputs are regenerated
 from seeds (tests/golden/ref_gpu_cases.py), only outputs are stored."""
@@ -152,5 +153,25 @@ def main(out_path):
     print(f"wrote {len(G)} arrays, {os.path.getsize(out_path)} bytes -> {out_path}")
 
 
+def main_f2(out_path):
+    """kQ35QNormRoPE + kQ35KNormRoPE -> ref_gpu_golden_f2.npz (python ... f2 [out.npz])."""
+    G = {}
+    u32 = C.c_uint32
+    for i, (name, c) in enumerate(cases.CASES_F2.items()):
+        qg, k, wq, wk = cases.norm_rope_case(20 + i, c)
+        cosT, sinT = oracle.mrope_tables(c["rows"], c["nDims"], c["theta"])
+        qOut = torch.zeros((c["S"], c["nH"], c["hd"]), device="cuda")
+        dk = d(k)
+        call(lib.ref_gpu_qk_norm_rope, p(d(qg)), p(qOut), p(dk), p(d(wq)), p(d(wk)), u32(c["hd"]), u32(c["nDims"]),
+             u32(c["nH"]), u32(c["nKV"]), u32(c["S"]), u32(c["pos"]), p(d(cosT)), p(d(sinT)))
+        G[f"{name}.q"] = qOut.cpu().numpy()
+        G[f"{name}.k"] = dk.cpu().numpy()
+    np.savez_compressed(out_path, **G)
+    print(f"wrote {len(G)} arrays, {os.path.getsize(out_path)} bytes -> {out_path}")
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "ref_gpu_golden.npz"))
+    if len(sys.argv) > 1 and sys.argv[1] == "f2":
+        main_f2(sys.argv[2] if len(sys.argv) > 2 else os.path.join(HERE, "ref_gpu_golden_f2.npz"))
+    else:
+        main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "ref_gpu_golden.npz"))

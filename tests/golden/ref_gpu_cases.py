@@ -64,3 +64,19 @@ CASES = {
     "sigmoid_gate": dict(S=2, nH=4, hd=256),
     "softmax_causal": dict(S=8, nH=2, scale=1.0 / math.sqrt(128.0)),
 }
+
+# recorded later into ref_gpu_golden_f2.npz (the step in front of attention in the gated models)
+CASES_F2 = {
+    "qk_norm_rope_256": dict(S=3, nH=4, nKV=2, hd=256, nDims=64, pos=5, rows=16, theta=1e7),
+    "qk_norm_rope_128": dict(S=2, nH=6, nKV=3, hd=128, nDims=128, pos=0, rows=8, theta=1e6),
+    "qk_norm_rope_64": dict(S=4, nH=2, nKV=1, hd=64, nDims=32, pos=9, rows=16, theta=1e4),
+}
+
+
+def norm_rope_case(case, c):
+    r = _rng(case)
+    qg = r.standard_normal((c["S"], c["nH"], 2 * c["hd"]), dtype=np.float32) * 2
+    k = r.standard_normal((c["S"], c["nKV"], c["hd"]), dtype=np.float32) * 0.5
+    wq = (1 + 0.1 * r.standard_normal(c["hd"])).astype(np.float32)
+    wk = (1 + 0.1 * r.standard_normal(c["hd"])).astype(np.float32)
+    return qg, k, wq, wk

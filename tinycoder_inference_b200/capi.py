@@ -149,6 +149,10 @@ SIGNATURES = {
                                _u32, _f, _i, _vp, _vp]),
     "tc_attn_merge_partials": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "tc_attn_merge_gathered": (_i, [_vp, _vp, _u32, _u32, _u32, _u32, _vp]),
+    "tc_qk_norm_rope": (_i, [_vp, _u32, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _u32,
+                            _vp]),
+    "tc_rope_tables": (_i, [_vp, _vp, _u32, _u32, _f]),
+    "tc_mrope_tables": (_i, [_vp, _vp, _u32, _u32, _f]),
     "tc_attn_exchange_bytes": (_i, [_u32, _u32, _u32, _sz_p]),
     "tc_attn_merge_exchange": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, C.POINTER(PeerGroup), _u32, _vp]),
     "tc_attn_merge_exchange_local": (_i, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),

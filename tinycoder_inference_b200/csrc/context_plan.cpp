@@ -12,7 +12,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cmath>
 #include <string>
+#include <vector>
 
 #include <cuda_runtime.h>
 
@@ -204,6 +206,38 @@ int tc_kv_pool_geometry_compute(uint32_t maxSeqLen, uint32_t nLayersOnGpu, uint3
     g->partialAccBytes = static_cast<uint64_t>(nHeads) * g->attnChunks * hd * sizeof(float);
     g->partialMLBytes = static_cast<uint64_t>(nHeads) * g->attnChunks * sizeof(float);
     return rc;
+}
+
+// Rotation tables (host).  Plain float arithmetic in the reference's order, so the tables are
+// the ones the engine uploads (GPUComputeUpload.cu:1149-1163 and 1178-1203).
+int tc_rope_tables(float *cosT, float *sinT, uint32_t rows, uint32_t headDim, float theta) {
+    if (!cosT || !sinT || headDim < 2 || (headDim % 2u) != 0) return TC_EINVAL;
+    const uint32_t pairs = headDim / 2;
+    std::vector<float> freq(pairs);
+    for (uint32_t j = 0; j < pairs; ++j)
+        freq[j] = 1.0f / std::pow(theta, static_cast<float>(2 * j) / static_cast<float>(headDim));
+    for (uint32_t p = 0; p < rows; ++p)
+        for (uint32_t j = 0; j < pairs; ++j) {
+            const float ang = static_cast<float>(p) * freq[j];
+            cosT[static_cast<size_t>(p) * pairs + j] = std::cos(ang);
+            sinT[static_cast<size_t>(p) * pairs + j] = std::sin(ang);
+        }
+    return TC_OK;
+}
+
+int tc_mrope_tables(float *cosT, float *sinT, uint32_t rows, uint32_t nDims, float thetaBase) {
+    if (!cosT || !sinT || nDims < 2 || (nDims % 2u) != 0) return TC_EINVAL;
+    const uint32_t half = nDims / 2;
+    const float thetaScale = std::pow(thetaBase, -2.0f / static_cast<float>(nDims));
+    for (uint32_t p = 0; p < rows; ++p) {
+        float theta = 1.0f;
+        for (uint32_t j = 0; j < half; ++j) {
+            cosT[static_cast<size_t>(p) * half + j] = std::cos(static_cast<float>(p) * theta);
+            sinT[static_cast<size_t>(p) * half + j] = std::sin(static_cast<float>(p) * theta);
+            theta *= thetaScale;
+        }
+    }
+    return TC_OK;
 }
 
 }  // extern "C"

@@ -56,6 +56,32 @@ def kv_append_rope(q, kSrc, vSrc, kDst, vDst, seqLen, nHeads, nKV, hd, cachePos,
                                 max_rows, _stream()))
 
 
+def qk_norm_rope(qIn, qOut, k, wq, wk, hd, nDims, nHeads, nKV, seqLen, pos, cosT, sinT, dev_pos=None,
+                 q_in_stride=None):
+    """Per-head RMSNorm of q (out of place, rows of stride q_in_stride) and k (in place) + partial rotation."""
+    stride = (2 * hd if q_in_stride is None else q_in_stride) if qIn is not None else 0
+    rows = cosT.numel() // max(1, nDims // 2)
+    check(lib.tc_qk_norm_rope(_ptr(qIn), stride, _ptr(qOut), _ptr(k), _ptr(wq), _ptr(wk), hd, nDims, nHeads, nKV,
+                              seqLen, pos, _ptr(dev_pos), _ptr(cosT), _ptr(sinT), rows, _stream()))
+
+
+def rope_tables(rows, headDim, theta):
+    """Host: the engine's NEOX tables [rows][headDim/2] (numpy float32 pair)."""
+    import numpy as np
+    c = np.zeros((rows, headDim // 2), np.float32)
+    s = np.zeros_like(c)
+    check(lib.tc_rope_tables(c.ctypes.data, s.ctypes.data, rows, headDim, theta))
+    return c, s
+
+
+def mrope_tables(rows, nDims, thetaBase):
+    import numpy as np
+    c = np.zeros((rows, nDims // 2), np.float32)
+    s = np.zeros_like(c)
+    check(lib.tc_mrope_tables(c.ctypes.data, s.ctypes.data, rows, nDims, thetaBase))
+    return c, s
+
+
 def rope_q(q, cosT, sinT, seqLen, nHeads, hd, pos, dev_pos=None):
     check(lib.tc_rope_q(_ptr(q), _ptr(cosT), _ptr(sinT), seqLen, nHeads, hd, pos, _ptr(dev_pos), _stream()))
 
