@@ -411,6 +411,71 @@ int tc_kv_pool_geometry_compute(uint32_t maxSeqLen, uint32_t nLayersOnGpu,
                                 int kvStoreI8, int kvMirror,
                                 tc_kv_pool_geometry *g);
 
+/* ------------------------------------------------------------------------- */
+/* the attention block's host bookkeeping                                       */
+/* ------------------------------------------------------------------------- */
+
+/* What GPUModel keeps around its attention kernels
+ * (src/cpp/core/cuda/forward/GPUComputeMoE.cu:3013-3200; GPUComputeForward.cu:3778-4040,
+ * 3362-3372, 5175-5222; include/GPUCompute.hpp:844-899): the KV mode chosen by
+ * the context plan, the per-slot row count of the int8 pool (kv8Rows_), the
+ * position and the window guard.  A session owns NO device memory: every buffer
+ * below belongs to the caller and is laid out as tc_kv_pool_geometry_compute
+ * says ([slot][row][nKV][hd]; int8 pools and scales have maxSeqLen + 16 rows per
+ * slot).  One caller and one stream at a time per session. */
+typedef struct tc_kv_session tc_kv_session;
+
+typedef struct tc_kv_session_config {
+    uint32_t nHeads, nKV, hd;
+    uint32_t maxSeqLen;          /* the window (tc_context_plan.seqLen) */
+    uint32_t slots;              /* layers that own K/V */
+    int kvStoreI8;               /* plan.kv == int8: int8 rows ARE the store, no f32 cache */
+    int kvMirror;                /* plan.kvMirror: f32 store + int8 pool for decode */
+    int kvHalf;                  /* fp16 store (dense models, opt-in) */
+    void *kvK, *kvV;             /* NULL when kvStoreI8 */
+    int8_t *kvK8, *kvV8;         /* NULL without an int8 pool */
+    float *kvK8Scale, *kvV8Scale;
+    float *pAcc, *pM, *pL;       /* split-KV partials for one token */
+    uint32_t numChunks;
+    const float *ropeCos, *ropeSin; /* dense models: K (and q, in place) rotated in the store; NULL = verbatim */
+    void *prefillScratch;        /* optional: lets a fresh prompt on the f32 cache use tc_attn_prefill_f16 */
+    size_t prefillScratchBytes;
+} tc_kv_session_config;
+
+int tc_kv_session_create(const tc_kv_session_config *cfg, tc_kv_session **out);
+void tc_kv_session_destroy(tc_kv_session *s);
+
+/* GPUModel::clearKVCache: f32 / fp16 cache zeroed, every slot's int8 row count
+ * and the position reset, "context full" cleared; synchronises the stream. */
+int tc_kv_session_clear(tc_kv_session *s, tc_stream stream);
+
+/* GPUModel::forward's window guard: TC_ECONTEXT_FULL (and the sticky flag) when
+ * position + newTokens passes the window, before anything is written; else
+ * *pos = the position the new rows start at.  tc_kv_session_commit advances the
+ * position after the layers have run (kvPos_ += tokens). */
+int tc_kv_session_begin(tc_kv_session *s, uint32_t newTokens, uint32_t *pos);
+int tc_kv_session_commit(tc_kv_session *s, uint32_t newTokens);
+uint32_t tc_kv_session_pos(const tc_kv_session *s);
+int tc_kv_session_context_full(const tc_kv_session *s);
+uint32_t tc_kv_session_rows8(const tc_kv_session *s, uint32_t slot);
+
+/* One layer's attention block: store the seqLen new K/V rows of `slot` at `pos`
+ * and attend.  q [seqLen][nHeads][hd] (rotated in place when the session has
+ * rotation tables), kSrc/vSrc [seqLen][nKV][hd] f32, attnOut [seqLen][nHeads][hd].
+ *   - one row, int8 pool present, not under graph capture, host position: the
+ *     pool first receives the rows a prefill left only in the f32 cache
+ *     ([rows8, pos)), then the new row, and the int8 decode kernel runs;
+ *   - int8 store, several rows or graph capture: quantise into the pool, causal
+ *     attention over it (devPos allowed);
+ *   - f32 / fp16 store: append (with rotation if configured), then split-KV
+ *     decode (one row) or causal attention (several; a fresh prompt takes the
+ *     tensor-core prefill when scratch was given).
+ * graphCapture != 0 says the call is being captured: nothing that depends on
+ * host-side row counts is chosen. */
+int tc_kv_session_attend(tc_kv_session *s, uint32_t slot, float *q, const float *kSrc,
+                         const float *vSrc, float *attnOut, uint32_t seqLen, uint32_t pos,
+                         const uint32_t *devPos, int graphCapture, tc_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -94,6 +94,21 @@ class KvPoolGeometry(C.Structure):
     ]
 
 
+class KvSessionConfig(C.Structure):
+    _fields_ = [
+        ("nHeads", C.c_uint32), ("nKV", C.c_uint32), ("hd", C.c_uint32),
+        ("maxSeqLen", C.c_uint32), ("slots", C.c_uint32),
+        ("kvStoreI8", C.c_int), ("kvMirror", C.c_int), ("kvHalf", C.c_int),
+        ("kvK", C.c_void_p), ("kvV", C.c_void_p),
+        ("kvK8", C.c_void_p), ("kvV8", C.c_void_p),
+        ("kvK8Scale", C.c_void_p), ("kvV8Scale", C.c_void_p),
+        ("pAcc", C.c_void_p), ("pM", C.c_void_p), ("pL", C.c_void_p),
+        ("numChunks", C.c_uint32),
+        ("ropeCos", C.c_void_p), ("ropeSin", C.c_void_p),
+        ("prefillScratch", C.c_void_p), ("prefillScratchBytes", C.c_size_t),
+    ]
+
+
 class PeerGroup(C.Structure):
     _fields_ = [("buffers", C.c_void_p * 16), ("world", C.c_uint32), ("rank", C.c_uint32)]
 
@@ -149,6 +164,15 @@ SIGNATURES = {
                                _u32, _f, _i, _vp, _vp]),
     "tc_attn_merge_partials": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "tc_attn_merge_gathered": (_i, [_vp, _vp, _u32, _u32, _u32, _u32, _vp]),
+    "tc_kv_session_create": (_i, [C.POINTER(KvSessionConfig), C.POINTER(_vp)]),
+    "tc_kv_session_destroy": (None, [_vp]),
+    "tc_kv_session_clear": (_i, [_vp, _vp]),
+    "tc_kv_session_begin": (_i, [_vp, _u32, C.POINTER(_u32)]),
+    "tc_kv_session_commit": (_i, [_vp, _u32]),
+    "tc_kv_session_pos": (_u32, [_vp]),
+    "tc_kv_session_context_full": (_i, [_vp]),
+    "tc_kv_session_rows8": (_u32, [_vp, _u32]),
+    "tc_kv_session_attend": (_i, [_vp, _u32, _vp, _vp, _vp, _vp, _u32, _u32, _vp, _i, _vp]),
     "tc_qk_norm_rope": (_i, [_vp, _u32, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _u32,
                             _vp]),
     "tc_rope_tables": (_i, [_vp, _vp, _u32, _u32, _f]),

@@ -270,3 +270,83 @@ def kv_pool_geometry(maxSeqLen, nLayersOnGpu, fullAttentionInterval, nHeads, nKV
     check(lib.tc_kv_pool_geometry_compute(maxSeqLen, nLayersOnGpu, fullAttentionInterval, nHeads, nKV, hd,
                                           int(kvHalf), int(kvStoreI8), int(kvMirror), C.byref(g)))
     return g
+
+
+# ---- the attention block's host bookkeeping ----------------------------------------
+
+class KvSession:
+    """tc_kv_session over torch-allocated pools (what GPUModel holds around its attention
+    kernels): mode = "f32" | "f32+i8" (f32 store, int8 decode pool) | "i8" (int8 store) | "f16"."""
+
+    def __init__(self, nHeads, nKV, hd, max_seq, slots, mode="f32", rope=None, prefill_scratch_rows=0, chunks=None):
+        self.nH, self.nKV, self.hd, self.max_seq, self.slots, self.mode = nHeads, nKV, hd, max_seq, slots, mode
+        store_i8, mirror, half = mode == "i8", mode == "f32+i8", mode == "f16"
+        g = kv_pool_geometry(max_seq, slots, 1, nHeads, nKV, hd, half, store_i8, mirror)
+        self.geom = g
+        dev = "cuda"
+        cfg = capi.KvSessionConfig()
+        cfg.nHeads, cfg.nKV, cfg.hd, cfg.maxSeqLen, cfg.slots = nHeads, nKV, hd, max_seq, slots
+        cfg.kvStoreI8, cfg.kvMirror, cfg.kvHalf = int(store_i8), int(mirror), int(half)
+        self._keep = []
+        if not store_i8:
+            dt = torch.float16 if half else torch.float32
+            self.kvK = torch.zeros((slots, max_seq, nKV, hd), dtype=dt, device=dev)
+            self.kvV = torch.zeros_like(self.kvK)
+            cfg.kvK, cfg.kvV = self.kvK.data_ptr(), self.kvV.data_ptr()
+        if store_i8 or mirror:
+            # stale bytes on purpose: the bookkeeping, not a memset, keeps old rows out
+            self.k8 = torch.full((slots, max_seq + 16, nKV, hd), 77, dtype=torch.int8, device=dev)
+            self.v8 = torch.full_like(self.k8, -55)
+            self.ks = torch.full((slots, max_seq + 16, nKV), float("nan"), device=dev)
+            self.vs = torch.full_like(self.ks, float("nan"))
+            cfg.kvK8, cfg.kvV8 = self.k8.data_ptr(), self.v8.data_ptr()
+            cfg.kvK8Scale, cfg.kvV8Scale = self.ks.data_ptr(), self.vs.data_ptr()
+        self.chunks = chunks or g.attnChunks
+        self.ws = workspace(1, nHeads, hd, self.chunks)
+        cfg.pAcc, cfg.pM, cfg.pL = (w.data_ptr() for w in self.ws)
+        cfg.numChunks = self.chunks
+        if rope is not None:
+            self._keep += list(rope)
+            cfg.ropeCos, cfg.ropeSin = rope[0].data_ptr(), rope[1].data_ptr()
+        if prefill_scratch_rows:
+            n = prefill_f16_scratch_bytes(prefill_scratch_rows, nHeads, nKV, hd)
+            buf = torch.empty(n + 1024, dtype=torch.uint8, device=dev)
+            off = (-buf.data_ptr()) % 1024
+            self._keep.append(buf)
+            cfg.prefillScratch, cfg.prefillScratchBytes = buf.data_ptr() + off, n
+        self.cfg = cfg
+        h = C.c_void_p()
+        check(lib.tc_kv_session_create(C.byref(cfg), C.byref(h)))
+        self.h = h
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib.tc_kv_session_destroy(self.h)
+            self.h = None
+
+    def clear(self):
+        check(lib.tc_kv_session_clear(self.h, _stream()))
+
+    def begin(self, n):
+        pos = C.c_uint32(0)
+        check(lib.tc_kv_session_begin(self.h, n, C.byref(pos)))
+        return pos.value
+
+    def commit(self, n):
+        check(lib.tc_kv_session_commit(self.h, n))
+
+    @property
+    def pos(self):
+        return lib.tc_kv_session_pos(self.h)
+
+    @property
+    def context_full(self):
+        return bool(lib.tc_kv_session_context_full(self.h))
+
+    def rows8(self, slot):
+        return lib.tc_kv_session_rows8(self.h, slot)
+
+    def attend(self, slot, q, k, v, out, pos, dev_pos=None, graph_capture=False):
+        seqLen = q.shape[0]
+        check(lib.tc_kv_session_attend(self.h, slot, _ptr(q), _ptr(k), _ptr(v), _ptr(out), seqLen, pos, _ptr(dev_pos),
+                                       int(graph_capture), _stream()))
