@@ -10,23 +10,29 @@
 // scores, probabilities rounded to fp16 -- but flash-style, so the score matrix
 // never exists and the sequence length is not capped at 512.
 //
-// One CTA = one q head x 256 query rows = two 128-row query tiles A and B.  Warp roles:
-//   warps 0-3 / 4-7  softmax of tile A / B: thread r owns query row r, reads its 128
-//              scores from TMEM in one pass (tcgen05.ld), keeps (m, l), writes the fp16
-//              probabilities over the first 64 columns of the same S region (tcgen05.st)
-//              as the A operand of the PV product, rescales O in TMEM only when the row
-//              maximum ran ahead by 2^8 (lazy rescale);
-//   warp 8     TMA producer: both Q tiles once, then K / V tiles of 128 tokens into
-//              two-stage rings (cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA
-//              shared-memory layout, so no register pass touches the operands);
-//   warp 9     MMA issuer: one thread issues tcgen05.mma -- S_X = Q_X K^T (M128 N128 K16
-//              x8), O_X += P_X V (A from TMEM, B = V MN-major from shared memory) -- in the
-//              order S_A, S_B, then per KV tile [O_A, S_A(next)], [O_B, S_B(next)], so the
-//              tensor pipe works for one tile while the other tile's softmax runs;
-//              tcgen05.commit onto mbarriers.
-// Causality: a query tile only visits KV tiles up to its own diagonal tile, which is
-// masked element-wise; heavy (late) query blocks are scheduled first.
-// TMEM: S_A, S_B (128 columns each, f32; P aliases their first 64), O_A, O_B (128 each) = 512.
+// One CTA = one q head x 256 query rows = two 128-row query tiles A and B; KV tiles of 64
+// tokens.  Warp roles:
+//   warps 0-3 / 4-7  softmax of tile A / B: thread r owns query row r, reads its 64 scores
+//              of a KV tile from TMEM (tcgen05.ld), keeps (m, l), writes the fp16
+//              probabilities over the first 32 columns of the same S buffer (tcgen05.st) as
+//              the A operand of the PV product, rescales O in TMEM only when the row maximum
+//              ran ahead by 2^8 (lazy rescale);
+//   warp 8     TMA producer: both Q tiles and K_0, K_1 once, then a four-stage ring whose
+//              stage j holds what step j of the MMA warps consumes, K_{j+2} and V_j
+//              (cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA shared-memory
+//              layout, so no register pass touches the operands);
+//   warps 9, 10  MMA issuers of tile A / B: lane 0 issues tcgen05.mma -- S_X(j) = Q_X K_j^T
+//              (M128 N64 K16 x8), O_X += P_X(j) V_j (A from TMEM, B = V MN-major from shared
+//              memory, K16 x4) -- and tcgen05.commit onto mbarriers.  One warp per query tile:
+//              the waits and bookkeeping of one tile's step overlap the other tile's issue.
+// S is DOUBLE-BUFFERED per query tile: S_X(j+2) is issued right behind O_X += P_X(j) V_j into
+// the buffer that P_X(j) just left, so S_X(j+1) is already waiting when the softmax of tile j
+// finishes -- the softmax warps never wait for the tensor pipe, and the tensor pipe always has
+// the other buffer's and the other tile's products queued.  (With one S buffer per tile the
+// chain softmax -> PV -> QK^T -> softmax left both pipes idle about half of the time.)
+// Causality: a query tile only visits KV tiles up to its diagonal, the last two are masked
+// element-wise; heavy (late) query blocks are scheduled first.
+// TMEM (512 columns): O_A, O_B (128 each, f32), S_{A,0}, S_{A,1}, S_{B,0}, S_{B,1} (64 each).
 // Every wait is bounded; a wait that runs out records an error bit, the CTA drains and
 // frees its TMEM before it returns.
 #include <algorithm>
@@ -36,9 +42,9 @@
 namespace tc {
 
 constexpr int kPfHD = 128;    // head_dim the kernel is built for
-constexpr int kPfBM = 128;    // query rows per CTA
-constexpr int kPfBN = 128;    // tokens per KV tile
-constexpr int kPfStages = 2;  // K and V ring depth
+constexpr int kPfBM = 128;    // query rows per tile (two tiles per CTA)
+constexpr int kPfBN = 64;     // tokens per KV tile
+constexpr int kPfStages = 4;  // K and V ring depth
 constexpr float kPfLazyLog2 = 8.0f;
 
 // f32 -> fp16 twins (the reference's kF32ToF16, GpuElementwiseKernels.hpp:92-101)
@@ -64,12 +70,15 @@ struct PrefillF16Params {
 };
 
 struct PrefillF16Smem {
-    static constexpr int kTile = kPfBM * kPfHD * 2;          // 32 KB: one 128x128 fp16 tile (two 64-column halves)
-    static constexpr int kQ = 0;                             // two query tiles
-    static constexpr int kK = 2 * kTile;
-    static constexpr int kV = kK + kPfStages * kTile;
-    static constexpr int kBars = kV + kPfStages * kTile;
-    static constexpr int kNumBars = 1 + 4 * kPfStages + 6;   // qFull, k/v full+empty, sFull[2], pFull[2], pvDone[2]
+    static constexpr int kQTile = kPfBM * kPfHD * 2;   // 32 KB: 128 x 128 fp16 as two 64-column halves
+    static constexpr int kKvTile = kPfBN * kPfHD * 2;  // 16 KB: 64 x 128 fp16 as two 64-column halves
+    static constexpr int kQ = 0;                       // two query tiles
+    static constexpr int kK01 = 2 * kQTile;            // K_0, K_1 (the products issued before the loop)
+    static constexpr int kStage = kK01 + 2 * kKvTile;  // stage s: K slot, then V slot
+    static constexpr int kStageBytes = 2 * kKvTile;
+    static constexpr int kBars = kStage + kPfStages * kStageBytes;
+    // qFull, k01Full, stage full + empty, sFull[2][2], pFull[2][2], pvDone[2]
+    static constexpr int kNumBars = 2 + 2 * kPfStages + 4 + 4 + 2;
     static constexpr int kTmemSlot = kBars + kNumBars * 8;
     static constexpr int kTotal = kTmemSlot + 16 + 1024;
 };
@@ -86,17 +95,50 @@ __device__ __forceinline__ bool pfWait(uint64_t *bar, uint32_t parity, unsigned 
     return false;
 }
 
-// 320 threads: warps 0-3 softmax of query tile A, warps 4-7 softmax of query tile B
-// (rows 128 further down), warp 8 TMA producer, warp 9 MMA issuer.
-__global__ void __launch_bounds__(320, 1)
+// 2^x for a pair of arguments on the FMA pipe instead of the special-function unit (which, at 16
+// results per clock and SM, is what bounds the softmax): x = n + f with n = round(x) through the
+// 1.5 * 2^23 trick, 2^f on [-0.5, 0.5] by a cubic (maximum relative error 1.0e-4, below the
+// 4.9e-4 of the fp16 rounding the probabilities get anyway), and n added into the exponent field.
+// Arguments are clamped at -126 so that masked (-inf) scores give 2^-126, i.e. nothing.
+__device__ __forceinline__ float2 exp2Poly2(float2 x) {
+    const float kMagic = 12582912.0f;  // 1.5 * 2^23
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    const float2 t = __fadd2_rn(x, make_float2(kMagic, kMagic));
+    const float2 n = __fadd2_rn(t, make_float2(-kMagic, -kMagic));
+    const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+    float2 pl = __ffma2_rn(f, make_float2(0.05500893f, 0.05500893f), make_float2(0.24221095f, 0.24221095f));
+    pl = __ffma2_rn(pl, f, make_float2(0.6932829f, 0.6932829f));
+    pl = __ffma2_rn(pl, f, make_float2(1.0f, 1.0f));
+    // (the magic constant's own bits vanish in the shift: its low 22 bits are zero)
+    return make_float2(__int_as_float(__float_as_int(pl.x) + (__float_as_int(t.x) << 23)),
+                       __int_as_float(__float_as_int(pl.y) + (__float_as_int(t.y) << 23)));
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// A matrix descriptor whose start address is moved by `bytes` (the address field holds
+// bytes >> 4 in its low 14 bits; shared memory is far smaller than their range, so the sum
+// never carries out of the field).
+__device__ __forceinline__ uint64_t descAdvance(uint64_t d, uint32_t bytes) { return d + (bytes >> 4); }
+
+// 352 threads: warps 0-3 softmax of query tile A, warps 4-7 softmax of query tile B
+// (rows 128 further down), warp 8 TMA producer, warps 9 and 10 MMA issuers of A and B.
+constexpr int kPfThreads = 352;
+__global__ void __launch_bounds__(kPfThreads, 1)
 prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const PrefillF16Params p) {
     using L = PrefillF16Smem;
+    constexpr uint32_t NS = kPfStages;
     extern __shared__ uint8_t smemRaw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::kBars);
-    uint64_t *qFull = bars, *kFull = bars + 1, *kEmpty = bars + 3, *vFull = bars + 5, *vEmpty = bars + 7,
-             *sFull = bars + 9, *pFull = bars + 11, *pvDone = bars + 13;
+    uint64_t *qFull = bars, *k01Full = bars + 1, *stFull = bars + 2, *stEmpty = stFull + NS,
+             *sFull = stEmpty + NS /* [x][b] */, *pFull = sFull + 4 /* [x][b] */, *pvDone = pFull + 4 /* [x] */;
     uint32_t *tmemSlot = reinterpret_cast<uint32_t *>(smem + L::kTmemSlot);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -105,22 +147,25 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t head = blockIdx.x % p.nHeads;
     const uint32_t kvHead = head / p.group;
     const uint32_t m0 = qb * 2u * kPfBM;
-    // query tile X (0 = A, 1 = B) sits on KV tile 2*qb + X; B may lie wholly past the sequence
+    // query tile X (0 = A, 1 = B) covers rows m0 + 128 X ..; it sees KV tiles 0 .. nX - 1 (64 tokens
+    // each; the last two straddle its diagonal).  B may lie wholly past the sequence.
     const bool activeB = m0 + kPfBM < p.seqLen;
-    const uint32_t qtA = 2u * qb, qtB = qtA + 1u;
-    const uint32_t nTiles = activeB ? qtB + 1u : qtA + 1u;
+    const uint32_t nA = 4u * qb + 2u, nB = activeB ? 4u * qb + 4u : 0u;
+    const uint32_t nTiles = activeB ? nB : nA;
 
     if (threadIdx.x == 0) {
         mbarInit(qFull, 1);
-        for (int s = 0; s < 2; ++s) {
-            mbarInit(&kFull[s], 1);
-            mbarInit(&kEmpty[s], 1);
-            mbarInit(&vFull[s], 1);
-            mbarInit(&vEmpty[s], 1);
-            mbarInit(&sFull[s], 1);
-            mbarInit(&pFull[s], 128);
-            mbarInit(&pvDone[s], 1);
+        mbarInit(k01Full, 1);
+        for (uint32_t s = 0; s < NS; ++s) {
+            mbarInit(&stFull[s], 1);
+            mbarInit(&stEmpty[s], 2);  // both MMA warps release a stage
         }
+        for (int i = 0; i < 4; ++i) {
+            mbarInit(&sFull[i], 1);
+            mbarInit(&pFull[i], 128);
+        }
+        mbarInit(&pvDone[0], 1);
+        mbarInit(&pvDone[1], 1);
         fenceBarrierInit();
         tmaPrefetchDesc(&tmQ);
         tmaPrefetchDesc(&tmK);
@@ -134,165 +179,191 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncthreads();
     tcFenceAfter();
     const uint32_t tmemBase = *reinterpret_cast<volatile uint32_t *>(tmemSlot);
-    // S of tile X at columns 128X (its fp16 probabilities overwrite the first 64 of them), O at 256 + 128X
+    // O of tile X at columns 128 X; S buffer b of tile X at 256 + 128 X + 64 b (its fp16
+    // probabilities overwrite the first 32 of those columns)
 
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            mbarExpectTx(qFull, 2 * L::kTile);
+            mbarExpectTx(qFull, 2 * L::kQTile);
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
-                tmaLoad3D(smem + L::kQ + x * L::kTile, &tmQ, qFull, 0, head, m0 + x * kPfBM);
-                tmaLoad3D(smem + L::kQ + x * L::kTile + L::kTile / 2, &tmQ, qFull, 64, head, m0 + x * kPfBM);
+                tmaLoad3D(smem + L::kQ + x * L::kQTile, &tmQ, qFull, 0, head, m0 + x * kPfBM);
+                tmaLoad3D(smem + L::kQ + x * L::kQTile + L::kQTile / 2, &tmQ, qFull, 64, head, m0 + x * kPfBM);
+            }
+            // K_0 and K_1 feed the products issued ahead of the loop (nTiles >= 2 always)
+            mbarExpectTx(k01Full, 2 * L::kKvTile);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                uint8_t *kd = smem + L::kK01 + j * L::kKvTile;
+                tmaLoad3D(kd, &tmK, k01Full, 0, kvHead, j * kPfBN);
+                tmaLoad3D(kd + L::kKvTile / 2, &tmK, k01Full, 64, kvHead, j * kPfBN);
             }
             for (uint32_t j = 0; j < nTiles; ++j) {
-                const uint32_t b = j & 1u;
-                if (j >= kPfStages && !pfWait(&kEmpty[b], ((j >> 1) - 1u) & 1u, p.err, kDevErrEmptyWait)) break;
-                uint8_t *kd = smem + L::kK + b * L::kTile;
-                mbarExpectTx(&kFull[b], L::kTile);
-                tmaLoad3D(kd, &tmK, &kFull[b], 0, kvHead, j * kPfBN);
-                tmaLoad3D(kd + L::kTile / 2, &tmK, &kFull[b], 64, kvHead, j * kPfBN);
-                if (j >= kPfStages && !pfWait(&vEmpty[b], ((j >> 1) - 1u) & 1u, p.err, kDevErrEmptyWait)) break;
-                uint8_t *vd = smem + L::kV + b * L::kTile;
-                mbarExpectTx(&vFull[b], L::kTile);
-                tmaLoad3D(vd, &tmV, &vFull[b], 0, kvHead, j * kPfBN);
-                tmaLoad3D(vd + L::kTile / 2, &tmV, &vFull[b], 64, kvHead, j * kPfBN);
+                const uint32_t s = j % NS;
+                if (j >= NS && !pfWait(&stEmpty[s], ((j / NS) - 1u) & 1u, p.err, kDevErrEmptyWait)) break;
+                uint8_t *kd = smem + L::kStage + s * L::kStageBytes, *vd = kd + L::kKvTile;
+                const bool withK = j + 2 < nTiles;
+                mbarExpectTx(&stFull[s], withK ? 2 * L::kKvTile : L::kKvTile);
+                if (withK) {
+                    tmaLoad3D(kd, &tmK, &stFull[s], 0, kvHead, (j + 2) * kPfBN);
+                    tmaLoad3D(kd + L::kKvTile / 2, &tmK, &stFull[s], 64, kvHead, (j + 2) * kPfBN);
+                }
+                tmaLoad3D(vd, &tmV, &stFull[s], 0, kvHead, j * kPfBN);
+                tmaLoad3D(vd + L::kKvTile / 2, &tmV, &stFull[s], 64, kvHead, j * kPfBN);
             }
         }
-    } else if (warp == 9) {
-        // ------------------------------- MMA issuer -------------------------------
-        // Order: S_A(0), S_B(0), then per KV tile j: [P_A(j)] O_A += P_A V, S_A(j+1); [P_B(j)] O_B += P_B V,
-        // S_B(j+1) -- while one tile's softmax runs, the tensor pipe works for the other tile.
-        if (lane == 0) {
-            constexpr uint32_t idQK = umaInstrDescF16(kPfBM, kPfBN, 0, 0);
-            constexpr uint32_t idPV = umaInstrDescF16(kPfBM, kPfHD, 0, 1);
-            auto tileOn = [&](uint32_t x, uint32_t j) { return x == 0 ? j <= qtA : (activeB && j <= qtB); };
-            auto issueQK = [&](uint32_t x, uint32_t j) {
-                const uint32_t qAddr = smemAddr(smem + L::kQ + x * L::kTile);
-                const uint32_t kAddr = smemAddr(smem + L::kK + (j & 1u) * L::kTile);
+    } else if (warp >= 9) {
+        // ------------------------------- MMA issuers -------------------------------
+        // Warp 9 + X issues for query tile X: S_X(0), S_X(1), then per KV tile j:
+        // [wait P_X(j)] O_X += P_X(j) V_j, S_X(j+2) -- the latter into the buffer P_X(j) occupies,
+        // hence behind its PV product (products of one thread execute in issue order).
+        // All 32 lanes run this warp-uniform code; only lane 0 executes the tcgen05 instructions.
+        const uint32_t x = warp - 9u;
+        const uint32_t issue = lane == 0 ? 1u : 0u;
+        const uint32_t myTiles = x == 0 ? nA : nB;
+        constexpr uint32_t idQK = umaInstrDescF16(kPfBM, kPfBN, 0, 0);
+        constexpr uint32_t idPV = umaInstrDescF16(kPfBM, kPfHD, 0, 1);
+        const uint64_t dQ = umaSmemDesc(smemAddr(smem + L::kQ + x * L::kQTile), 16, 1024);
+        const uint64_t dK01 = umaSmemDesc(smemAddr(smem + L::kK01), 16, 1024);
+        const uint64_t dKs = umaSmemDesc(smemAddr(smem + L::kStage), 16, 1024);
+        const uint64_t dVs = umaSmemDesc(smemAddr(smem + L::kStage + L::kKvTile), L::kKvTile / 2, 1024);
+        const uint32_t tO = tmemBase + 128u * x, tS0 = tmemBase + 256u + 128u * x;
+        auto issueQK = [&](uint64_t dK, uint32_t j) {
 #pragma unroll
-                for (uint32_t ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (ks >> 2) * (L::kTile / 2) + (ks & 3u) * 32u;
-                    umaMmaSS(tmemBase + 128u * x, umaSmemDesc(qAddr + off, 16, 1024), umaSmemDesc(kAddr + off, 16, 1024),
-                             idQK, ks > 0 ? 1u : 0u);
-                }
-                umaCommit(&sFull[x]);
-            };
-            bool ok = pfWait(qFull, 0, p.err, kDevErrFullWait) && pfWait(&kFull[0], 0, p.err, kDevErrFullWait);
-            if (ok) {
-                tcFenceAfter();
-                issueQK(0, 0);
-                if (tileOn(1, 0)) issueQK(1, 0);
-                umaCommit(&kEmpty[0]);
+            for (uint32_t ks = 0; ks < 8; ++ks) {
+                // k step ks: dims 16 ks .. +15 = 32 bytes inside the (ks >> 2)-th 64-dim half
+                umaMmaSSIf(issue, tS0 + 64u * (j & 1u), descAdvance(dQ, (ks >> 2) * (L::kQTile / 2) + (ks & 3u) * 32u),
+                           descAdvance(dK, (ks >> 2) * (L::kKvTile / 2) + (ks & 3u) * 32u), idQK, ks > 0 ? 1u : 0u);
             }
-            for (uint32_t j = 0; ok && j < nTiles; ++j) {
-                const uint32_t b = j & 1u;
-                const bool more = j + 1 < nTiles;
-                if (!pfWait(&vFull[b], (j >> 1) & 1u, p.err, kDevErrFullWait)) break;
-                if (more && !pfWait(&kFull[b ^ 1u], ((j + 1) >> 1) & 1u, p.err, kDevErrFullWait)) break;
-                const uint32_t vAddr = smemAddr(smem + L::kV + b * L::kTile);
-                for (uint32_t x = 0; x < 2 && ok; ++x) {
-                    if (!tileOn(x, j)) continue;
-                    if (!pfWait(&pFull[x], j & 1u, p.err, kDevErrMmaWait)) {
-                        ok = false;
-                        break;
-                    }
+            umaCommitIf(issue, &sFull[2u * x + (j & 1u)]);
+        };
+        bool ok = myTiles != 0 && pfWait(qFull, 0, p.err, kDevErrFullWait) && pfWait(k01Full, 0, p.err, kDevErrFullWait);
+        if (ok) {
+            tcFenceAfter();
+            issueQK(dK01, 0);
+            issueQK(descAdvance(dK01, L::kKvTile), 1);
+        }
+        // Every stage is released by both warps, also the ones past this tile's diagonal -- but
+        // only after the stage has been filled: a warp with nothing to do must not run ahead and
+        // hand in the release of a later round, or the barrier would complete without the warp
+        // that still reads the stage.
+        bool okFull = true;
+        for (uint32_t j = 0; j < nTiles; ++j) {
+            const uint32_t s = j % NS;
+            okFull = okFull && pfWait(&stFull[s], (j / NS) & 1u, p.err, kDevErrFullWait);
+            if (ok && okFull && j < myTiles) {
+                ok = pfWait(&pFull[2u * x + (j & 1u)], (j >> 1) & 1u, p.err, kDevErrMmaWait);
+                if (ok) {
                     tcFenceAfter();
+                    const uint64_t dV = descAdvance(dVs, s * L::kStageBytes);
+                    const uint32_t tP = tS0 + 64u * (j & 1u);
 #pragma unroll
-                    for (uint32_t ks = 0; ks < 8; ++ks)
-                        umaMmaTS(tmemBase + 256u + 128u * x, tmemBase + 128u * x + ks * 8u,
-                                 umaSmemDesc(vAddr + ks * 2048u, L::kTile / 2, 1024), idPV, (j > 0 || ks > 0) ? 1u : 0u);
-                    umaCommit(&pvDone[x]);
-                    if (more && tileOn(x, j + 1)) issueQK(x, j + 1);  // overwrites P_x(j): issued after its PV
+                    for (uint32_t ks = 0; ks < 4; ++ks)  // 16 tokens per step: 8 columns of fp16 P, 2 KB of V
+                        umaMmaTSIf(issue, tO, tP + ks * 8u, descAdvance(dV, ks * 2048u), idPV, (j > 0 || ks > 0) ? 1u : 0u);
+                    umaCommitIf(issue, &pvDone[x]);
+                    if (j + 2 < myTiles) issueQK(descAdvance(dKs, s * L::kStageBytes), j + 2);
                 }
-                umaCommit(&vEmpty[b]);
-                if (more) umaCommit(&kEmpty[b ^ 1u]);
             }
+            umaCommitIf(issue, &stEmpty[s]);
         }
     } else {
         // --------------------------------- softmax ---------------------------------
         const uint32_t x = warp >> 2;                         // which query tile this warpgroup owns
         const uint32_t row = (warp & 3u) * 32u + lane;        // row of that tile = TMEM lane
         const uint32_t laneBase = ((warp & 3u) * 32u) << 16;  // TMEM lane field
-        const uint32_t rq = m0 + x * kPfBM + row;             // query position
-        const uint32_t qt = x == 0 ? qtA : qtB;               // diagonal KV tile of this query tile
-        const uint32_t tS = tmemBase + 128u * x, tO = tmemBase + 256u + 128u * x;
+        const uint32_t rowInBlock = x * kPfBM + row;          // row inside the 256-row block
+        const uint32_t rq = m0 + rowInBlock;                  // query position
+        const uint32_t tO = tmemBase + 128u * x;
         float m = kNegBig, l = 0.0f;
-        bool ok = x == 0 || activeB;
-        const uint32_t myTiles = ok ? qt + 1u : 0u;
+        const uint32_t myTiles = x == 0 ? nA : nB;
+        bool ok = myTiles != 0;
         for (uint32_t j = 0; j < myTiles; ++j) {
-            if (!pfWait(&sFull[x], j & 1u, p.err, kDevErrMmaWait)) {
+            const uint32_t b = j & 1u;
+            const uint32_t tS = tmemBase + 256u + 128u * x + 64u * b;
+            if (!pfWait(&sFull[2u * x + b], (j >> 1) & 1u, p.err, kDevErrMmaWait)) {
                 ok = false;
                 break;
             }
             tcFenceAfter();
-            // the whole score row in registers: one TMEM pass per tile
-            uint32_t r[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmemLd32(tS + laneBase + c * 32u, r[c]);
+            uint32_t r[2][32];  // the 64 scores of this row
+            tmemLd32(tS + laneBase, r[0]);
+            tmemLd32(tS + laneBase + 32u, r[1]);
             tmemLdWait();
-            if (j == qt) {
-                // causal edge: column c of the diagonal tile is visible iff c <= row
+            if (j + 2u >= myTiles) {
+                // causal edge: token 64 j + c is visible iff it is not past the query position;
+                // relative to the block's first row that is 64 (j - 4 qb) + c <= rowInBlock
+                const int32_t first = 64 * (static_cast<int32_t>(j) - 4 * static_cast<int32_t>(qb));
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < 2; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (static_cast<uint32_t>(c * 32 + i) > row) r[c][i] = 0xff800000u;  // -inf
+                        if (first + c * 32 + i > static_cast<int32_t>(rowInBlock)) r[c][i] = 0xff800000u;  // -inf
             }
             float mxa = -INFINITY, mxb = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 2; ++c)
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    mxa = fmaxf(mxa, __uint_as_float(r[c][i]));
-                    mxb = fmaxf(mxb, __uint_as_float(r[c][i + 1]));
+                for (int i = 0; i < 32; i += 4) {
+                    mxa = max3(mxa, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+                    mxb = max3(mxb, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
                 }
             const float mx = fmaxf(mxa, mxb) * p.scaleLog2;  // scale > 0: max commutes with it
             const float mNew = mx > m + kPfLazyLog2 ? mx : m;
             const float alpha = fastExp2(m - mNew);
-            // O is stable once the previous tile's PV has completed
-            if (j > 0) {
+            const bool rescale = j > 0 && __any_sync(0xffffffffu, mNew != m);
+            // O may only be touched between two of its PV products: the previous one has to be
+            // complete (the next one cannot start before this thread publishes P).  The last
+            // step takes the wait in any case: a parity wait can only tell the current phase from
+            // the one before it, and the final wait below must not find the barrier two behind.
+            if (j > 0 && (rescale || j + 1u == myTiles)) {
                 if (!pfWait(&pvDone[x], (j - 1u) & 1u, p.err, kDevErrMmaWait)) {
                     ok = false;
                     break;
                 }
                 tcFenceAfter();
-                if (__any_sync(0xffffffffu, mNew != m)) {
+            }
+            if (rescale) {
 #pragma unroll 1
-                    for (uint32_t c = 0; c < 4; ++c) {
-                        uint32_t o[32];
-                        tmemLd32(tO + laneBase + c * 32u, o);
-                        tmemLdWait();
+                for (uint32_t c = 0; c < 4; ++c) {
+                    uint32_t o[32];
+                    tmemLd32(tO + laneBase + c * 32u, o);
+                    tmemLdWait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmemSt32(tO + laneBase + c * 32u, o);
-                    }
-                    tmemStWait();
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmemSt32(tO + laneBase + c * 32u, o);
                 }
+                tmemStWait();
             }
             m = mNew;
-            // probabilities as fp16 pairs, written over the first 64 columns of this tile's S:
-            // the A operand of the PV product (every score of the row is already in registers)
-            float suma = 0.0f, sumb = 0.0f;
+            // probabilities as fp16 pairs over the first 32 columns of this S buffer: the A
+            // operand of the PV product (every score of the row is already in registers)
+            // Pairs of elements with packed f32x2 arithmetic; every other pair takes its 2^x from
+            // the FMA pipe (exp2Poly2), the rest from the special-function unit, so that the two
+            // pipes share the work about evenly.
+            float2 sum2 = make_float2(0.0f, 0.0f);
+            const float2 scale2 = make_float2(p.scaleLog2, p.scaleLog2), negM2 = make_float2(-m, -m);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t h[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = fastExp2(fmaf(__uint_as_float(r[c][2 * i]), p.scaleLog2, -m));
-                    const float p1 = fastExp2(fmaf(__uint_as_float(r[c][2 * i + 1]), p.scaleLog2, -m));
-                    suma += p0;
-                    sumb += p1;
-                    h[i] = packHalf2(p0, p1);
+                    const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])),
+                                                 scale2, negM2);
+                    float2 p2;
+                    if (i & 1) p2 = exp2Poly2(x2);
+                    else p2 = make_float2(fastExp2(x2.x), fastExp2(x2.y));
+                    sum2 = __fadd2_rn(sum2, p2);
+                    h[i] = packHalf2(p2.x, p2.y);
                 }
                 tmemSt16(tS + laneBase + c * 16u, h);
             }
-            l = l * alpha + (suma + sumb);
+            l = l * alpha + (sum2.x + sum2.y);
             tmemStWait();
             tcFenceBefore();
-            mbarArrive(&pFull[x]);
+            mbarArrive(&pFull[2u * x + b]);
         }
-        if (ok && myTiles && pfWait(&pvDone[x], (myTiles - 1u) & 1u, p.err, kDevErrMmaWait)) {
+        if (ok && pfWait(&pvDone[x], (myTiles - 1u) & 1u, p.err, kDevErrMmaWait)) {
             tcFenceAfter();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             float *orow = p.out + (static_cast<size_t>(rq) * p.nHeads + head) * kPfHD;
@@ -319,7 +390,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
 }
 
-static int f16Map(const void *base, uint32_t heads, uint32_t rows, CUtensorMap *out) {
+static int f16Map(const void *base, uint32_t heads, uint32_t rows, uint32_t boxRows, CUtensorMap *out) {
     TensorMapKey key;
     memset(&key, 0, sizeof(key));
     key.base = base;
@@ -333,7 +404,7 @@ static int f16Map(const void *base, uint32_t heads, uint32_t rows, CUtensorMap *
     key.strides[1] = static_cast<uint64_t>(heads) * kPfHD * 2;
     key.box[0] = 64;  // 128 bytes: one swizzle span
     key.box[1] = 1;
-    key.box[2] = kPfBM;
+    key.box[2] = boxRows;
     return getTensorMap(key, out);
 }
 
@@ -391,11 +462,11 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     conv(kvV, v16, kvElems);
     TC_CUDA_OK(cudaGetLastError());
     CUtensorMap tmQ, tmK, tmV;
-    int rc = f16Map(q16, nHeads, seqLen, &tmQ);
+    int rc = f16Map(q16, nHeads, seqLen, kPfBM, &tmQ);
     if (rc != TC_OK) return rc;
-    rc = f16Map(k16, nKV, seqLen, &tmK);
+    rc = f16Map(k16, nKV, seqLen, kPfBN, &tmK);
     if (rc != TC_OK) return rc;
-    rc = f16Map(v16, nKV, seqLen, &tmV);
+    rc = f16Map(v16, nKV, seqLen, kPfBN, &tmV);
     if (rc != TC_OK) return rc;
     PrefillF16Params prm;
     prm.out = out;
@@ -415,7 +486,7 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
                                         PrefillF16Smem::kTotal));
         attrDone[dev] = true;
     }
-    prefillF16Kernel<<<nQTiles * nHeads, 320, PrefillF16Smem::kTotal, st>>>(tmQ, tmK, tmV, prm);
+    prefillF16Kernel<<<nQTiles * nHeads, kPfThreads, PrefillF16Smem::kTotal, st>>>(tmQ, tmK, tmV, prm);
     TC_CUDA_OK(cudaGetLastError());
     return TC_OK;
 }

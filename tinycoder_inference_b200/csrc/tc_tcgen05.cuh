@@ -71,6 +71,37 @@ __device__ __forceinline__ void umaMmaTS(uint32_t dTmem, uint32_t aTmem, uint64_
             ::"r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate)
             : "memory");
 }
+// The same two with an issue predicate: every lane of the issuing warp runs the surrounding
+// (warp-uniform) code so that descriptors and addresses stay uniform values, and only the lane
+// with `issue` != 0 executes the instruction itself.
+__device__ __forceinline__ void umaMmaSSIf(uint32_t issue, uint32_t dTmem, uint64_t aDesc, uint64_t bDesc,
+                                           uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "setp.ne.b32 q, %5, 0;\n\t"
+            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(dTmem), "l"(aDesc), "l"(bDesc), "r"(idesc), "r"(accumulate), "r"(issue)
+            : "memory");
+}
+__device__ __forceinline__ void umaMmaTSIf(uint32_t issue, uint32_t dTmem, uint32_t aTmem, uint64_t bDesc,
+                                           uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+            "{\n\t.reg .pred p, q;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "setp.ne.b32 q, %5, 0;\n\t"
+            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+            ::"r"(dTmem), "r"(aTmem), "l"(bDesc), "r"(idesc), "r"(accumulate), "r"(issue)
+            : "memory");
+}
+__device__ __forceinline__ void umaCommitIf(uint32_t issue, uint64_t *bar) {
+    asm volatile(
+            "{\n\t.reg .pred q;\n\t"
+            "setp.ne.b32 q, %1, 0;\n\t"
+            "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+            ::"r"(smemAddr(bar)), "r"(issue)
+            : "memory");
+}
 // mbarrier arrive once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umaCommit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smemAddr(bar))
