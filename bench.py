@@ -190,7 +190,11 @@ def run_reference(args):
                            "(CPU arm: a 32-row slice, f32)"}
         ms_scale = (2.0 * hd * nH * S * (S + 1)) / flops * layers
     else:
-        nH, nKV, hd, ctx, batch, layers = WORKLOADS[args.workload]
+        # sharded / ragged workloads: the CPU arm times one layer of their shape (the 131072-row
+        # sequence for the 32B workloads; one 32768-row sequence for the ragged mix)
+        wl = {"c4_heads": "c4_32b_128k", "c4_ctxsplit": "c4_32b_128k", "ragged64": "decode32k"}.get(args.workload,
+                                                                                                   args.workload)
+        nH, nKV, hd, ctx, batch, layers = WORKLOADS[wl]
         c = CpuAttention(nH, nKV, hd, ctx, 1)
         nbytes = algorithmic_bytes(nKV, hd, ctx)
         metric = ("decode_attn_kv_gbs_ctx32k" if args.workload == "decode32k"
@@ -198,7 +202,7 @@ def run_reference(args):
         unit = "GB/s"
         per_unit = lambda t: nbytes / t / 1e9  # noqa: E731
         sample = f"one layer of one sequence per step, f32 copy of the int8 store, ctx {ctx}; {c.how}"
-        cfg = workload_config(args.workload, args.gpus)
+        cfg = workload_config(wl, args.gpus)
         ms_scale = layers * batch
     one = c.time(1)
     # keep the whole run within a few minutes whatever K and W are
@@ -879,8 +883,12 @@ def main():
         "data": "synthetic", "config": workload_config(args.workload, world),
         "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": per_gpu_gbs / pk["hbm_gbs"], "peak_source": pk["source"],
-                     "traffic": None,
-                     "note": "algorithmic bytes per layer / (step time / layers); split and merge launches both inside"},
+                     # dram__bytes_read + write of one decodeI8Kernel launch, from the ncu capture
+                     # summarised in profiles/decode_i8_ctx32k_b1.md (34.65 MB read, 512 B written:
+                     # every KV byte leaves DRAM once); scaled by rows for the other decode shapes
+                     "traffic": 34650512.0 * (ctx * nKV * batch) / (32768.0 * 4.0),
+                     "note": "algorithmic bytes per layer / (step time / layers); split and merge launches both inside; "
+                             "traffic per launch from the committed ncu summary, not measured by this run"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms_per_step,
                 "h2d_bytes_per_step": layers * batch * (nH + 2 * nKV) * hd * 4,
                 "d2h_bytes_per_step": layers * batch * nH * hd * 4},
