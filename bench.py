@@ -374,7 +374,7 @@ def run_prefill(args):
         "e2e": {"value": world * layers * flops_layer / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": layers * (S * nH * hd + 2 * S * nKV * hd) * 4,
                 "d2h_bytes_per_step": layers * S * nH * hd * 4},
-        "gpu_launches": args.steps * layers * 5, "clocks": clocks, "device_error_flags": flags,
+        "gpu_launches": args.steps * layers * 3, "clocks": clocks, "device_error_flags": flags,
     }
     print(json.dumps(line), flush=True)
     if world > 1:

@@ -47,17 +47,31 @@ constexpr int kPfBN = 64;     // tokens per KV tile
 constexpr int kPfStages = 4;  // K and V ring depth
 constexpr float kPfLazyLog2 = 8.0f;
 
-// f32 -> fp16 twins (the reference's kF32ToF16, GpuElementwiseKernels.hpp:92-101)
+// f32 -> fp16 twins of q, K and V in ONE launch (the reference's kF32ToF16 x3,
+// GpuElementwiseKernels.hpp:92-101; GPUComputeForward.cu:3957-3968): the index space is the
+// concatenation of the three arrays, in units of four floats.
 __global__ void __launch_bounds__(256)
-f32ToF16Kernel(const float4 *__restrict__ x, uint2 *__restrict__ y, size_t n4) {
+f32ToF16x3Kernel(const float4 *__restrict__ q, const float4 *__restrict__ k, const float4 *__restrict__ v,
+                 uint2 *__restrict__ q16, uint2 *__restrict__ k16, uint2 *__restrict__ v16, size_t nq4, size_t nkv4) {
     size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (; i < n4; i += stride) {
-        const float4 v = __ldg(x + i);
+    const size_t total = nq4 + 2 * nkv4;
+    for (; i < total; i += stride) {
+        const float4 *src;
+        uint2 *dst;
+        size_t j;
+        if (i < nq4) {
+            src = q, dst = q16, j = i;
+        } else if (i < nq4 + nkv4) {
+            src = k, dst = k16, j = i - nq4;
+        } else {
+            src = v, dst = v16, j = i - nq4 - nkv4;
+        }
+        const float4 x = __ldg(src + j);
         uint2 o;
-        o.x = packHalf2(v.x, v.y);
-        o.y = packHalf2(v.z, v.w);
-        y[i] = o;
+        o.x = packHalf2(x.x, x.y);
+        o.y = packHalf2(x.z, x.w);
+        dst[j] = o;
     }
 }
 
@@ -452,14 +466,13 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     uint8_t *sc = static_cast<uint8_t *>(scratch);
     void *q16 = sc, *k16 = sc + al(qElems * 2), *v16 = sc + al(qElems * 2) + al(kvElems * 2);
     const int sms = numSMs();
-    auto conv = [&](const float *src, void *dst, size_t n) {
-        const size_t n4 = n / 4;
-        const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((n4 + 255) / 256, static_cast<size_t>(sms) * 8));
-        f32ToF16Kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float4 *>(src), static_cast<uint2 *>(dst), n4);
-    };
-    conv(q, q16, qElems);
-    conv(kvK, k16, kvElems);
-    conv(kvV, v16, kvElems);
+    {
+        const size_t nq4 = qElems / 4, nkv4 = kvElems / 4, total = nq4 + 2 * nkv4;
+        const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((total + 255) / 256, static_cast<size_t>(sms) * 16));
+        f32ToF16x3Kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float4 *>(q), reinterpret_cast<const float4 *>(kvK),
+                                                 reinterpret_cast<const float4 *>(kvV), static_cast<uint2 *>(q16),
+                                                 static_cast<uint2 *>(k16), static_cast<uint2 *>(v16), nq4, nkv4);
+    }
     TC_CUDA_OK(cudaGetLastError());
     CUtensorMap tmQ, tmK, tmV;
     int rc = f16Map(q16, nHeads, seqLen, kPfBM, &tmQ);
