@@ -547,7 +547,7 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     const uint64_t warpTiles32 = static_cast<uint64_t>(d->batch) * d->nKV * ((d->maxLen + 31) / 32);
     // (head_dim 256: a 32-token tile of K and V no longer leaves room for a second stage)
     const uint32_t mt = hd == 128 && warpTiles32 >= 2ull * 8ull * static_cast<uint64_t>(numSMs()) ? 2u : 1u;
-    const DecodePlan pl = planDecode(d->batch, d->nKV, d->maxLen, d->numChunks, 8u * 16u * mt);
+    const DecodePlan pl = planDecode(d->batch, d->nKV, d->maxLen, d->numChunks, 8u * 16u * mt, d->lens == nullptr);
     const bool pdl = (d->flags & TC_DECODE_PDL) != 0;
     const bool direct = pl.chunksPerSeq == 1 && !d->partialsOnly;
     if (!direct)
