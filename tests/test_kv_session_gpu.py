@@ -154,3 +154,54 @@ def test_window_guard_is_a_state_not_a_fault():
 def test_config_guards():
     with pytest.raises(capi.TcError):
         ops.KvSession(7, 2, 128, 64, 1)          # heads not a multiple of kv heads
+
+
+def test_decode_sequence_replayed_from_a_cuda_graph():
+    """The graph-safe decode sequence of the int8 store: quantise-append and attention read the
+    position from device memory, so ONE captured step replays for every token (the reference
+    cannot capture its int8 store path: the row counts live on the host)."""
+    e = Engine("i8", seed=11)
+    _check(*e.forward(33), "prompt before capture")
+    s = e.s
+    dq = torch.zeros((1, NH, HD), device="cuda")
+    dk = torch.zeros((SLOTS, 1, NKV, HD), device="cuda")
+    dv = torch.zeros_like(dk)
+    douts = torch.zeros((SLOTS, 1, NH, HD), device="cuda")
+    dpos = torch.tensor([s.pos], dtype=torch.int32, device="cuda")
+    qs = torch.zeros((SLOTS, 1, NH, HD), device="cuda")
+
+    def step():
+        for slot in range(SLOTS):
+            s.attend(slot, qs[slot], dk[slot], dv[slot], douts[slot], 0, dev_pos=dpos, graph_capture=True)
+        dpos.add_(1)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()                      # warm-up outside capture (writes row 33 with zeros, position -> 34)
+    torch.cuda.current_stream().wait_stream(side)
+    dpos.fill_(s.pos)               # back to the real position; the zero row is overwritten below
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    dpos.fill_(s.pos)               # capture does not execute
+    inv = 1.0 / math.sqrt(HD)
+    for t in range(4):
+        pos = s.begin(1)
+        rows = [e.rows(slot, pos, 1) for slot in range(SLOTS)]
+        for slot, (q, k, v) in enumerate(rows):
+            qs[slot].copy_(dev(q))
+            dk[slot].copy_(dev(k))
+            dv[slot].copy_(dev(v))
+        g.replay()
+        torch.cuda.synchronize()
+        assert int(dpos.item()) == pos + 1
+        for slot, (q, k, v) in enumerate(rows):
+            e.hist[slot][0].append(k)
+            e.hist[slot][1].append(v)
+            K, V = np.concatenate(e.hist[slot][0]), np.concatenate(e.hist[slot][1])
+            k8, v8, ks, vs = oracle.quant_kv8(K, V, NKV, HD)
+            want = oracle.attention_i8(q, k8, v8, ks, vs, 1, NH, NKV, HD, pos, inv)
+            assert_close(host(douts[slot]), want, what=f"graph replay {t}, slot {slot}")
+        s.commit(1)
+    assert ops.device_status() == 0
