@@ -824,27 +824,47 @@ def main():
     us_per_layer = ms_per_step * 1e3 / layers
 
     # ---- end to end through the C ABI with HOST buffers ---------------------------
-    # per layer: the new token's q, k, v come from pinned host memory, k/v are
-    # quantised and appended at the last row, attention runs, the result goes back
+    # A step: the new token's q, k, v of every layer come from pinned host memory (one
+    # asynchronous copy each), then per layer k/v are quantised and appended at the last row
+    # and attention runs (the captured launch sequence of the step), and the step's outputs go
+    # back to pinned host memory; the host waits for them.
     hq = torch.randn((layers, batch, nH, hd)).pin_memory()
     hk = torch.randn((layers, batch, nKV, hd)).pin_memory()
     hv = torch.randn((layers, batch, nKV, hd)).pin_memory()
     hout = torch.empty((layers, batch, nH, hd)).pin_memory()
-    dq = torch.empty((batch, nH, hd), device=dev)
-    dk = torch.empty((batch, nKV, hd), device=dev)
-    dv = torch.empty((batch, nKV, hd), device=dev)
-    dout = torch.empty((batch, nH, hd), device=dev)
+    dq = torch.empty((layers, batch, nH, hd), device=dev)
+    dk = torch.empty((layers, batch, nKV, hd), device=dev)
+    dv = torch.empty((layers, batch, nKV, hd), device=dev)
+    dout = torch.empty((layers, batch, nH, hd), device=dev)
+
+    def e2e_layers():
+        for l in range(layers):
+            ops.kv_quantize_i8_batch(dk[l], dv[l], k8[l], v8[l], ks[l], vs[l], batch, nKV, hd, rows_per_seq=rows,
+                                     pos=ctx - 1)
+            ops.decode_i8_batch(dq[l], k8[l], v8[l], ks[l], vs[l], dout[l], ws, lens_arg, batch, nH, nKV, hd, ctx,
+                                chunks, rows_per_seq=rows, invSqrt=inv, pdl=not args.no_pdl, prefetch_rows=ctx - 1)
+
+    if args.no_graph:
+        e2e_run = e2e_layers
+    else:
+        e2e_layers()
+        torch.cuda.synchronize()
+        s2 = torch.cuda.Stream()
+        s2.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s2):
+            e2e_layers()
+        torch.cuda.current_stream().wait_stream(s2)
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2):
+            e2e_layers()
+        e2e_run = g2.replay
 
     def e2e_step():
-        for l in range(layers):
-            dq.copy_(hq[l], non_blocking=True)
-            dk.copy_(hk[l], non_blocking=True)
-            dv.copy_(hv[l], non_blocking=True)
-            for b in range(batch):
-                ops.kv_quantize_i8(dk[b], dv[b], k8[l, b], v8[l, b], ks[l, b], vs[l, b], 1, nKV, hd, dst_base=ctx - 1)
-            ops.decode_i8_batch(dq, k8[l], v8[l], ks[l], vs[l], dout, ws, lens_arg, batch, nH, nKV, hd, ctx, chunks,
-                                rows_per_seq=rows, invSqrt=inv, pdl=not args.no_pdl, prefetch_rows=ctx - 1)
-            hout[l].copy_(dout, non_blocking=True)
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        e2e_run()
+        hout.copy_(dout, non_blocking=True)
         torch.cuda.synchronize()
 
     e2e_steps = max(3, min(args.steps, 50))

@@ -104,6 +104,18 @@ int tc_kv_quantize_i8(const float *k, const float *v, int8_t *k8, int8_t *v8,
                       const uint32_t *devDstBase, uint64_t maxRows,
                       tc_stream stream);
 
+/* The same quantiser for a batch of sequences that live in ONE pool (batched serving,
+ * the layout tc_attn_decode_i8_batch reads): k/v [batch][nKV][hd] hold the new token
+ * of every sequence; sequence b's row goes to
+ *   (rowBase ? rowBase[b] : b * rowsPerSeq) + (lens ? lens[b] + lenAdd : pos).
+ * lens / rowBase are device arrays (nullable).  With lens counting the new token
+ * already (as tc_attn_decode_i8_batch wants it) pass lenAdd = -1.  One launch. */
+int tc_kv_quantize_i8_batch(const float *k, const float *v, int8_t *k8, int8_t *v8,
+                            float *ks, float *vs, uint32_t batch, uint32_t nKV,
+                            uint32_t hd, uint64_t rowsPerSeq, const uint64_t *rowBase,
+                            uint32_t pos, const uint32_t *lens, int32_t lenAdd,
+                            uint64_t totalRows, tc_stream stream);
+
 /* ------------------------------------------------------------------------- */
 /* decode attention                                                            */
 /* ------------------------------------------------------------------------- */

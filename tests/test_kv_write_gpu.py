@@ -135,3 +135,44 @@ def test_cpu_engine_append_is_within_tolerance_of_gpu_form():
     oracle.kv_append(kSrc, kSrc, a, np.zeros_like(a), seqLen, nKV, hd, 3, 3, cosT, sinT)
     oracle.kv_append_cpu(kSrc, kSrc, b, np.zeros_like(b), seqLen, 3, nKV, hd, cosT, sinT)
     assert np.allclose(a, b, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_batched_quantise_appends_one_row_per_sequence():
+    """tc_kv_quantize_i8_batch: the new token of every sequence lands behind that sequence's rows,
+    with host position, device lengths and explicit row bases; bytes equal the oracle's."""
+    import oracle
+    B, nKV, hd, rps = 5, 4, 128, 40
+    rng = np.random.default_rng(77)
+    k = rng.standard_normal((B, nKV, hd), dtype=np.float32)
+    v = rng.standard_normal((B, nKV, hd), dtype=np.float32) * 2
+    want = oracle.quant_kv8(k, v, nKV, hd)
+
+    def fresh():
+        return (torch.zeros((B * rps, nKV, hd), dtype=torch.int8, device="cuda"),
+                torch.zeros((B * rps, nKV, hd), dtype=torch.int8, device="cuda"),
+                torch.zeros((B * rps, nKV), device="cuda"), torch.zeros((B * rps, nKV), device="cuda"))
+
+    def check_rows(pool, rows):
+        k8, v8, ks, vs = (host(t) for t in pool)
+        for b, r in enumerate(rows):
+            assert np.array_equal(k8[r], want[0][b]) and np.array_equal(v8[r], want[1][b])
+            assert np.array_equal(ks[r], want[2][b]) and np.array_equal(vs[r], want[3][b])
+        mask = np.ones(B * rps, bool)
+        mask[list(rows)] = False
+        assert not k8[mask].any() and not vs[mask].any(), "only the new rows are written"
+
+    pool = fresh()
+    ops.kv_quantize_i8_batch(dev(k), dev(v), *pool, B, nKV, hd, rows_per_seq=rps, pos=7)
+    check_rows(pool, [b * rps + 7 for b in range(B)])
+    lens = np.array([1, 40, 13, 2, 30], np.uint32)          # lengths that already count the new token
+    pool = fresh()
+    ops.kv_quantize_i8_batch(dev(k), dev(v), *pool, B, nKV, hd, rows_per_seq=rps, lens=dev(lens), len_add=-1)
+    check_rows(pool, [b * rps + int(lens[b]) - 1 for b in range(B)])
+    base = np.array([120, 0, 41, 81, 160], np.uint64)
+    pool = fresh()
+    ops.kv_quantize_i8_batch(dev(k), dev(v), *pool, B, nKV, hd, row_base=dev(base), lens=dev(lens), len_add=-1)
+    check_rows(pool, [int(base[b]) + int(lens[b]) - 1 for b in range(B)])
+    from tinycoder_inference_b200 import capi
+    with pytest.raises(capi.ContextFull):
+        ops.kv_quantize_i8_batch(dev(k), dev(v), *pool, B, nKV, hd, rows_per_seq=rps, pos=rps * 2)

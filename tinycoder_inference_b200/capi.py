@@ -164,6 +164,8 @@ SIGNATURES = {
                                _u32, _f, _i, _vp, _vp]),
     "tc_attn_merge_partials": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _vp]),
     "tc_attn_merge_gathered": (_i, [_vp, _vp, _u32, _u32, _u32, _u32, _vp]),
+    "tc_kv_quantize_i8_batch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u64, _vp, _u32, _vp, C.c_int32,
+                                    _u64, _vp]),
     "tc_kv_session_create": (_i, [C.POINTER(KvSessionConfig), C.POINTER(_vp)]),
     "tc_kv_session_destroy": (None, [_vp]),
     "tc_kv_session_clear": (_i, [_vp, _vp]),

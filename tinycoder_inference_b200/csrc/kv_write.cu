@@ -24,14 +24,22 @@ __global__ void __launch_bounds__(256)
 kvQuantKernel(const float *__restrict__ k, const float *__restrict__ v, int8_t *__restrict__ k8,
               int8_t *__restrict__ v8, float *__restrict__ ks, float *__restrict__ vs, uint32_t tokens,
               uint32_t nKV, uint32_t hd, uint64_t dstTokenBase, uint64_t srcTokenBase,
-              const uint32_t *__restrict__ devDstBase) {
+              const uint32_t *__restrict__ devDstBase, uint32_t batchMode, uint64_t rowsPerSeq,
+              const uint64_t *__restrict__ rowBase, const uint32_t *__restrict__ devLens, int32_t lenAdd) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint64_t row = static_cast<uint64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= static_cast<uint64_t>(tokens) * nKV) return;
     if (devDstBase != nullptr) dstTokenBase = devDstBase[0];
     const uint64_t t = row / nKV, h = row % nKV;
     const uint64_t src = ((srcTokenBase + t) * nKV + h) * hd;
-    const uint64_t dst = (dstTokenBase + t) * nKV + h;
+    uint64_t dst = (dstTokenBase + t) * nKV + h;
+    if (batchMode) {
+        // source row t is the new token of sequence t; it goes behind that sequence's rows
+        const uint64_t base = rowBase != nullptr ? rowBase[t] : t * rowsPerSeq;
+        const uint64_t pos = devLens != nullptr ? static_cast<uint64_t>(static_cast<int64_t>(devLens[t]) + lenAdd)
+                                                : dstTokenBase;
+        dst = (base + pos) * nKV + h;
+    }
     const uint32_t nvec = hd >> 2;
     float4 kx[MAXV], vx[MAXV];
     float mk = 0.0f, mv = 0.0f;
@@ -174,13 +182,46 @@ int tc_kv_quantize_i8(const float *k, const float *v, int8_t *k8, int8_t *v8, fl
     const uint32_t nvec = hd / 4;
     if (nvec <= 32)
         tc::kvQuantKernel<1><<<static_cast<uint32_t>(blocks), 256, 0, st>>>(
-                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase);
+                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase, 0u, 0ull, nullptr, nullptr, 0);
     else if (nvec <= 64)
         tc::kvQuantKernel<2><<<static_cast<uint32_t>(blocks), 256, 0, st>>>(
-                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase);
+                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase, 0u, 0ull, nullptr, nullptr, 0);
     else
         tc::kvQuantKernel<8><<<static_cast<uint32_t>(blocks), 256, 0, st>>>(
-                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase);
+                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase, 0u, 0ull, nullptr, nullptr, 0);
+    TC_CUDA_OK(cudaGetLastError());
+    return TC_OK;
+}
+
+int tc_kv_quantize_i8_batch(const float *k, const float *v, int8_t *k8, int8_t *v8, float *ks, float *vs,
+                            uint32_t batch, uint32_t nKV, uint32_t hd, uint64_t rowsPerSeq, const uint64_t *rowBase,
+                            uint32_t pos, const uint32_t *lens, int32_t lenAdd, uint64_t totalRows, tc_stream stream) {
+    TC_REQUIRE(k && v && k8 && v8 && ks && vs, TC_EINVAL, "tc_kv_quantize_i8_batch: null pointer");
+    TC_REQUIRE(nKV > 0 && hd > 0 && (hd % 4u) == 0 && hd <= 1024, TC_EUNSUPPORTED,
+               "tc_kv_quantize_i8_batch: hd=%u must be a multiple of 4 and <= 1024", hd);
+    TC_REQUIRE(((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15u) == 0 &&
+                       ((reinterpret_cast<uintptr_t>(k8) | reinterpret_cast<uintptr_t>(v8)) & 3u) == 0,
+               TC_EINVAL, "tc_kv_quantize_i8_batch: k/v need 16-byte, k8/v8 4-byte alignment");
+    if (batch == 0) return TC_OK;
+    if (lens == nullptr && rowBase == nullptr && totalRows != 0 &&
+        static_cast<uint64_t>(batch - 1) * rowsPerSeq + pos >= totalRows) {
+        tc::setError("tc_kv_quantize_i8_batch: row %u of sequence %u passes the pool's %llu rows", pos, batch - 1,
+                     (unsigned long long) totalRows);
+        return TC_ECONTEXT_FULL;
+    }
+    const uint64_t rows = static_cast<uint64_t>(batch) * nKV;
+    const uint32_t blocks = static_cast<uint32_t>((rows + 7) / 8);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint32_t nvec = hd / 4;
+    if (nvec <= 32)
+        tc::kvQuantKernel<1><<<blocks, 256, 0, st>>>(k, v, k8, v8, ks, vs, batch, nKV, hd, pos, 0, nullptr, 1u, rowsPerSeq,
+                                                     rowBase, lens, lenAdd);
+    else if (nvec <= 64)
+        tc::kvQuantKernel<2><<<blocks, 256, 0, st>>>(k, v, k8, v8, ks, vs, batch, nKV, hd, pos, 0, nullptr, 1u, rowsPerSeq,
+                                                     rowBase, lens, lenAdd);
+    else
+        tc::kvQuantKernel<8><<<blocks, 256, 0, st>>>(k, v, k8, v8, ks, vs, batch, nKV, hd, pos, 0, nullptr, 1u, rowsPerSeq,
+                                                     rowBase, lens, lenAdd);
     TC_CUDA_OK(cudaGetLastError());
     return TC_OK;
 }

@@ -40,6 +40,14 @@ def kv_quantize_i8(k, v, k8, v8, ks, vs, tokens, nKV, hd, dst_base=0, src_base=0
                                 dst_base, src_base, _ptr(dev_dst_base), max_rows, _stream()))
 
 
+def kv_quantize_i8_batch(k, v, k8, v8, ks, vs, batch, nKV, hd, rows_per_seq=0, row_base=None, pos=0, lens=None,
+                         len_add=0):
+    """The new token of every sequence of a batch into one pool, one launch."""
+    total = k8.numel() // (nKV * hd)
+    check(lib.tc_kv_quantize_i8_batch(_ptr(k), _ptr(v), _ptr(k8), _ptr(v8), _ptr(ks), _ptr(vs), batch, nKV, hd,
+                                      rows_per_seq, _ptr(row_base), pos, _ptr(lens), len_add, total, _stream()))
+
+
 def kv_append(kSrc, vSrc, kDst, vDst, seqLen, nKV, hd, cachePos, dev_pos=None):
     half = kDst.dtype == torch.float16
     max_rows = kDst.numel() // (nKV * hd)
