@@ -55,7 +55,8 @@ def test_qwen05b_shape(ctx):
 
 @pytest.mark.parametrize("nH,nKV,hd,ctx", [(28, 4, 128, 1000), (40, 8, 128, 777), (12, 2, 128, 300), (8, 8, 64, 200),
                                           (7, 1, 64, 90), (9, 3, 128, 33), (16, 4, 64, 4096),
-                                          (32, 2, 64, 400), (18, 2, 128, 200), (9, 1, 64, 150)])
+                                          (32, 2, 64, 400), (18, 2, 128, 200), (9, 1, 64, 150),
+                                          (16, 2, 256, 700), (8, 8, 256, 100), (24, 4, 256, 3000), (7, 1, 256, 33)])
 def test_shapes(nH, nKV, hd, ctx):
     _decode(nH, nKV, hd, ctx, numChunks=128, seed=nH + ctx)
 
@@ -149,7 +150,8 @@ def test_append_then_attend_fp16_cache():
 
 
 @pytest.mark.parametrize("S,nH,nKV,hd,cachePos", [(37, 14, 2, 64, 0), (8, 28, 4, 128, 100), (1, 14, 2, 64, 55),
-                                                 (129, 12, 2, 128, 17), (64, 8, 8, 64, 0)])
+                                                 (129, 12, 2, 128, 17), (64, 8, 8, 64, 0), (21, 8, 2, 256, 40),
+                                                 (70, 16, 4, 256, 0)])
 def test_causal_rows(S, nH, nKV, hd, cachePos):
     rng = np.random.default_rng(S + cachePos)
     rows = cachePos + S

@@ -367,7 +367,9 @@ static int launchKv(const CUtensorMap &tmK, const CUtensorMap &tmV, const Decode
 template <int HD, int NW>
 static int launchKvHpc(uint32_t hpc, const CUtensorMap &tmK, const CUtensorMap &tmV, const DecodeKvParams &prm,
                        dim3 grid, cudaStream_t st) {
-    if (hpc == 4) return launchKv<HD, NW, 4>(tmK, tmV, prm, grid, st);
+    if constexpr (NW % 4 == 0) {
+        if (hpc == 4) return launchKv<HD, NW, 4>(tmK, tmV, prm, grid, st);
+    }
     if (hpc == 2) return launchKv<HD, NW, 2>(tmK, tmV, prm, grid, st);
     return launchKv<HD, NW, 1>(tmK, tmV, prm, grid, st);
 }
@@ -397,8 +399,8 @@ static int kvMaps(const void *kvK, const void *kvV, uint32_t nKV, uint32_t hd, u
 static int kvCommonChecks(const char *who, const float *q, const void *kvK, const void *kvV, float *out,
                           uint32_t nHeads, uint32_t nKV, uint32_t hd, uint64_t totalRows, int kvHalf) {
     TC_REQUIRE(q && kvK && kvV && out, TC_EINVAL, "%s: null pointer", who);
-    (void) kvHalf;
-    TC_REQUIRE(hd == 64 || hd == 128, TC_EUNSUPPORTED, "%s: head_dim %u (built for 64 and 128)", who, hd);
+    TC_REQUIRE(hd == 64 || hd == 128 || (hd == 256 && !kvHalf), TC_EUNSUPPORTED,
+               "%s: head_dim %u (built for 64, 128 and -- f32 cache only -- 256)", who, hd);
     TC_REQUIRE(nKV > 0 && nHeads % nKV == 0, TC_EINVAL, "%s: nHeads %u not a multiple of nKV %u", who, nHeads, nKV);
     TC_REQUIRE(nHeads / nKV <= 64, TC_EUNSUPPORTED, "%s: %u q heads per kv head (built for <= 64)", who, nHeads / nKV);
     TC_REQUIRE(totalRows >= 1 && totalRows < (1ull << 31), TC_EUNSUPPORTED, "%s: cache of %llu rows", who,
@@ -425,7 +427,7 @@ static int prefillKv(const float *q, const void *kvK, const void *kvV, float *ou
     TC_REQUIRE(rowBlocks <= 65535 && nHeads <= 65535, TC_EUNSUPPORTED, "prefill_kv: %u rows x %u heads", seqLen, nHeads);
     if (kvHalf)
         return prefillKv16(q, kvK, kvV, out, seqLen, nHeads, nKV, hd, cachePos, devPos, totalRows, invSqrt, st);
-    const uint32_t nw = hd == 64 ? 8u : 4u;
+    const uint32_t nw = hd == 64 ? 8u : (hd == 128 ? 4u : 2u);  // consumer warps: 16 rows of K and V each per stage
     CUtensorMap tmK, tmV;
     rc = kvMaps(kvK, kvV, nKV, hd, totalRows, nw * 16u, &tmK, &tmV);
     if (rc != TC_OK) return rc;
@@ -449,6 +451,7 @@ static int prefillKv(const float *q, const void *kvK, const void *kvV, float *ou
     TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "prefill_kv: no device error word");
     dim3 grid(1, nHeads, rowBlocks);
     if (hd == 64) return launchKv<64, 8, 1>(tmK, tmV, prm, grid, st);
+    if (hd == 256) return launchKv<256, 2, 1>(tmK, tmV, prm, grid, st);
     return launchKv<128, 4, 1>(tmK, tmV, prm, grid, st);
 }
 
@@ -484,8 +487,8 @@ int tc_attn_decode_kv(const float *q, const void *kvK, const void *kvV, float *a
     if (kvHalf)
         return decodeKv16(q, kvK, kvV, attnOut, pAcc, pM, pL, nHeads, nKV, hd, pos, devPos, totalRows, numChunks,
                           invSqrt, q81Out, st);
-    const uint32_t nw = hd == 64 ? 8u : 4u;
-    DecodePlan pl = planDecode(1, nKV, pos + 1, numChunks, nw * 16u);
+    const uint32_t nw = hd == 64 ? 8u : (hd == 128 ? 4u : 2u);
+    DecodePlan pl = planDecode(1, nKV, pos + 1, numChunks, nw * 16u, true, nw >= 4u ? 4u : 2u);
     const bool direct = pl.chunksPerSeq == 1 && q81Out == nullptr;
     if (!direct) TC_REQUIRE(pAcc && pM && pL, TC_EWORKSPACE, "tc_attn_decode_kv: partial buffers are required");
     CUtensorMap tmK, tmV;
@@ -513,8 +516,9 @@ int tc_attn_decode_kv(const float *q, const void *kvK, const void *kvV, float *a
     dim3 grid(pl.chunksPerSeq, pl.headGroups, 1);
     for (uint32_t cb = 0; cb < prm.group; cb += 8) {  // 8 q heads of a kv head per launch
         prm.colBase = cb;
-        rc = hd == 64 ? launchKvHpc<64, 8>(pl.hpc, tmK, tmV, prm, grid, st)
-                      : launchKvHpc<128, 4>(pl.hpc, tmK, tmV, prm, grid, st);
+        rc = hd == 64    ? launchKvHpc<64, 8>(pl.hpc, tmK, tmV, prm, grid, st)
+             : hd == 128 ? launchKvHpc<128, 4>(pl.hpc, tmK, tmV, prm, grid, st)
+                         : launchKvHpc<256, 2>(pl.hpc, tmK, tmV, prm, grid, st);
         if (rc != TC_OK) return rc;
     }
     if (direct) return TC_OK;

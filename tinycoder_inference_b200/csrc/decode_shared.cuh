@@ -49,9 +49,9 @@ struct DecodePlan {
 // chunks let the hardware scheduler even things out (64 sequences in [512, 32768]: 182 us with
 // four waves, 186 with two, 324 with one).
 inline DecodePlan planDecode(uint32_t batch, uint32_t nKV, uint32_t maxLen, uint32_t slots, uint32_t rowsPerStage,
-                             bool uniformLengths = true) {
+                             bool uniformLengths = true, uint32_t maxHpc = 4) {
     DecodePlan pl;
-    pl.hpc = (nKV % 4u == 0) ? 4u : (nKV % 2u == 0 ? 2u : 1u);
+    pl.hpc = (nKV % 4u == 0 && maxHpc >= 4u) ? 4u : ((nKV % 2u == 0 && maxHpc >= 2u) ? 2u : 1u);
     pl.headGroups = nKV / pl.hpc;
     pl.tileTokens = rowsPerStage / pl.hpc;
     const uint32_t tilesMax = (maxLen + pl.tileTokens - 1) / pl.tileTokens;
