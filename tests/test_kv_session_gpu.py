@@ -20,17 +20,17 @@ NH, NKV, HD, SLOTS, WINDOW = 8, 2, 128, 2, 256
 class Engine:
     """A toy caller: every 'layer' gets its own seeded q/k/v rows per token."""
 
-    def __init__(self, mode, seed, rope=False, scratch_rows=0):
-        self.mode, self.seed = mode, seed
-        self.tables = oracle.rope_tables(WINDOW, HD, 1e6) if rope else None
+    def __init__(self, mode, seed, rope=False, scratch_rows=0, hd=HD):
+        self.mode, self.seed, self.hd = mode, seed, hd
+        self.tables = oracle.rope_tables(WINDOW, self.hd, 1e6) if rope else None
         rp = tuple(dev(t) for t in self.tables) if rope else None
-        self.s = ops.KvSession(NH, NKV, HD, WINDOW, SLOTS, mode=mode, rope=rp, prefill_scratch_rows=scratch_rows)
+        self.s = ops.KvSession(NH, NKV, self.hd, WINDOW, SLOTS, mode=mode, rope=rp, prefill_scratch_rows=scratch_rows)
         self.hist = [([], []) for _ in range(SLOTS)]     # what every slot's store should hold
 
     def rows(self, slot, pos, n):
         r = np.random.default_rng([self.seed, slot, pos])
-        return (r.standard_normal((n, NH, HD), dtype=np.float32), r.standard_normal((n, NKV, HD), dtype=np.float32),
-                r.standard_normal((n, NKV, HD), dtype=np.float32))
+        return (r.standard_normal((n, NH, self.hd), dtype=np.float32), r.standard_normal((n, NKV, self.hd), dtype=np.float32),
+                r.standard_normal((n, NKV, self.hd), dtype=np.float32))
 
     def forward(self, n, graph_capture=False, dev_pos=False):
         pos = self.s.begin(n)
@@ -38,28 +38,28 @@ class Engine:
         for slot in range(SLOTS):
             q, k, v = self.rows(slot, pos, n)
             dq = dev(q)
-            out = torch.full((n, NH, HD), float("nan"), device="cuda")
+            out = torch.full((n, NH, self.hd), float("nan"), device="cuda")
             dp = torch.tensor([pos], dtype=torch.int32, device="cuda") if dev_pos else None
             self.s.attend(slot, dq, dev(k), dev(v), out, pos, dev_pos=dp, graph_capture=graph_capture)
             if self.tables is not None:
-                q = oracle.rope_q(q, self.tables[0], self.tables[1], n, NH, HD, pos)
-                kk = np.zeros((pos + n, NKV, HD), np.float32)
+                q = oracle.rope_q(q, self.tables[0], self.tables[1], n, NH, self.hd, pos)
+                kk = np.zeros((pos + n, NKV, self.hd), np.float32)
                 vv = np.zeros_like(kk)
-                oracle.kv_append(k, v, kk, vv, n, NKV, HD, pos, ropePos=pos, cosT=self.tables[0], sinT=self.tables[1])
+                oracle.kv_append(k, v, kk, vv, n, NKV, self.hd, pos, ropePos=pos, cosT=self.tables[0], sinT=self.tables[1])
                 k = kk[pos:]
                 assert np.array_equal(host(dq), q), "q is rotated in place"
             self.hist[slot][0].append(k)
             self.hist[slot][1].append(v)
             K = np.concatenate(self.hist[slot][0])
             V = np.concatenate(self.hist[slot][1])
-            inv = 1.0 / math.sqrt(HD)
+            inv = 1.0 / math.sqrt(self.hd)
             if self.mode == "i8" or (self.mode == "f32+i8" and n == 1 and not graph_capture and not dev_pos):
-                k8, v8, ks, vs = oracle.quant_kv8(K, V, NKV, HD)
-                want = oracle.attention_i8(q, k8, v8, ks, vs, n, NH, NKV, HD, pos, inv)
+                k8, v8, ks, vs = oracle.quant_kv8(K, V, NKV, self.hd)
+                want = oracle.attention_i8(q, k8, v8, ks, vs, n, NH, NKV, self.hd, pos, inv)
             elif self.mode == "f16":
-                want = oracle.attention_kv(q, K.astype(np.float16), V.astype(np.float16), n, NH, NKV, HD, pos, inv)
+                want = oracle.attention_kv(q, K.astype(np.float16), V.astype(np.float16), n, NH, NKV, self.hd, pos, inv)
             else:
-                want = oracle.attention_kv(q, K, V, n, NH, NKV, HD, pos, inv)
+                want = oracle.attention_kv(q, K, V, n, NH, NKV, self.hd, pos, inv)
             outs.append(host(out))
             wants.append(want)
         self.s.commit(n)
@@ -99,6 +99,19 @@ def test_prefill_then_decode_then_a_second_conversation(mode):
     # a follow-up chunk after decoded tokens reads the whole history
     _check(*e.forward(5), f"{mode}: follow-up rows")
     _check(*e.forward(1), f"{mode}: decode after the follow-up")
+
+
+@pytest.mark.parametrize("mode", ["f32+i8", "i8", "f32"])
+def test_gated_model_shape_head_dim_256(mode):
+    """The reference's own int8 shape: f32 store + int8 decode pool (or int8 store) at head_dim 256."""
+    e = Engine(mode, seed=21, hd=256)
+    _check(*e.forward(45), f"{mode} hd256: prompt")
+    for t in range(2):
+        _check(*e.forward(1), f"{mode} hd256: decode {t}")
+    if mode != "f32":
+        assert e.s.rows8(0) == 47 and e.s.rows8(1) == 47
+    _check(*e.forward(3), f"{mode} hd256: follow-up rows")
+    _check(*e.forward(1), f"{mode} hd256: decode after the follow-up")
 
 
 @pytest.mark.parametrize("mode", ["f32", "i8"])
