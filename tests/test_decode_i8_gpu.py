@@ -208,7 +208,9 @@ def test_dependent_launch_chain_and_host_lengths():
         assert ops.device_status() == 0
         assert_close(host(out), want, what=f"pdl={pdl}")
         outs[pdl] = out
-    assert torch.equal(outs[False], outs[True])
+    # the two launch forms use different merge kernels (block per head / 32-dim slices): same rule,
+    # different summation order
+    assert torch.allclose(outs[False], outs[True], rtol=1e-5, atol=1e-6)
 
 
 def test_context_split_partials_merge_on_one_gpu():

@@ -190,6 +190,124 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
     }
 }
 
+// The same merge cut into 32-dim slices: grid (head, token, hd / 32), so that the accumulator
+// rows a block has to pull through one SM's L2 port shrink from chunks x hd floats to
+// chunks x 32 (at 128 chunks x 128 dims that is 64 KB against 16 KB; the merge sits on the
+// critical path of a batch-1 decode step and is pure latency).  Thread t owns float4 t % 8 of
+// the slice and the chunks t / 8, t / 8 + 32, ...; (m, l) and the weights are recomputed by every
+// slice's block -- a few hundred bytes.  No Q8_1 epilogue here (that needs the whole head).
+__global__ void __launch_bounds__(256)
+mergeSliceKernel(const float *__restrict__ pAcc, const float *__restrict__ pM, const float *__restrict__ pL,
+                 float *__restrict__ out, uint32_t nHeads, uint32_t numChunks, uint32_t activeHost, uint32_t hd,
+                 const uint32_t *__restrict__ devLens, uint32_t lenAdd, uint32_t chunkTokens, uint32_t chunksPerRank,
+                 uint64_t rankStride) {
+    constexpr int NW = 8;
+    const uint32_t head = blockIdx.x, s = blockIdx.y, slice = blockIdx.z;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t v4 = threadIdx.x & 7u, cl = threadIdx.x >> 3;
+    const uint64_t headRow = static_cast<uint64_t>(s) * nHeads + head;
+    auto mlOff = [&](uint32_t c) -> uint64_t {
+        if (rankStride == 0) return headRow * numChunks + c;
+        const uint32_t r = c / chunksPerRank;
+        return static_cast<uint64_t>(r) * rankStride + headRow * chunksPerRank + (c - r * chunksPerRank);
+    };
+    auto accOff = [&](uint32_t c) -> uint64_t {
+        if (rankStride == 0) return (headRow * numChunks + c) * hd;
+        const uint32_t r = c / chunksPerRank;
+        return static_cast<uint64_t>(r) * rankStride + (headRow * chunksPerRank + (c - r * chunksPerRank)) * hd;
+    };
+    gridDepLaunch();
+    gridDepWait();
+    uint32_t active = activeHost < numChunks ? activeHost : numChunks;
+    if (devLens != nullptr) {
+        const uint32_t len = devLens[s] + lenAdd;
+        const uint32_t need = (len + chunkTokens - 1) / chunkTokens;
+        active = need < numChunks ? need : numChunks;
+    }
+    __shared__ float sw[kMergeMaxChunks], sl[kMergeMaxChunks];
+    __shared__ float sred[NW];
+    __shared__ float4 sacc[NW][8];
+
+    constexpr int kB = 8;  // 8 x 32 chunk lanes = 256 chunks per batch
+    float4 a[kB];
+    auto loadBatch = [&](uint32_t c0) {
+#pragma unroll
+        for (int u = 0; u < kB; ++u) {
+            const uint32_t c = c0 + cl + 32u * u;
+            const uint32_t cc = c < active ? c : (active ? active - 1 : 0);  // always a valid address
+            a[u] = reinterpret_cast<const float4 *>(pAcc + accOff(cc) + 32u * slice)[v4];
+        }
+    };
+    if (active) loadBatch(0);
+    float M = kNegBig;
+    for (uint32_t c = threadIdx.x; c < active; c += 256) {
+        const float m = pM[mlOff(c)];
+        sw[c] = m;
+        sl[c] = pL[mlOff(c)];
+        M = fmaxf(M, m);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) sred[warp] = M;
+    __syncthreads();
+    M = sred[0];
+#pragma unroll
+    for (int w2 = 1; w2 < NW; ++w2) M = fmaxf(M, sred[w2]);
+    __syncthreads();
+    float lsum = 0.0f;
+    for (uint32_t c = threadIdx.x; c < active; c += 256) {
+        const float lc = sl[c];
+        const float w = lc > 0.0f ? exp2f((sw[c] - M) * kLog2e) : 0.0f;
+        sw[c] = w;
+        lsum = fmaf(w, lc > 0.0f ? lc : 0.0f, lsum);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+    if (lane == 0) sred[warp] = lsum;
+    __syncthreads();  // also publishes the weights
+    lsum = 0.0f;
+#pragma unroll
+    for (int w2 = 0; w2 < NW; ++w2) lsum += sred[w2];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t c0 = 0; c0 < active; c0 += 32u * kB) {
+        if (c0) loadBatch(c0);
+#pragma unroll
+        for (int u = 0; u < kB; ++u) {
+            const uint32_t c = c0 + cl + 32u * u;
+            const float w = c < active ? sw[c < active ? c : 0] : 0.0f;
+            const float4 v = w != 0.0f ? a[u] : make_float4(0.f, 0.f, 0.f, 0.f);  // empty chunk: select, never multiply
+            acc.x = fmaf(w, v.x, acc.x);
+            acc.y = fmaf(w, v.y, acc.y);
+            acc.z = fmaf(w, v.z, acc.z);
+            acc.w = fmaf(w, v.w, acc.w);
+        }
+    }
+    // a warp holds 4 chunk lanes x 8 float4: fold the chunk lanes, then the warps
+#pragma unroll
+    for (int o = 8; o <= 16; o <<= 1) {
+        acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
+        acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
+        acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
+        acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
+    }
+    if (lane < 8) sacc[warp][lane] = acc;
+    __syncthreads();
+    if (threadIdx.x < 8) {
+        float4 r = sacc[0][threadIdx.x];
+#pragma unroll
+        for (int w2 = 1; w2 < NW; ++w2) {
+            const float4 x = sacc[w2][threadIdx.x];
+            r.x += x.x;
+            r.y += x.y;
+            r.z += x.z;
+            r.w += x.w;
+        }
+        const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
+        reinterpret_cast<float4 *>(out + headRow * hd + 32u * slice)[threadIdx.x] =
+                make_float4(r.x * inv, r.y * inv, r.z * inv, r.w * inv);
+    }
+}
+
 int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out, uint32_t seqLen,
                 uint32_t nHeads, uint32_t numChunks, uint32_t activeHost, uint32_t hd, const uint32_t *devLens,
                 uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st,
@@ -204,6 +322,16 @@ int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
+    // In plain stream order the sliced form is faster (batch-1 decode step at ctx 32768: 13.7 us per
+    // layer against 15.0); under programmatic dependent launch its 4x as many blocks are resident next
+    // to the decode blocks they wait for and the step gets slower (13.5 against 13.0), so that path
+    // keeps the block-per-head form.
+    if (q81 == nullptr && !pdl) {
+        cfg.gridDim = dim3(nHeads, seqLen, hd / 32u);
+        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, mergeSliceKernel, pAcc, pM, pL, out, nHeads, numChunks, activeHost, hd,
+                                      devLens, lenAdd, chunkTokens, chunksPerRank, rankStride));
+        return TC_OK;
+    }
     if (hd <= 128)
         TC_CUDA_OK(cudaLaunchKernelEx(&cfg, mergePartialsKernel<1>, pAcc, pM, pL, out, nHeads, numChunks,
                                       activeHost, hd, devLens, lenAdd, chunkTokens, q81, chunksPerRank, rankStride));
