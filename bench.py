@@ -410,7 +410,8 @@ def quick_decode(name, dev, steps=20, warmup=5):
     def step():
         for l in range(layers):
             ops.decode_i8_batch(q[l], k8[l], v8[l], ks[l], vs[l], out[l], ws, None, batch, nH, nKV, hd, ctx, chunks,
-                                rows_per_seq=rows, invSqrt=inv, pdl=True, prefetch_rows=ctx - 1)
+                                rows_per_seq=rows, invSqrt=inv, pdl=True, prefetch_rows=ctx - 1,
+                                next_kv=(k8[(l + 1) % layers], v8[(l + 1) % layers]))
 
     step()
     torch.cuda.synchronize()
@@ -696,6 +697,8 @@ def main():
     ap.add_argument("--workload", default="decode32k", choices=sorted(WORKLOADS) + ["prefill4k", "c4_heads", "c4_ctxsplit", "ragged64"])
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="c4_ctxsplit: partials exchanged by the library's own kernel over peer memory, or by NCCL")
+    ap.add_argument("--no-next-prefetch", action="store_true",
+                    help="do not hint the next layer's pools to the decode call (L2 prefetch while a layer drains)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary batch-8 measurement of the default line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -757,9 +760,10 @@ def main():
     def step(pdl):
         # rows [0, ctx-1) are old rows; the last row is the one a decode step appends
         for l in range(layers):
+            nxt = None if args.no_next_prefetch else (k8[(l + 1) % layers], v8[(l + 1) % layers])
             ops.decode_i8_batch(q[l], k8[l], v8[l], ks[l], vs[l], out[l], ws, lens_arg, batch, nH, nKV, hd, ctx,
                                 chunks, rows_per_seq=rows, invSqrt=inv, pdl=pdl, prefetch_rows=ctx - 1,
-                                partials_only=args.partials_only)
+                                partials_only=args.partials_only, next_kv=nxt)
 
     launches_per_step = layers * 2
     step(False)
@@ -841,8 +845,10 @@ def main():
         for l in range(layers):
             ops.kv_quantize_i8_batch(dk[l], dv[l], k8[l], v8[l], ks[l], vs[l], batch, nKV, hd, rows_per_seq=rows,
                                      pos=ctx - 1)
+            nxt = None if args.no_next_prefetch else (k8[(l + 1) % layers], v8[(l + 1) % layers])
             ops.decode_i8_batch(dq[l], k8[l], v8[l], ks[l], vs[l], dout[l], ws, lens_arg, batch, nH, nKV, hd, ctx,
-                                chunks, rows_per_seq=rows, invSqrt=inv, pdl=not args.no_pdl, prefetch_rows=ctx - 1)
+                                chunks, rows_per_seq=rows, invSqrt=inv, pdl=not args.no_pdl, prefetch_rows=ctx - 1,
+                                next_kv=nxt)
 
     if args.no_graph:
         e2e_run = e2e_layers

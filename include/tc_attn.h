@@ -185,6 +185,14 @@ typedef struct tc_decode_i8_batch {
      * long) and rowBase == NULL.  flags == 0 keeps plain stream order. */
     uint32_t flags;
     uint32_t prefetchRows;
+    /* Optional hint (NULL = none): the int8 pools the NEXT decode call on this stream
+     * will read with the same geometry and lengths -- the next layer's slot.  Once a
+     * block has requested its own last tile it asks the memory system to pull the
+     * same rows of these pools into L2 (cp.async.bulk.prefetch.tensor), so DRAM keeps
+     * streaming while this call's blocks fold their partials and the merge runs,
+     * instead of idling until the next call's blocks start.  Nothing is read or
+     * written through these pointers by the SMs. */
+    const int8_t *nextK8, *nextV8;
 } tc_decode_i8_batch;
 
 enum { TC_DECODE_PDL = 1u };

@@ -213,6 +213,28 @@ def test_dependent_launch_chain_and_host_lengths():
     assert torch.allclose(outs[False], outs[True], rtol=1e-5, atol=1e-6)
 
 
+def test_next_pool_hint_changes_nothing_but_timing():
+    """nextK8 / nextV8 only ask for an L2 prefetch of another pool: same bits out."""
+    nH, nKV, hd, ctx, C = 28, 4, 128, 9000, 160
+    rng = np.random.default_rng(41)
+    q = rng.standard_normal((1, nH, hd), dtype=np.float32)
+    k8, v8, ks, vs = make_i8_store(rng.standard_normal((ctx, nKV, hd), dtype=np.float32),
+                                   rng.standard_normal((ctx, nKV, hd), dtype=np.float32), nKV, hd)
+    other_k = torch.randint(-128, 127, (ctx, nKV, hd), dtype=torch.int8, device="cuda")
+    other_v = torch.randint(-128, 127, (ctx, nKV, hd), dtype=torch.int8, device="cuda")
+    dq, dk8, dv8, dks, dvs = dev(q), dev(k8), dev(v8), dev(ks), dev(vs)
+    ws = ops.workspace(1, nH, hd, C)
+    a = torch.empty((1, nH, hd), device="cuda")
+    b = torch.empty_like(a)
+    ops.decode_i8_batch(dq, dk8, dv8, dks, dvs, a, ws, None, 1, nH, nKV, hd, ctx, C)
+    ops.decode_i8_batch(dq, dk8, dv8, dks, dvs, b, ws, None, 1, nH, nKV, hd, ctx, C, next_kv=(other_k, other_v))
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert torch.equal(a, b)
+    want = oracle.attention_i8(q, k8, v8, ks, vs, 1, nH, nKV, hd, ctx - 1, 1.0 / math.sqrt(hd))
+    assert_close(host(b), want, what="decode with a next-pool hint")
+
+
 def test_context_split_partials_merge_on_one_gpu():
     """The context-axis split as two 'ranks' on one device: each half of the rows yields
     partials-only output, the partials are concatenated as the all-gather would and merged."""

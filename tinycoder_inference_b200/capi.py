@@ -139,6 +139,8 @@ class DecodeI8Batch(C.Structure):
         ("chunksUsed", C.POINTER(C.c_uint32)),
         ("flags", C.c_uint32),
         ("prefetchRows", C.c_uint32),
+        ("nextK8", C.c_void_p),
+        ("nextV8", C.c_void_p),
     ]
 
 

@@ -53,6 +53,7 @@ struct DecodeI8Params {
     const uint32_t *devPos;
     float invSqrt;
     int directOut;
+    int prefetchNext;  // tmKn / tmVn describe the pools of the next call: pull this block's rows of them into L2
     unsigned int *err;
 };
 
@@ -88,6 +89,7 @@ constexpr uint32_t kEarlyStages = 1;
 template <int HD, int HPC, int NW, int NSTAGE, int MT>
 __global__ void __launch_bounds__((NW + 1) * 32, 1)
 decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+               const __grid_constant__ CUtensorMap tmKn, const __grid_constant__ CUtensorMap tmVn,
                const DecodeI8Params p) {
     using L = DecodeI8Smem<HD, HPC, NW, NSTAGE, MT>;
     constexpr int T = L::T;
@@ -183,6 +185,21 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                 cpAsync4(&sV[idx], p.vs + r * p.nKV + kvHead0 + h);
             }
             cpAsyncMbarArriveNoinc(&fullBar[s]);
+        }
+        if (p.prefetchNext && lane == 0) {
+            // This block's own tiles are all requested.  DRAM would now idle through the fold, the
+            // merge and the next call's start-up: have it fetch the same rows of the next call's
+            // pools into L2 meanwhile (the next call's TMA loads then hit L2).
+            for (uint32_t it = 0; it < nTiles; ++it) {
+                const int row = static_cast<int>(rowBase + t0 + it * T);
+#pragma unroll
+                for (int h = 0; h < HPC; ++h)
+#pragma unroll
+                    for (int hf = 0; hf < HD / 128; ++hf) {
+                        tmaPrefetchL2_3D(&tmKn, hf * 128, kvHead0 + h, row);
+                        tmaPrefetchL2_3D(&tmVn, hf * 128, kvHead0 + h, row);
+                    }
+            }
         }
         return;
     }
@@ -498,8 +515,9 @@ decodeI8Kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 }
 
 template <int HD, int HPC, int MT>
-static int launchDecodeI8(const CUtensorMap &tmK, const CUtensorMap &tmV, const DecodeI8Params &prm,
-                          const DecodePlan &pl, uint32_t batch, bool pdl, cudaStream_t st) {
+static int launchDecodeI8(const CUtensorMap &tmK, const CUtensorMap &tmV, const CUtensorMap &tmKn,
+                          const CUtensorMap &tmVn, const DecodeI8Params &prm, const DecodePlan &pl, uint32_t batch,
+                          bool pdl, cudaStream_t st) {
     constexpr int NW = 8, NSTAGE = (MT == 2 || HD == 256) ? 3 : 6;
     using L = DecodeI8Smem<HD, HPC, NW, NSTAGE, MT>;
     static_assert(L::kTotal <= 227 * 1024, "stage ring exceeds the shared memory of an SM");
@@ -521,7 +539,7 @@ static int launchDecodeI8(const CUtensorMap &tmK, const CUtensorMap &tmV, const 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    TC_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tmK, tmV, prm));
+    TC_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, tmK, tmV, tmKn, tmVn, prm));
     return TC_OK;
 }
 
@@ -574,6 +592,19 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     key.base = d->v8;
     rc = getTensorMap(key, &tmV);
     if (rc != TC_OK) return rc;
+    // the pools of the next call, for the L2 prefetch hint (same geometry)
+    CUtensorMap tmKn = tmK, tmVn = tmV;
+    const bool prefetchNext = d->nextK8 != nullptr && d->nextV8 != nullptr;
+    if (prefetchNext) {
+        TC_REQUIRE(((reinterpret_cast<uintptr_t>(d->nextK8) | reinterpret_cast<uintptr_t>(d->nextV8)) & 15u) == 0,
+                   TC_EINVAL, "decode_i8: nextK8/nextV8 need 16-byte alignment");
+        key.base = d->nextK8;
+        rc = getTensorMap(key, &tmKn);
+        if (rc != TC_OK) return rc;
+        key.base = d->nextV8;
+        rc = getTensorMap(key, &tmVn);
+        if (rc != TC_OK) return rc;
+    }
 
     DecodeI8Params prm;
     prm.q = d->q;
@@ -601,6 +632,7 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     prm.devPos = nullptr;
     prm.invSqrt = d->invSqrt;
     prm.directOut = direct ? 1 : 0;
+    prm.prefetchNext = prefetchNext ? 1 : 0;
     prm.err = devErrorWord();
     TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "decode_i8: no device error word");
 
@@ -609,17 +641,17 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     for (uint32_t cb = 0; cb < group; cb += 8) {
         prm.colBase = cb;
         if (hd == 256) {
-            if (pl.hpc == 4) rc = launchDecodeI8<256, 4, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-            else if (pl.hpc == 2) rc = launchDecodeI8<256, 2, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-            else rc = launchDecodeI8<256, 1, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+            if (pl.hpc == 4) rc = launchDecodeI8<256, 4, 1>(tmK, tmV, tmKn, tmVn, prm, pl, d->batch, pdl, st);
+            else if (pl.hpc == 2) rc = launchDecodeI8<256, 2, 1>(tmK, tmV, tmKn, tmVn, prm, pl, d->batch, pdl, st);
+            else rc = launchDecodeI8<256, 1, 1>(tmK, tmV, tmKn, tmVn, prm, pl, d->batch, pdl, st);
         } else if (mt == 2) {
-            if (pl.hpc == 4) rc = launchDecodeI8<128, 4, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
-            else if (pl.hpc == 2) rc = launchDecodeI8<128, 2, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
-            else rc = launchDecodeI8<128, 1, 2>(tmK, tmV, prm, pl, d->batch, pdl, st);
+            if (pl.hpc == 4) rc = launchDecodeI8<128, 4, 2>(tmK, tmV, tmKn, tmVn, prm, pl, d->batch, pdl, st);
+            else if (pl.hpc == 2) rc = launchDecodeI8<128, 2, 2>(tmK, tmV, tmKn, tmVn, prm, pl, d->batch, pdl, st);
+            else rc = launchDecodeI8<128, 1, 2>(tmK, tmV, tmKn, tmVn, prm, pl, d->batch, pdl, st);
         } else {
-            if (pl.hpc == 4) rc = launchDecodeI8<128, 4, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-            else if (pl.hpc == 2) rc = launchDecodeI8<128, 2, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
-            else rc = launchDecodeI8<128, 1, 1>(tmK, tmV, prm, pl, d->batch, pdl, st);
+            if (pl.hpc == 4) rc = launchDecodeI8<128, 4, 1>(tmK, tmV, tmKn, tmVn, prm, pl, d->batch, pdl, st);
+            else if (pl.hpc == 2) rc = launchDecodeI8<128, 2, 1>(tmK, tmV, tmKn, tmVn, prm, pl, d->batch, pdl, st);
+            else rc = launchDecodeI8<128, 1, 1>(tmK, tmV, tmKn, tmVn, prm, pl, d->batch, pdl, st);
         }
         if (rc != TC_OK) return rc;
     }
@@ -703,8 +735,8 @@ static int prefillI8(const float *q, const int8_t *k8, const int8_t *v8, const f
     pl.tileTokens = tileTokens;
     // heaviest row blocks first would need a reversed grid; the hardware scheduler
     // hands out blocks in z-major order, so late (long) blocks start last -- acceptable here
-    if (hd == 256) return launchDecodeI8<256, 1, 1>(tmK, tmV, prm, pl, rowBlocks, false, st);
-    return launchDecodeI8<128, 1, 2>(tmK, tmV, prm, pl, rowBlocks, false, st);
+    if (hd == 256) return launchDecodeI8<256, 1, 1>(tmK, tmV, tmK, tmV, prm, pl, rowBlocks, false, st);
+    return launchDecodeI8<128, 1, 2>(tmK, tmV, tmK, tmV, prm, pl, rowBlocks, false, st);
 }
 
 }  // namespace tc

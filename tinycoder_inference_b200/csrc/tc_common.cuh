@@ -117,6 +117,13 @@ __device__ __forceinline__ void tmaLoad3D(void *dst, const CUtensorMap *m, uint6
             "l"(reinterpret_cast<uint64_t>(m)), "r"(smemAddr(bar)), "r"(c0), "r"(c1), "r"(c2)
             : "memory");
 }
+// The same tile pulled into L2 only (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tmaPrefetchL2_3D(const CUtensorMap *m, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
+                         reinterpret_cast<uint64_t>(m)),
+                 "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
 __device__ __forceinline__ void tmaLoad2D(void *dst, const CUtensorMap *m, uint64_t *bar, int c0, int c1) {
     asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"

@@ -136,7 +136,7 @@ def decode_i8_noalloc(q, k8, v8, ks, vs, out, nHeads, nKV, hd, cachePos, invSqrt
 
 def decode_i8_batch(q, k8, v8, ks, vs, out, ws, lens, batch, nHeads, nKV, hd, maxLen, numChunks,
                     rows_per_seq=0, row_base=None, invSqrt=None, partials_only=False, pdl=False,
-                    prefetch_rows=0):
+                    prefetch_rows=0, next_kv=None):
     """`batch` sequences in one pool; returns the chunk slots used per head.
     lens=None: every sequence is maxLen rows long (host length)."""
     if invSqrt is None:
@@ -150,6 +150,8 @@ def decode_i8_batch(q, k8, v8, ks, vs, out, ws, lens, batch, nHeads, nKV, hd, ma
     d.lens = lens.data_ptr() if lens is not None else None
     d.flags = capi.TC_DECODE_PDL if pdl else 0
     d.prefetchRows = prefetch_rows
+    if next_kv is not None:
+        d.nextK8, d.nextV8 = next_kv[0].data_ptr(), next_kv[1].data_ptr()
     d.rowBase = row_base.data_ptr() if row_base is not None else None
     d.rowsPerSeq = rows_per_seq
     d.totalRows = k8.numel() // (nKV * hd)
