@@ -191,7 +191,8 @@ typedef struct tc_decode_i8_batch {
      * same rows of these pools into L2 (cp.async.bulk.prefetch.tensor), so DRAM keeps
      * streaming while this call's blocks fold their partials and the merge runs,
      * instead of idling until the next call's blocks start.  Nothing is read or
-     * written through these pointers by the SMs. */
+     * written through these pointers by the SMs.  Ignored when a call's rows
+     * (batch * maxLen * nKV * hd * 2 bytes) exceed 48 MB: they would not stay in L2. */
     const int8_t *nextK8, *nextV8;
 } tc_decode_i8_batch;
 
