@@ -54,7 +54,10 @@ enum {
 const char *tc_strerror(int code);
 const char *tc_last_error(void);
 /* Reads and clears the device-side error word of the current device
- * (synchronises the given stream).  0 = no kernel gave up on a wait. */
+ * (synchronises the given stream).  0 = no kernel reported anything.  Bits:
+ * 1 / 2 / 4 / 16 a bounded wait ran out (TMA stage, free stage, tensor-core commit,
+ * partials of another rank), 8 TMEM allocation, 32 a KV writer read a
+ * device-side position outside its pool and skipped the store. */
 int tc_device_status(tc_stream stream, uint32_t *flags);
 
 /* ------------------------------------------------------------------------- */
@@ -66,7 +69,10 @@ int tc_device_status(tc_stream stream, uint32_t *flags);
  * receive kSrc/vSrc [seqLen][nKV*hd] verbatim.  devPos (nullable) overrides
  * cachePos.  kvHalf != 0 stores fp16 (the KV16 cache of
  * include/gpu/GpuElementwiseKernels.hpp:64-89).  maxRows bounds the write:
- * cachePos + seqLen > maxRows returns TC_ECONTEXT_FULL (host position only). */
+ * cachePos + seqLen > maxRows returns TC_ECONTEXT_FULL with a host position;
+ * with devPos the kernel checks each row, skips a store that would land outside
+ * and raises bit 32 of the device error word (the reference's *Pos kernels write
+ * unchecked). */
 int tc_kv_append(const float *kSrc, const float *vSrc, void *kDst, void *vDst,
                  int kvHalf, uint32_t seqLen, uint32_t nKV, uint32_t hd,
                  uint32_t cachePos, const uint32_t *devPos, uint32_t maxRows,
@@ -97,7 +103,8 @@ int tc_rope_q(float *q, const float *cosT, const float *sinT, uint32_t seqLen,
  * f32 k/v [row][nKV][hd] into rows dstTokenBase+t of the int8 pool, one f32
  * scale per (row, kv head): scale = amax/127 (1 when amax == 0),
  * q = clamp(lrintf(x/scale), -128, 127).  Bit-exact with the reference.
- * devDstBase (nullable) overrides dstTokenBase at kernel time. */
+ * devDstBase (nullable) overrides dstTokenBase at kernel time; a row it sends
+ * past maxRows (!= 0) is not stored and raises bit 32 of the device error word. */
 int tc_kv_quantize_i8(const float *k, const float *v, int8_t *k8, int8_t *v8,
                       float *ks, float *vs, uint32_t tokens, uint32_t nKV,
                       uint32_t hd, uint64_t dstTokenBase, uint64_t srcTokenBase,
@@ -225,7 +232,13 @@ int tc_attn_decode_i8_noalloc(const float *q, const int8_t *k8, const int8_t *v8
  * f32 (kvHalf == 0) or fp16 (kvHalf != 0) cache, seqLen query rows (the
  * reference only calls it with seqLen == 1), row s attends [0, pos + s].
  * q81Out (nullable): the merge also emits the Q8_1 blocks of the output
- * (40-byte slots per 32 values, GpuAttentionKernels.hpp:1068-1096). */
+ * (40-byte slots per 32 values, GpuAttentionKernels.hpp:1068-1096).
+ * With devPos != NULL the position is read on the device at run time and `pos`
+ * is an UPPER BOUND of it: the grid and the chunk length are sized from pos + 1,
+ * so a launch captured in a CUDA graph and replayed at growing positions passes
+ * the last position of the window (maxSeqLen - 1), as the reference's *Pos
+ * launch covers its whole attnChunk x attnChunks grid.  Rows past a bound that
+ * was too small are not attended. */
 int tc_attn_decode_kv(const float *q, const void *kvK, const void *kvV,
                       float *attnOut, float *pAcc, float *pM, float *pL,
                       uint32_t seqLen, uint32_t nHeads, uint32_t nKV, uint32_t hd,

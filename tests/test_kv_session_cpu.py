@@ -61,6 +61,21 @@ def test_rejected_configurations(bad):
     assert rc == capi.TC_EINVAL and not h.value
 
 
+I8 = dict(kvK8=FAKE, kvV8=FAKE, kvK8Scale=FAKE, kvV8Scale=FAKE)
+
+
+@pytest.mark.parametrize("bad", [
+    # rotation tables with an int8 pool: the int8 paths never rotate, the f32 prefill would
+    dict(kvMirror=1, ropeCos=FAKE, ropeSin=FAKE, **I8),
+    dict(kvStoreI8=1, kvK=None, kvV=None, ropeCos=FAKE, ropeSin=FAKE, **I8),
+    # an fp16 store has no f32 rows to rebuild the decode pool from
+    dict(kvHalf=1, kvMirror=1, **I8),
+])
+def test_unsupported_configurations(bad):
+    rc, h = _create(_cfg(**bad))
+    assert rc == capi.TC_EUNSUPPORTED and not h.value
+
+
 def test_int8_store_needs_no_f32_cache():
     rc, h = _create(_cfg(kvStoreI8=1, kvK=None, kvV=None, kvK8=FAKE, kvV8=FAKE, kvK8Scale=FAKE, kvV8Scale=FAKE))
     assert rc == capi.TC_OK

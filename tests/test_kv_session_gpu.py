@@ -218,3 +218,59 @@ def test_decode_sequence_replayed_from_a_cuda_graph():
             assert_close(host(douts[slot]), want, what=f"graph replay {t}, slot {slot}")
         s.commit(1)
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("mode", ["f32", "f16", "f32+i8"])
+def test_split_decode_replayed_at_a_growing_device_position(mode):
+    """A decode step on the f32 / fp16 store (also the captured form of the mirror mode) captured
+    once and replayed while the position -- which lives on the device -- grows well past the
+    value it had at capture time: the launch has to be sized for the window, not for the
+    capture-time position (the reference's *Pos decode launches its fixed chunk grid)."""
+    e = Engine(mode, seed=31)
+    _check(*e.forward(33), "prompt before capture")
+    s = e.s
+    dk = torch.zeros((SLOTS, 1, NKV, HD), device="cuda")
+    dv = torch.zeros_like(dk)
+    douts = torch.zeros((SLOTS, 1, NH, HD), device="cuda")
+    dpos = torch.tensor([s.pos], dtype=torch.int32, device="cuda")
+    qs = torch.zeros((SLOTS, 1, NH, HD), device="cuda")
+
+    def step():
+        for slot in range(SLOTS):
+            s.attend(slot, qs[slot], dk[slot], dv[slot], douts[slot], s.pos, dev_pos=dpos, graph_capture=True)
+        dpos.add_(1)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()                      # warm-up outside capture (its zero row is overwritten below)
+    torch.cuda.current_stream().wait_stream(side)
+    dpos.fill_(s.pos)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    dpos.fill_(s.pos)
+    inv = 1.0 / math.sqrt(HD)
+    for t in range(150):            # 33 -> 183: several times the capture-time length
+        pos = s.begin(1)
+        rows = [e.rows(slot, pos, 1) for slot in range(SLOTS)]
+        for slot, (q, k, v) in enumerate(rows):
+            qs[slot].copy_(dev(q))
+            dk[slot].copy_(dev(k))
+            dv[slot].copy_(dev(v))
+        g.replay()
+        for slot, (q, k, v) in enumerate(rows):
+            e.hist[slot][0].append(k)
+            e.hist[slot][1].append(v)
+        s.commit(1)
+        if t % 10 != 9 and t not in (0, 30, 31, 32, 94, 95):
+            continue
+        torch.cuda.synchronize()
+        assert int(dpos.item()) == pos + 1
+        for slot, (q, k, v) in enumerate(rows):
+            K, V = np.concatenate(e.hist[slot][0]), np.concatenate(e.hist[slot][1])
+            if mode == "f16":
+                K, V = K.astype(np.float16), V.astype(np.float16)
+            want = oracle.attention_kv(q, K, V, 1, NH, NKV, HD, pos, inv)
+            assert_close(host(douts[slot]), want, what=f"{mode}: graph replay {t} (position {pos}), slot {slot}")
+    assert ops.device_status() == 0

@@ -176,3 +176,44 @@ def test_batched_quantise_appends_one_row_per_sequence():
     from tinycoder_inference_b200 import capi
     with pytest.raises(capi.ContextFull):
         ops.kv_quantize_i8_batch(dev(k), dev(v), *pool, B, nKV, hd, rows_per_seq=rps, pos=rps * 2)
+
+
+def test_device_position_outside_the_pool_is_skipped_and_reported():
+    """A position read from device memory cannot be checked on the host.  The writers check it
+    where it is known: a row that would land outside the pool is not stored (rows behind the
+    pool keep their canary bytes) and bit 32 of the device error word says so.  Nothing faults."""
+    nKV, hd, rows, canary = 2, 128, 8, 4
+    r = np.random.default_rng(3)
+    k = dev(r.standard_normal((1, nKV, hd), dtype=np.float32))
+    v = dev(r.standard_normal((1, nKV, hd), dtype=np.float32))
+    # int8 quantiser, single-sequence form with the destination row on the device
+    k8 = torch.full((rows + canary, nKV, hd), 91, dtype=torch.int8, device="cuda")
+    v8 = torch.full_like(k8, -37)
+    ks = torch.full((rows + canary, nKV), 7.0, device="cuda")
+    vs = torch.full_like(ks, 9.0)
+    assert ops.device_status() == 0
+    for bad in (rows, rows + 2):
+        ops.kv_quantize_i8(k, v, k8, v8, ks, vs, 1, nKV, hd, dev_dst_base=torch.tensor([bad], dtype=torch.int32, device="cuda"),
+                           max_rows=rows)
+        torch.cuda.synchronize()
+        assert ops.device_status(raise_on_flags=False) == 32
+        assert (k8 == 91).all() and (v8 == -37).all() and (ks == 7.0).all() and (vs == 9.0).all()
+    ops.kv_quantize_i8(k, v, k8, v8, ks, vs, 1, nKV, hd, dev_dst_base=torch.tensor([rows - 1], dtype=torch.int32, device="cuda"),
+                       max_rows=rows)      # the last row of the pool is fine
+    assert ops.device_status() == 0 and not (k8[rows - 1] == 91).all() and (k8[rows:] == 91).all()
+    # batched form: one sequence's length points past the pool
+    k8.fill_(91)
+    kb = dev(r.standard_normal((2, nKV, hd), dtype=np.float32))
+    lens = torch.tensor([3, rows + 1], dtype=torch.int32, device="cuda")     # rows per sequence: 4
+    ops.kv_quantize_i8_batch(kb, kb, k8, v8, ks, vs, 2, nKV, hd, rows_per_seq=4, lens=lens, len_add=0, total_rows=rows)
+    assert ops.device_status(raise_on_flags=False) == 32
+    assert not (k8[3] == 91).all() and (k8[rows:] == 91).all(), "the good sequence is stored, the bad one is not"
+    # f32 append with a device position
+    kd = torch.full((rows + canary, nKV, hd), 5.0, device="cuda")
+    vd = torch.full_like(kd, 6.0)
+    two = dev(r.standard_normal((2, nKV, hd), dtype=np.float32))
+    ops.kv_append(two, two, kd, vd, 2, nKV, hd, 0, dev_pos=torch.tensor([rows - 1], dtype=torch.int32, device="cuda"),
+                  max_rows=rows)           # first row fits, second does not
+    assert ops.device_status(raise_on_flags=False) == 32
+    assert torch.equal(kd[rows - 1], two[0]) and (kd[rows:] == 5.0).all() and (vd[rows:] == 6.0).all()
+    assert ops.device_status() == 0

@@ -50,6 +50,12 @@ int tc_kv_session_create(const tc_kv_session_config *cfg, tc_kv_session **out) {
     if (!cfg->kvStoreI8 && (!cfg->kvK || !cfg->kvV)) return TC_EINVAL;
     if (int8Pool && (!cfg->kvK8 || !cfg->kvV8 || !cfg->kvK8Scale || !cfg->kvV8Scale)) return TC_EINVAL;
     if ((cfg->ropeCos == nullptr) != (cfg->ropeSin == nullptr)) return TC_EINVAL;
+    // The int8 paths attend over rows as the caller hands them in (already rotated, as the gated
+    // models do it in their own Q/K norm + rotation kernel): rotation tables together with an int8
+    // pool would rotate the prefill rows and not the decode rows.
+    if (int8Pool && cfg->ropeCos != nullptr) return TC_EUNSUPPORTED;
+    // The decode pool is rebuilt from f32 rows; an fp16 store has none to rebuild it from.
+    if (cfg->kvHalf && cfg->kvMirror) return TC_EUNSUPPORTED;
     tc_kv_session *s = new (std::nothrow) tc_kv_session();
     if (!s) return TC_EINVAL;
     s->c = *cfg;
@@ -183,9 +189,15 @@ int tc_kv_session_attend(tc_kv_session *s, uint32_t slot, float *q, const float 
         rc = tc_kv_append(kSrc, vSrc, kvK, kvV, c.kvHalf, seqLen, nKV, hd, pos, devPos, c.maxSeqLen, stream);
     if (rc != TC_OK) return rc;
     // (no int8 bookkeeping here: the next decode's rebuild converts exactly the rows the pool lacks)
-    if (seqLen == 1)
-        return tc_attn_decode_kv(q, kvK, kvV, attnOut, c.pAcc, c.pM, c.pL, 1, nH, nKV, hd, pos, devPos,
+    if (seqLen == 1) {
+        // A launch whose position lives on the device (the form a captured graph replays) is sized
+        // for the whole window: the host position is only the value at capture time, the grid and
+        // the chunk length must cover every position a replay can reach (the reference's *Pos
+        // decode launches its fixed attnChunk_ x attnChunks_ grid for the same reason).
+        const uint32_t hostBound = devPos != nullptr ? c.maxSeqLen - 1u : pos;
+        return tc_attn_decode_kv(q, kvK, kvV, attnOut, c.pAcc, c.pM, c.pL, 1, nH, nKV, hd, hostBound, devPos,
                                  c.maxSeqLen, c.numChunks, 0, s->invSqrt, c.kvHalf, nullptr, stream);
+    }
     // a fresh prompt on the f32 cache takes the tensor-core prefill when the caller gave it scratch
     if (pos == 0 && devPos == nullptr && !graphCapture && !c.kvHalf && hd == 128 && c.prefillScratch != nullptr) {
         size_t need = 0;

@@ -25,7 +25,8 @@ kvQuantKernel(const float *__restrict__ k, const float *__restrict__ v, int8_t *
               int8_t *__restrict__ v8, float *__restrict__ ks, float *__restrict__ vs, uint32_t tokens,
               uint32_t nKV, uint32_t hd, uint64_t dstTokenBase, uint64_t srcTokenBase,
               const uint32_t *__restrict__ devDstBase, uint32_t batchMode, uint64_t rowsPerSeq,
-              const uint64_t *__restrict__ rowBase, const uint32_t *__restrict__ devLens, int32_t lenAdd) {
+              const uint64_t *__restrict__ rowBase, const uint32_t *__restrict__ devLens, int32_t lenAdd,
+              uint64_t maxRows, unsigned int *__restrict__ err) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint64_t row = static_cast<uint64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= static_cast<uint64_t>(tokens) * nKV) return;
@@ -39,6 +40,12 @@ kvQuantKernel(const float *__restrict__ k, const float *__restrict__ v, int8_t *
         const uint64_t pos = devLens != nullptr ? static_cast<uint64_t>(static_cast<int64_t>(devLens[t]) + lenAdd)
                                                 : dstTokenBase;
         dst = (base + pos) * nKV + h;
+    }
+    // A destination row read from device memory (a replayed graph past its window, a bad length)
+    // is checked here, where it is known: the store is skipped and the error word says so.
+    if (maxRows != 0 && dst >= maxRows * nKV) {
+        if (lane == 0) atomicOr(err, kDevErrRowBound);
+        return;
     }
     const uint32_t nvec = hd >> 2;
     float4 kx[MAXV], vx[MAXV];
@@ -101,7 +108,8 @@ __global__ void __launch_bounds__(256)
 kvAppendKernel(float *__restrict__ q, const float *__restrict__ kSrc, const float *__restrict__ vSrc,
                KVT *__restrict__ kDst, KVT *__restrict__ vDst, uint32_t nHeads, uint32_t nKV, uint32_t hd,
                uint32_t cachePos, uint32_t ropePos, const uint32_t *__restrict__ devPos,
-               const float *__restrict__ cosT, const float *__restrict__ sinT) {
+               const float *__restrict__ cosT, const float *__restrict__ sinT, uint32_t maxRows,
+               unsigned int *__restrict__ err) {
     const uint32_t s = blockIdx.x;
     if (devPos != nullptr) {
         cachePos = devPos[0];
@@ -122,6 +130,11 @@ kvAppendKernel(float *__restrict__ q, const float *__restrict__ kSrc, const floa
         }
     }
     if (kSrc == nullptr) return;
+    if (maxRows != 0 && static_cast<uint64_t>(cachePos) + s >= maxRows) {
+        // device-side position outside the window: no store, reported through the error word
+        if (threadIdx.x == 0) atomicOr(err, kDevErrRowBound);
+        return;
+    }
     const float *ks = kSrc + static_cast<size_t>(s) * kvSize;
     const float *vs = vSrc + static_cast<size_t>(s) * kvSize;
     KVT *kd = kDst + static_cast<size_t>(cachePos + s) * kvSize;
@@ -174,6 +187,8 @@ int tc_kv_quantize_i8(const float *k, const float *v, int8_t *k8, int8_t *v8, fl
                      (unsigned long long) maxRows);
         return TC_ECONTEXT_FULL;
     }
+    unsigned int *err = tc::devErrorWord();
+    TC_REQUIRE(err != nullptr, TC_ECUDA, "tc_kv_quantize_i8: no device error word");
     const uint64_t rows = static_cast<uint64_t>(tokens) * nKV;
     const uint32_t warpsPerBlock = 8;
     const uint64_t blocks = (rows + warpsPerBlock - 1) / warpsPerBlock;
@@ -182,13 +197,13 @@ int tc_kv_quantize_i8(const float *k, const float *v, int8_t *k8, int8_t *v8, fl
     const uint32_t nvec = hd / 4;
     if (nvec <= 32)
         tc::kvQuantKernel<1><<<static_cast<uint32_t>(blocks), 256, 0, st>>>(
-                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase, 0u, 0ull, nullptr, nullptr, 0);
+                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase, 0u, 0ull, nullptr, nullptr, 0, maxRows, err);
     else if (nvec <= 64)
         tc::kvQuantKernel<2><<<static_cast<uint32_t>(blocks), 256, 0, st>>>(
-                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase, 0u, 0ull, nullptr, nullptr, 0);
+                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase, 0u, 0ull, nullptr, nullptr, 0, maxRows, err);
     else
         tc::kvQuantKernel<8><<<static_cast<uint32_t>(blocks), 256, 0, st>>>(
-                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase, 0u, 0ull, nullptr, nullptr, 0);
+                k, v, k8, v8, ks, vs, tokens, nKV, hd, dstTokenBase, srcTokenBase, devDstBase, 0u, 0ull, nullptr, nullptr, 0, maxRows, err);
     TC_CUDA_OK(cudaGetLastError());
     return TC_OK;
 }
@@ -209,19 +224,21 @@ int tc_kv_quantize_i8_batch(const float *k, const float *v, int8_t *k8, int8_t *
                      (unsigned long long) totalRows);
         return TC_ECONTEXT_FULL;
     }
+    unsigned int *err = tc::devErrorWord();
+    TC_REQUIRE(err != nullptr, TC_ECUDA, "tc_kv_quantize_i8_batch: no device error word");
     const uint64_t rows = static_cast<uint64_t>(batch) * nKV;
     const uint32_t blocks = static_cast<uint32_t>((rows + 7) / 8);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint32_t nvec = hd / 4;
     if (nvec <= 32)
         tc::kvQuantKernel<1><<<blocks, 256, 0, st>>>(k, v, k8, v8, ks, vs, batch, nKV, hd, pos, 0, nullptr, 1u, rowsPerSeq,
-                                                     rowBase, lens, lenAdd);
+                                                     rowBase, lens, lenAdd, totalRows, err);
     else if (nvec <= 64)
         tc::kvQuantKernel<2><<<blocks, 256, 0, st>>>(k, v, k8, v8, ks, vs, batch, nKV, hd, pos, 0, nullptr, 1u, rowsPerSeq,
-                                                     rowBase, lens, lenAdd);
+                                                     rowBase, lens, lenAdd, totalRows, err);
     else
         tc::kvQuantKernel<8><<<blocks, 256, 0, st>>>(k, v, k8, v8, ks, vs, batch, nKV, hd, pos, 0, nullptr, 1u, rowsPerSeq,
-                                                     rowBase, lens, lenAdd);
+                                                     rowBase, lens, lenAdd, totalRows, err);
     TC_CUDA_OK(cudaGetLastError());
     return TC_OK;
 }
@@ -241,14 +258,16 @@ static int appendCommon(float *q, const float *kSrc, const float *vSrc, void *kD
         return TC_ECONTEXT_FULL;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned int *err = tc::devErrorWord();
+    TC_REQUIRE(err != nullptr, TC_ECUDA, "%s: no device error word", who);
     if (kvHalf)
         tc::kvAppendKernel<__half><<<seqLen, 256, 0, st>>>(q, kSrc, vSrc, static_cast<__half *>(kDst),
                                                           static_cast<__half *>(vDst), nHeads, nKV, hd,
-                                                          cachePos, ropePos, devPos, cosT, sinT);
+                                                          cachePos, ropePos, devPos, cosT, sinT, maxRows, err);
     else
         tc::kvAppendKernel<float><<<seqLen, 256, 0, st>>>(q, kSrc, vSrc, static_cast<float *>(kDst),
                                                          static_cast<float *>(vDst), nHeads, nKV, hd, cachePos,
-                                                         ropePos, devPos, cosT, sinT);
+                                                         ropePos, devPos, cosT, sinT, maxRows, err);
     TC_CUDA_OK(cudaGetLastError());
     return TC_OK;
 }
@@ -275,7 +294,7 @@ int tc_rope_q(float *q, const float *cosT, const float *sinT, uint32_t seqLen, u
     TC_REQUIRE(hd > 0 && (hd % 2u) == 0, TC_EUNSUPPORTED, "tc_rope_q: hd=%u must be even", hd);
     if (seqLen == 0) return TC_OK;
     tc::kvAppendKernel<float><<<seqLen, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-            q, nullptr, nullptr, nullptr, nullptr, nHeads, 0, hd, 0, pos, devPos, cosT, sinT);
+            q, nullptr, nullptr, nullptr, nullptr, nHeads, 0, hd, 0, pos, devPos, cosT, sinT, 0u, nullptr);
     TC_CUDA_OK(cudaGetLastError());
     return TC_OK;
 }

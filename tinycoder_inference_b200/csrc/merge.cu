@@ -58,7 +58,9 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
     if (devLens != nullptr) {
         const uint32_t len = devLens[s] + lenAdd;
         const uint32_t need = (len + chunkTokens - 1) / chunkTokens;
-        active = need < numChunks ? need : numChunks;
+        // never past the slots the launch that wrote the partials covered (activeHost): a device
+        // length beyond the host bound the plan was built from must not pull in stale slots
+        active = need < active ? need : active;
     }
     __shared__ float sw[kMergeMaxChunks], sl[kMergeMaxChunks];
     __shared__ float sred[NW];
@@ -222,7 +224,9 @@ mergeSliceKernel(const float *__restrict__ pAcc, const float *__restrict__ pM, c
     if (devLens != nullptr) {
         const uint32_t len = devLens[s] + lenAdd;
         const uint32_t need = (len + chunkTokens - 1) / chunkTokens;
-        active = need < numChunks ? need : numChunks;
+        // never past the slots the launch that wrote the partials covered (activeHost): a device
+        // length beyond the host bound the plan was built from must not pull in stale slots
+        active = need < active ? need : active;
     }
     __shared__ float sw[kMergeMaxChunks], sl[kMergeMaxChunks];
     __shared__ float sred[NW];

@@ -23,6 +23,7 @@ enum : uint32_t {
     kDevErrMmaWait = 4u,    // waited too long for a tcgen05 commit
     kDevErrTmemAlloc = 8u,
     kDevErrMergeWait = 16u,  // a block waited too long for the partials of another rank
+    kDevErrRowBound = 32u,   // a KV writer was handed a device-side position outside its pool: store skipped
 };
 // The word lives in one translation unit; kernels receive its device address as
 // an argument (devErrorWord(), resolved once per device).

@@ -25,32 +25,39 @@ def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def device_status() -> int:
+def device_status(raise_on_flags=True) -> int:
+    """Reads and clears the device error word; raises when a kernel reported anything
+    (raise_on_flags=False returns the bits instead)."""
     flags = C.c_uint32(0)
-    check(lib.tc_device_status(_stream(), C.byref(flags)))
+    rc = lib.tc_device_status(_stream(), C.byref(flags))
+    if rc != capi.TC_EDEVICE or raise_on_flags:
+        check(rc)
     return flags.value
 
 
 # ---- KV writers ---------------------------------------------------------------
 
-def kv_quantize_i8(k, v, k8, v8, ks, vs, tokens, nKV, hd, dst_base=0, src_base=0, dev_dst_base=None):
+def kv_quantize_i8(k, v, k8, v8, ks, vs, tokens, nKV, hd, dst_base=0, src_base=0, dev_dst_base=None,
+                   max_rows=None):
     """k, v f32 [rows][nKV][hd] -> rows dst_base.. of the int8 pool k8/v8 + scales ks/vs."""
-    max_rows = k8.numel() // (nKV * hd)
+    if max_rows is None:
+        max_rows = k8.numel() // (nKV * hd)
     check(lib.tc_kv_quantize_i8(_ptr(k), _ptr(v), _ptr(k8), _ptr(v8), _ptr(ks), _ptr(vs), tokens, nKV, hd,
                                 dst_base, src_base, _ptr(dev_dst_base), max_rows, _stream()))
 
 
 def kv_quantize_i8_batch(k, v, k8, v8, ks, vs, batch, nKV, hd, rows_per_seq=0, row_base=None, pos=0, lens=None,
-                         len_add=0):
+                         len_add=0, total_rows=None):
     """The new token of every sequence of a batch into one pool, one launch."""
-    total = k8.numel() // (nKV * hd)
+    total = k8.numel() // (nKV * hd) if total_rows is None else total_rows
     check(lib.tc_kv_quantize_i8_batch(_ptr(k), _ptr(v), _ptr(k8), _ptr(v8), _ptr(ks), _ptr(vs), batch, nKV, hd,
                                       rows_per_seq, _ptr(row_base), pos, _ptr(lens), len_add, total, _stream()))
 
 
-def kv_append(kSrc, vSrc, kDst, vDst, seqLen, nKV, hd, cachePos, dev_pos=None):
+def kv_append(kSrc, vSrc, kDst, vDst, seqLen, nKV, hd, cachePos, dev_pos=None, max_rows=None):
     half = kDst.dtype == torch.float16
-    max_rows = kDst.numel() // (nKV * hd)
+    if max_rows is None:
+        max_rows = kDst.numel() // (nKV * hd)
     check(lib.tc_kv_append(_ptr(kSrc), _ptr(vSrc), _ptr(kDst), _ptr(vDst), int(half), seqLen, nKV, hd, cachePos,
                            _ptr(dev_pos), max_rows, _stream()))
 
