@@ -230,6 +230,20 @@ def prefill_f16(q, k, v, S, nHeads, nKV, hd, scale):
     return out
 
 
+def prefill_f16_rows(q, k, v, rows, S, nHeads, nKV, hd, scale, cachePos=0):
+    """The same contract for a sample of query rows (indices into q's S rows) over a cache that
+    already holds cachePos rows: k, v are [cachePos + S][nKV][hd]; returns [len(rows)][nHeads][hd]."""
+    q = _c(q, np.float32)
+    k = _c(k, np.float32)
+    v = _c(v, np.float32)
+    rows = _c(rows, np.uint32)
+    out = np.zeros((rows.size, nHeads, hd), np.float32)
+    _lib.orc_prefill_f16_rows(_p(q, _f32p), _p(k, _f32p), _p(v, _f32p), _p(out, _f32p), _p(rows, _u32p),
+                              C.c_uint32(rows.size), C.c_uint32(S), C.c_uint32(cachePos), C.c_uint32(nHeads),
+                              C.c_uint32(nKV), C.c_uint32(hd), C.c_float(scale))
+    return out
+
+
 # ---- RoPE / append -----------------------------------------------------------
 
 def rope_tables(rows, headDim, theta):

@@ -109,6 +109,73 @@ int ref_gpu_softmax_causal(const float *scores, __half *pOut, uint32_t seqLen, u
     return done();
 }
 
+// The whole materialised prefill of GPUComputeForward.cu:3957-4026 for one layer, call for call:
+// kF32ToF16 twins of q and of the stored K/V rows, one cublasGemmStridedBatchedEx per q head
+// for the scores (A = K of the head's group with batch stride 0, B = Q of the head, fp16
+// operands, f32 output, f32 compute, CUBLAS_GEMM_DEFAULT_TENSOR_OP), kAttnSoftmaxCausal, one
+// cublasGemmStridedBatchedEx per q head for P V into attnOut with the head stride.  The K/V
+// rows are taken as already stored (the rotation / store kernels in front are pinned on their
+// own); the scratch the engine keeps in scratch_ is allocated and freed here.
+int ref_gpu_prefill_f16_gemm(const float *q, const float *kF, const float *vF, float *attnOut, uint32_t seqLen,
+                             uint32_t nHeads, uint32_t nKV, uint32_t hd, float invSqrt) {
+    const uint32_t qLen = nHeads * hd, kvLen = nKV * hd, pos = 0;
+    const uint32_t s2 = seqLen * seqLen;
+    __half *q16 = nullptr, *kv16 = nullptr, *p16 = nullptr;
+    float *scores = nullptr;
+    const uint64_t cap = seqLen;  // attnGemmCap
+    if (cudaMalloc(&q16, sizeof(__half) * seqLen * qLen) != cudaSuccess ||
+        cudaMalloc(&kv16, sizeof(__half) * 2 * cap * kvLen) != cudaSuccess ||
+        cudaMalloc(&scores, sizeof(float) * static_cast<uint64_t>(nHeads) * s2) != cudaSuccess ||
+        cudaMalloc(&p16, sizeof(__half) * static_cast<uint64_t>(nHeads) * s2) != cudaSuccess)
+        return -2;
+    cublasHandle_t handle = nullptr;
+    if (cublasCreate(&handle) != CUBLAS_STATUS_SUCCESS) return -3;
+    cublasSetStream(handle, nullptr);
+    int rc = 0;
+    {
+        const uint32_t qElems = seqLen * qLen;
+        kF32ToF16<<<(qElems + 511u) / 512u, 256>>>(q, reinterpret_cast<__half2 *>(q16), qElems / 2u);
+        const uint32_t nRows = pos + seqLen;
+        const uint32_t kvElems = nRows * kvLen;
+        __half *k16 = kv16;
+        __half *v16 = k16 + cap * kvLen;
+        kF32ToF16<<<(kvElems + 511u) / 512u, 256>>>(kF, reinterpret_cast<__half2 *>(k16), kvElems / 2u);
+        kF32ToF16<<<(kvElems + 511u) / 512u, 256>>>(vF, reinterpret_cast<__half2 *>(v16), kvElems / 2u);
+        const uint32_t gw = nHeads / nKV;
+        const float geAlpha = 1.0f, geBeta = 0.0f;
+        for (uint32_t h0 = 0; h0 < nHeads && rc == 0; ++h0) {
+            const uint32_t g = h0 / gw;
+            cublasStatus_t st = cublasGemmStridedBatchedEx(
+                    handle, CUBLAS_OP_T, CUBLAS_OP_N, static_cast<int>(seqLen), static_cast<int>(seqLen),
+                    static_cast<int>(hd), &geAlpha, k16 + static_cast<uint64_t>(g) * hd, CUDA_R_16F,
+                    static_cast<int>(kvLen), 0LL, q16 + static_cast<uint64_t>(h0) * hd, CUDA_R_16F,
+                    static_cast<int>(qLen), static_cast<long long>(hd), &geBeta,
+                    scores + static_cast<uint64_t>(h0) * s2, CUDA_R_32F, static_cast<int>(seqLen),
+                    static_cast<long long>(s2), 1, CUDA_R_32F, CUBLAS_GEMM_DEFAULT_TENSOR_OP);
+            if (st != CUBLAS_STATUS_SUCCESS) rc = -4;
+        }
+        kAttnSoftmaxCausal<<<dim3(seqLen, nHeads), 128>>>(scores, p16, seqLen, s2, pos, invSqrt);
+        for (uint32_t h0 = 0; h0 < nHeads && rc == 0; ++h0) {
+            const uint32_t g = h0 / gw;
+            cublasStatus_t st = cublasGemmStridedBatchedEx(
+                    handle, CUBLAS_OP_N, CUBLAS_OP_N, static_cast<int>(hd), static_cast<int>(seqLen),
+                    static_cast<int>(seqLen), &geAlpha, v16 + static_cast<uint64_t>(g) * hd, CUDA_R_16F,
+                    static_cast<int>(kvLen), 0LL, p16 + static_cast<uint64_t>(h0) * s2, CUDA_R_16F,
+                    static_cast<int>(seqLen), static_cast<long long>(s2), &geBeta,
+                    attnOut + static_cast<uint64_t>(h0) * hd, CUDA_R_32F, static_cast<int>(qLen),
+                    static_cast<long long>(hd), 1, CUDA_R_32F, CUBLAS_GEMM_DEFAULT_TENSOR_OP);
+            if (st != CUBLAS_STATUS_SUCCESS) rc = -5;
+        }
+    }
+    const int e = done();
+    cublasDestroy(handle);
+    cudaFree(q16);
+    cudaFree(kv16);
+    cudaFree(scores);
+    cudaFree(p16);
+    return rc != 0 ? rc : e;
+}
+
 // kQ35QNormRoPE + kQ35KNormRoPE as launched at GPUComputeForward.cu:1330-1337
 int ref_gpu_qk_norm_rope(const float *qGate, float *qOut, float *k, const float *wq, const float *wk, uint32_t hd,
                          uint32_t nDims, uint32_t nHeads, uint32_t nKV, uint32_t seqLen, uint32_t pos,

@@ -491,51 +491,73 @@ void orc_attention_f64(const float *q, const void *kc, const void *vc,
  * p = exp2f((score*scale - mx) * LOG2E) / sum, rounded to fp16, zero past the
  * causal limit), then out = P . V in f32.  q [S][nHeads][hd] f32,
  * k, v [S][nKV][hd] f32 (rows [0, S), cachePos == 0). */
-void orc_prefill_f16(const float *q, const float *k, const float *v, float *out,
-                     uint32_t S, uint32_t nHeads, uint32_t nKV, uint32_t hd,
-                     float scale) {
-    float *sc = (float *) malloc((size_t) S * sizeof(float));
-    float *p16 = (float *) malloc((size_t) S * sizeof(float));
-    float *k16 = (float *) malloc((size_t) S * nKV * hd * sizeof(float));
-    float *v16 = (float *) malloc((size_t) S * nKV * hd * sizeof(float));
-    for (size_t i = 0; i < (size_t) S * nKV * hd; ++i) {
+/* One query row of one head: scores over K rows [0, lim], softmax, fp16 P, PV. */
+static void prefill_f16_row(const float *qp, const float *k16, const float *v16, float *op,
+                            uint32_t lim, uint32_t g, uint32_t nKV, uint32_t hd, float scale,
+                            float *sc, float *p16) {
+    float q16[256];
+    for (uint32_t i = 0; i < hd; ++i) q16[i] = half_round(qp[i]);
+    float mx = -1e30f;
+    for (uint32_t c = 0; c <= lim; ++c) {
+        const float *kp = k16 + ((uint64_t) c * nKV + g) * hd;
+        float d = 0.0f;
+        for (uint32_t i = 0; i < hd; ++i) d += q16[i] * kp[i];
+        sc[c] = d;
+        mx = fmaxf(mx, d);
+    }
+    mx *= scale;
+    float sum = 0.0f;
+    for (uint32_t c = 0; c <= lim; ++c)
+        sum += exp2f((sc[c] * scale - mx) * ORC_LOG2E);
+    const float inv = 1.0f / sum;
+    for (uint32_t c = 0; c <= lim; ++c)
+        p16[c] = half_round(exp2f((sc[c] * scale - mx) * ORC_LOG2E) * inv);
+    for (uint32_t i = 0; i < hd; ++i) op[i] = 0.0f;
+    for (uint32_t c = 0; c <= lim; ++c) {
+        const float *vp = v16 + ((uint64_t) c * nKV + g) * hd;
+        for (uint32_t i = 0; i < hd; ++i) op[i] += p16[c] * vp[i];
+    }
+}
+
+/* The same contract for a SAMPLE of query rows and a cache that already holds
+ * cachePos rows (query row s sits at position cachePos + s and sees K/V rows
+ * [0, cachePos + s]; the reference takes this path only with cachePos == 0,
+ * GPUComputeForward.cu:3828-3835 -- the rule itself is kAttnSoftmaxCausal's
+ * `pos + row`).  q: [S][nHeads][hd]; k, v: [cachePos + S][nKV][hd]; rows[r] < S;
+ * out: [nRows][nHeads][hd].  Lets a test check a long prompt without paying for
+ * every row on the CPU. */
+void orc_prefill_f16_rows(const float *q, const float *k, const float *v, float *out,
+                          const uint32_t *rows, uint32_t nRows, uint32_t S, uint32_t cachePos,
+                          uint32_t nHeads, uint32_t nKV, uint32_t hd, float scale) {
+    const size_t total = (size_t) cachePos + S;
+    float *sc = (float *) malloc(total * sizeof(float));
+    float *p16 = (float *) malloc(total * sizeof(float));
+    float *k16 = (float *) malloc(total * nKV * hd * sizeof(float));
+    float *v16 = (float *) malloc(total * nKV * hd * sizeof(float));
+    for (size_t i = 0; i < total * nKV * hd; ++i) {
         k16[i] = half_round(k[i]);
         v16[i] = half_round(v[i]);
     }
-    float q16[256];
-    for (uint32_t h = 0; h < nHeads; ++h) {
-        const uint32_t g = h / (nHeads / nKV);
-        for (uint32_t s = 0; s < S; ++s) {
-            const float *qp = q + ((uint64_t) s * nHeads + h) * hd;
-            for (uint32_t i = 0; i < hd; ++i) q16[i] = half_round(qp[i]);
-            const uint32_t lim = s; /* cachePos + row, cachePos == 0 */
-            float mx = -1e30f;
-            for (uint32_t c = 0; c <= lim; ++c) {
-                const float *kp = k16 + ((uint64_t) c * nKV + g) * hd;
-                float d = 0.0f;
-                for (uint32_t i = 0; i < hd; ++i) d += q16[i] * kp[i];
-                sc[c] = d;
-                mx = fmaxf(mx, d);
-            }
-            mx *= scale;
-            float sum = 0.0f;
-            for (uint32_t c = 0; c <= lim; ++c)
-                sum += exp2f((sc[c] * scale - mx) * ORC_LOG2E);
-            const float inv = 1.0f / sum;
-            for (uint32_t c = 0; c <= lim; ++c)
-                p16[c] = half_round(exp2f((sc[c] * scale - mx) * ORC_LOG2E) * inv);
-            float *op = out + ((uint64_t) s * nHeads + h) * hd;
-            for (uint32_t i = 0; i < hd; ++i) op[i] = 0.0f;
-            for (uint32_t c = 0; c <= lim; ++c) {
-                const float *vp = v16 + ((uint64_t) c * nKV + g) * hd;
-                for (uint32_t i = 0; i < hd; ++i) op[i] += p16[c] * vp[i];
-            }
-        }
+    for (uint32_t r = 0; r < nRows; ++r) {
+        const uint32_t s = rows[r];
+        for (uint32_t h = 0; h < nHeads; ++h)
+            prefill_f16_row(q + ((uint64_t) s * nHeads + h) * hd, k16, v16,
+                            out + ((uint64_t) r * nHeads + h) * hd, cachePos + s, h / (nHeads / nKV),
+                            nKV, hd, scale, sc, p16);
     }
     free(sc);
     free(p16);
     free(k16);
     free(v16);
+}
+
+void orc_prefill_f16(const float *q, const float *k, const float *v, float *out,
+                     uint32_t S, uint32_t nHeads, uint32_t nKV, uint32_t hd,
+                     float scale) {
+    uint32_t *rows = (uint32_t *) malloc((size_t) S * sizeof(uint32_t));
+    for (uint32_t s = 0; s < S; ++s) rows[s] = s;
+    orc_prefill_f16_rows(q, k, v, out, rows, S, S, 0, nHeads, nKV, hd, scale);
+    free(rows);
 }
 
 /* ------------------------------------------------------------------------- */

@@ -5,6 +5,7 @@ the reference checkout is mounted; the built library travels with the tree):
 
     python tests/golden/make_ref_gpu_golden.py [out.npz]
     python tests/golden/make_ref_gpu_golden.py f2 [out_f2.npz]      (ref_gpu_golden_f2.npz)
+    python tests/golden/make_ref_gpu_golden.py a8 [out_a8.npz]      (ref_gpu_golden_a8.npz)
 
 The result is committed as tests/golden/ref_gpu_golden.npz; inputs are regenerated
 from seeds (tests/golden/ref_gpu_cases.py), only outputs are stored."""
@@ -170,8 +171,24 @@ def main_f2(out_path):
     print(f"wrote {len(G)} arrays, {os.path.getsize(out_path)} bytes -> {out_path}")
 
 
+def main_a8(out_path):
+    """The reference's materialised fp16 prefill, cuBLAS products included -> ref_gpu_golden_a8.npz."""
+    G = {}
+    u32, f32 = C.c_uint32, C.c_float
+    for i, (name, c) in enumerate(cases.A8_CASES.items()):
+        q, k, v = cases.a8_case(40 + i, c)
+        out = torch.zeros((c["S"], c["nH"], c["hd"]), device="cuda")
+        call(lib.ref_gpu_prefill_f16_gemm, p(d(q)), p(d(k)), p(d(v)), p(out), u32(c["S"]), u32(c["nH"]), u32(c["nKV"]),
+             u32(c["hd"]), f32(1.0 / math.sqrt(c["hd"])))
+        G[f"{name}.out_rows"] = out.cpu().numpy()[cases.a8_rows(c["S"])]
+    np.savez_compressed(out_path, **G)
+    print(f"wrote {len(G)} arrays, {os.path.getsize(out_path)} bytes -> {out_path}")
+
+
 if __name__ == "__main__":
-    if len(sys.argv) > 1 and sys.argv[1] == "f2":
+    if len(sys.argv) > 1 and sys.argv[1] == "a8":
+        main_a8(sys.argv[2] if len(sys.argv) > 2 else os.path.join(HERE, "ref_gpu_golden_a8.npz"))
+    elif len(sys.argv) > 1 and sys.argv[1] == "f2":
         main_f2(sys.argv[2] if len(sys.argv) > 2 else os.path.join(HERE, "ref_gpu_golden_f2.npz"))
     else:
         main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "ref_gpu_golden.npz"))

@@ -80,3 +80,25 @@ def norm_rope_case(case, c):
     wq = (1 + 0.1 * r.standard_normal(c["hd"])).astype(np.float32)
     wk = (1 + 0.1 * r.standard_normal(c["hd"])).astype(np.float32)
     return qg, k, wq, wk
+
+
+# recorded into ref_gpu_golden_a8.npz: the reference's whole materialised prefill (kF32ToF16,
+# cuBLAS score and P.V products, kAttnSoftmaxCausal) -- the stored outputs are a sample of rows
+A8_CASES = {
+    "prefill_f16_s200": dict(nH=4, nKV=2, hd=128, S=200),
+    "prefill_f16_s512": dict(nH=7, nKV=1, hd=128, S=512),      # the reference's row cap, one full GQA group
+    "prefill_f16_hd64": dict(nH=4, nKV=2, hd=64, S=96),
+}
+
+
+def a8_rows(S):
+    """Rows whose outputs are stored: every 16th, the tile edges, the last 8."""
+    rows = set(range(0, S, 16)) | {1, 63, 64, 65, 127, 128, 129, 255, 256, 257} | set(range(S - 8, S))
+    return np.array(sorted(r for r in rows if r < S), np.uint32)
+
+
+def a8_case(case, c):
+    r = _rng(case)
+    return (r.standard_normal((c["S"], c["nH"], c["hd"]), dtype=np.float32),
+            r.standard_normal((c["S"], c["nKV"], c["hd"]), dtype=np.float32),
+            r.standard_normal((c["S"], c["nKV"], c["hd"]), dtype=np.float32))

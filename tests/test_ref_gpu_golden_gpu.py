@@ -106,3 +106,25 @@ def test_merge_and_gate_equal_reference_kernels():
     o = dev(cases.q_case(10, c["S"], c["nH"], c["hd"]))
     ops.sigmoid_gate(o, dev(cases.q_case(11, c["S"], c["nH"], 2 * c["hd"]) * 4), c["S"], c["nH"], c["hd"])
     assert_close(host(o), G["sigmoid_gate.out"], rtol=1e-5, atol=1e-6, what="gate")
+
+
+A8 = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_gpu_golden_a8.npz")
+
+
+@pytest.mark.parametrize("idx,name", [(i, n) for i, n in enumerate(cases.A8_CASES) if cases.A8_CASES[n]["hd"] == 128])
+def test_prefill_f16_equals_reference_materialised_path(idx, name):
+    """tc_attn_prefill_f16 (flash, tcgen05) against what the reference's materialised prefill --
+    its conversion and softmax kernels around the cuBLAS products -- produced on a B200 for the
+    same seeded rows; tolerance of the fp16 prefill (2e-2 relative)."""
+    g = np.load(A8)
+    c = cases.A8_CASES[name]
+    q, k, v = cases.a8_case(40 + idx, c)
+    S, nH, nKV, hd = c["S"], c["nH"], c["nKV"], c["hd"]
+    n = ops.prefill_f16_scratch_bytes(S, nH, nKV, hd)
+    buf = torch.empty(n + 1024, dtype=torch.uint8, device="cuda")
+    off = (-buf.data_ptr()) % 1024
+    out = torch.full((S, nH, hd), float("nan"), device="cuda")
+    ops.prefill_f16(dev(q), dev(k), dev(v), out, buf[off:off + n], S, nH, nKV, hd)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(host(out)[cases.a8_rows(S)], g[f"{name}.out_rows"], rtol=2e-2, atol=2e-3, what=name)
