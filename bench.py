@@ -704,6 +704,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream order between the kernels of a step")
     ap.add_argument("--partials-only", action="store_true", help="diagnostic: skip the merge launch")
+    ap.add_argument("--fused-merge", action="store_true",
+                    help="merge the chunk partials inside the decode kernel (last-arriving block) instead of a second launch")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -756,6 +758,7 @@ def main():
     torch.cuda.synchronize()
 
     lens_arg = None  # host lengths: every sequence holds exactly ctx rows
+    tickets = torch.zeros(batch * nKV, dtype=torch.int32, device=dev) if args.fused_merge else None
 
     def step(pdl):
         # rows [0, ctx-1) are old rows; the last row is the one a decode step appends
@@ -763,7 +766,7 @@ def main():
             nxt = None if args.no_next_prefetch else (k8[(l + 1) % layers], v8[(l + 1) % layers])
             ops.decode_i8_batch(q[l], k8[l], v8[l], ks[l], vs[l], out[l], ws, lens_arg, batch, nH, nKV, hd, ctx,
                                 chunks, rows_per_seq=rows, invSqrt=inv, pdl=pdl, prefetch_rows=ctx - 1,
-                                partials_only=args.partials_only, next_kv=nxt)
+                                partials_only=args.partials_only, next_kv=nxt, tickets=tickets)
 
     launches_per_step = layers * 2
     step(False)
@@ -848,7 +851,7 @@ def main():
             nxt = None if args.no_next_prefetch else (k8[(l + 1) % layers], v8[(l + 1) % layers])
             ops.decode_i8_batch(dq[l], k8[l], v8[l], ks[l], vs[l], dout[l], ws, lens_arg, batch, nH, nKV, hd, ctx,
                                 chunks, rows_per_seq=rows, invSqrt=inv, pdl=not args.no_pdl, prefetch_rows=ctx - 1,
-                                next_kv=nxt)
+                                next_kv=nxt, tickets=tickets)
 
     if args.no_graph:
         e2e_run = e2e_layers

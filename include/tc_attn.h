@@ -201,6 +201,14 @@ typedef struct tc_decode_i8_batch {
      * written through these pointers by the SMs.  Ignored when a call's rows
      * (batch * maxLen * nKV * hd * 2 bytes) exceed 48 MB: they would not stay in L2. */
     const int8_t *nextK8, *nextV8;
+    /* Optional (NULL = merge in a second launch): batch * nKV arrival counters in DEVICE memory,
+     * zero before the first call (the kernel leaves them zero).  With them the split-KV kernel
+     * merges its own partials (head_dim 128, at most 8 q heads per kv head): every block
+     * publishes its chunk partial and takes a ticket, the block that draws the last ticket of
+     * a (sequence, kv head) folds all chunks and writes the output -- no block waits for
+     * another, and the merge launch with its hand-off disappears.  Calls that may run
+     * concurrently (different streams) need counters of their own. */
+    uint32_t *mergeTickets;
 } tc_decode_i8_batch;
 
 enum { TC_DECODE_PDL = 1u };

@@ -284,3 +284,73 @@ def test_context_split_decoder_single_rank_matches_oracle():
     for _ in range(2):     # second call reuses the buffers
         dec(dev(q), dev(k8), dev(v8), dev(ks), dev(vs), out, ctx, invSqrt=inv)
     assert_close(host(out), want, what="ContextSplitDecoder, world 1")
+
+
+@pytest.mark.parametrize("pdl", [False, True])
+def test_merge_inside_the_kernel_by_the_last_arriving_block(pdl):
+    """With arrival counters the split-KV kernel merges its own partials: ragged batch (device
+    lengths, some chunks inactive), several layers back to back on the same partial buffers and
+    the same counters, NaN-poisoned partial slots.  The counters are zero again afterwards."""
+    nH, nKV, hd, B, layers, numChunks = 28, 4, 128, 5, 3, 64
+    lens = np.array([4000, 1, 129, 2600, 777], np.int64)
+    base = np.zeros(B, np.int64)
+    base[1:] = np.cumsum(lens[:-1] + 16)
+    rows = int((lens + 16).sum())
+    rng = np.random.default_rng(23)
+    inv = 1.0 / math.sqrt(hd)
+    q = rng.standard_normal((layers, B, nH, hd), dtype=np.float32)
+    pools, want = [], np.zeros((layers, B, nH, hd), np.float32)
+    for l in range(layers):
+        k8 = rng.integers(-128, 128, (rows, nKV, hd), dtype=np.int8)      # stale bytes between the sequences
+        v8 = rng.integers(-128, 128, (rows, nKV, hd), dtype=np.int8)
+        ks = np.full((rows, nKV), np.nan, np.float32)
+        vs = np.full_like(ks, np.nan)
+        for b in range(B):
+            n, r0 = int(lens[b]), int(base[b])
+            a, c, d, e = oracle.quant_kv8(rng.standard_normal((n, nKV, hd), dtype=np.float32),
+                                          rng.standard_normal((n, nKV, hd), dtype=np.float32), nKV, hd)
+            k8[r0:r0 + n], v8[r0:r0 + n], ks[r0:r0 + n], vs[r0:r0 + n] = a, c, d, e
+            want[l, b] = oracle.attention_i8(q[l, b:b + 1], a, c, d, e, 1, nH, nKV, hd, n - 1, inv)[0]
+        pools.append(tuple(dev(x) for x in (k8, v8, ks, vs)))
+    qd = dev(q)
+    ws = ops.workspace(B, nH, hd, numChunks)
+    for w in ws:
+        w.fill_(float("nan"))
+    tickets = torch.zeros(B * nKV, dtype=torch.int32, device="cuda")
+    dlens = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    dbase = torch.tensor(base, dtype=torch.int64, device="cuda")
+    out = torch.full((layers, B, nH, hd), float("nan"), device="cuda")
+    for rep in range(3):
+        for l in range(layers):
+            k8, v8, ks, vs = pools[l]
+            ops.decode_i8_batch(qd[l], k8, v8, ks, vs, out[l], ws, dlens, B, nH, nKV, hd, int(lens.max()), numChunks,
+                                row_base=dbase, invSqrt=inv, pdl=pdl, tickets=tickets)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert int(tickets.abs().sum().item()) == 0, "every counter is back at zero"
+    assert_close(host(out), want, what=f"in-kernel merge, pdl={pdl}")
+
+
+def test_merge_inside_the_kernel_equals_the_merge_launch():
+    """Same partials, same rule: the fused form against the two-launch form at the 7B shape, 8192 rows
+    (host length, one sequence), and a single-chunk call where nothing has to be merged."""
+    nH, nKV, hd = 28, 4, 128
+    rng = np.random.default_rng(29)
+    for ctx in (8192, 100):
+        k8, v8, ks, vs = oracle.quant_kv8(rng.standard_normal((ctx, nKV, hd), dtype=np.float32),
+                                          rng.standard_normal((ctx, nKV, hd), dtype=np.float32), nKV, hd)
+        q = rng.standard_normal((1, nH, hd), dtype=np.float32)
+        d = [dev(x) for x in (q, k8, v8, ks, vs)]
+        _, chunks = ops.split_geometry(ctx, nH, hd)
+        ws = ops.workspace(1, nH, hd, chunks)
+        tickets = torch.zeros(nKV, dtype=torch.int32, device="cuda")
+        a = torch.full((1, nH, hd), float("nan"), device="cuda")
+        b = torch.full_like(a, float("nan"))
+        ops.decode_i8_batch(*d, a, ws, None, 1, nH, nKV, hd, ctx, chunks, tickets=tickets)
+        ops.decode_i8_batch(*d, b, ws, None, 1, nH, nKV, hd, ctx, chunks)
+        torch.cuda.synchronize()
+        want = oracle.attention_i8(q, k8, v8, ks, vs, 1, nH, nKV, hd, ctx - 1, 1.0 / math.sqrt(hd))
+        assert_close(host(a), want, what=f"fused, ctx {ctx}")
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-6)
+        assert int(tickets.abs().sum().item()) == 0
+    assert ops.device_status() == 0

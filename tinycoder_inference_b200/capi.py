@@ -141,6 +141,7 @@ class DecodeI8Batch(C.Structure):
         ("prefetchRows", C.c_uint32),
         ("nextK8", C.c_void_p),
         ("nextV8", C.c_void_p),
+        ("mergeTickets", C.c_void_p),
     ]
 
 

@@ -27,6 +27,7 @@
 //     the caller's partial buffers in the reference's layout and are merged by
 //     the merge kernel (merge.cu).
 #include "tc_common.cuh"
+#include <cstdlib>
 #include <mutex>
 
 #include "decode_shared.cuh"
@@ -58,6 +59,15 @@ struct DecodeI8Params {
 };
 
 constexpr int kHD = 128;
+
+// TC_ATTN_LEGACY_DECODE=1 keeps head_dim 128 on the mma.sync kernel (comparison runs)
+static bool forceLegacyDecode() {
+    static const bool v = [] {
+        const char *e = getenv("TC_ATTN_LEGACY_DECODE");
+        return e != nullptr && e[0] == '1';
+    }();
+    return v;
+}
 // MT = 16-row MMA tiles one consumer warp folds per stage: 2 amortises the softmax
 // bookkeeping over 32 tokens (large problems), 1 halves the work quantum so that a
 // small problem still spreads evenly over 148 SMs x 8 warps.
@@ -560,6 +570,9 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
                  reinterpret_cast<uintptr_t>(d->q) | reinterpret_cast<uintptr_t>(d->out)) & 15u) == 0,
                TC_EINVAL, "decode_i8: q/out/k8/v8 need 16-byte alignment");
     TC_REQUIRE(d->numChunks >= 1, TC_EWORKSPACE, "decode_i8: no chunk slots");
+    // head_dim 128 runs on the tcgen05 integer path; this file's mma.sync kernel keeps head_dim
+    // 256 and the causal rows mode
+    if (hd == 128 && !forceLegacyDecode()) return decodeI8Tc(d, lenHost, lenAdd, st);
     // work quantum: 32 tokens per warp when every warp of the machine gets at least ~12
     // of them, 16 otherwise (see DecodeI8Smem)
     const uint64_t warpTiles32 = static_cast<uint64_t>(d->batch) * d->nKV * ((d->maxLen + 31) / 32);

@@ -11,6 +11,9 @@ int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out,
                 uint32_t lenAdd, uint32_t chunkTokens, uint8_t *q81, bool pdl, cudaStream_t st,
                 uint32_t chunksPerRank = 0, uint64_t rankStride = 0);
 
+// int8 decode on tcgen05 (decode_i8_tc.cu): head_dim 128, heads mode; arguments already validated
+int decodeI8Tc(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_t lenAdd, cudaStream_t st);
+
 // fp16-cache twins of the f32 decode / causal kernels (decode_kv16.cu); arguments already validated
 int decodeKv16(const float *q, const void *kvK, const void *kvV, float *attnOut, float *pAcc, float *pM, float *pL,
                uint32_t nHeads, uint32_t nKV, uint32_t hd, uint32_t pos, const uint32_t *devPos, uint64_t totalRows,

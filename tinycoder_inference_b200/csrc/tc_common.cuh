@@ -118,6 +118,32 @@ __device__ __forceinline__ void tmaLoad3D(void *dst, const CUtensorMap *m, uint6
             "l"(reinterpret_cast<uint64_t>(m)), "r"(smemAddr(bar)), "r"(c0), "r"(c1), "r"(c2)
             : "memory");
 }
+// L2 eviction policies for streaming data: evict_first for rows that are read once, evict_last for
+// rows fetched ahead of their use.
+__device__ __forceinline__ uint64_t l2PolicyEvictFirst() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2PolicyEvictLast() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tmaLoad3DHint(void *dst, const CUtensorMap *m, uint64_t *bar, int c0, int c1, int c2,
+                                              uint64_t policy) {
+    asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint"
+            " [%0], [%1, {%3, %4, %5}], [%2], %6;" ::"r"(smemAddr(dst)),
+            "l"(reinterpret_cast<uint64_t>(m)), "r"(smemAddr(bar)), "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+            : "memory");
+}
+__device__ __forceinline__ void tmaPrefetchL2_3DHint(const CUtensorMap *m, int c0, int c1, int c2, uint64_t policy) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile.L2::cache_hint [%0, {%1, %2, %3}], %4;" ::"l"(
+                         reinterpret_cast<uint64_t>(m)),
+                 "r"(c0), "r"(c1), "r"(c2), "l"(policy)
+                 : "memory");
+}
 // The same tile pulled into L2 only (no shared-memory destination, no completion to wait for).
 __device__ __forceinline__ void tmaPrefetchL2_3D(const CUtensorMap *m, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(

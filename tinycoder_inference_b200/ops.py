@@ -143,7 +143,7 @@ def decode_i8_noalloc(q, k8, v8, ks, vs, out, nHeads, nKV, hd, cachePos, invSqrt
 
 def decode_i8_batch(q, k8, v8, ks, vs, out, ws, lens, batch, nHeads, nKV, hd, maxLen, numChunks,
                     rows_per_seq=0, row_base=None, invSqrt=None, partials_only=False, pdl=False,
-                    prefetch_rows=0, next_kv=None):
+                    prefetch_rows=0, next_kv=None, tickets=None):
     """`batch` sequences in one pool; returns the chunk slots used per head.
     lens=None: every sequence is maxLen rows long (host length)."""
     if invSqrt is None:
@@ -159,6 +159,9 @@ def decode_i8_batch(q, k8, v8, ks, vs, out, ws, lens, batch, nHeads, nKV, hd, ma
     d.prefetchRows = prefetch_rows
     if next_kv is not None:
         d.nextK8, d.nextV8 = next_kv[0].data_ptr(), next_kv[1].data_ptr()
+    if tickets is not None:      # zeroed uint32 [batch * nKV]: the kernel merges its own partials
+        assert tickets.dtype == torch.int32 and tickets.numel() >= batch * nKV
+        d.mergeTickets = tickets.data_ptr()
     d.rowBase = row_base.data_ptr() if row_base is not None else None
     d.rowsPerSeq = rows_per_seq
     d.totalRows = k8.numel() // (nKV * hd)
