@@ -311,22 +311,29 @@ int tc_attn_merge_exchange_local(const float *const *pAcc, const float *const *p
 /* ------------------------------------------------------------------------- */
 
 /* Scratch bytes tc_attn_prefill_f16 needs (fp16 twins of q and of the K/V
- * rows; the reference keeps attnQ16 / attnKV16 for the same purpose,
- * GPUComputeForward.cu:3952-3968). */
-int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t nHeads,
-                                      uint32_t nKV, uint32_t hd, size_t *bytes);
+ * rows [0, cachePos + seqLen); the reference keeps attnQ16 / attnKV16 for the
+ * same purpose, GPUComputeForward.cu:3952-3968). */
+int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t cachePos,
+                                      uint32_t nHeads, uint32_t nKV,
+                                      uint32_t hd, size_t *bytes);
 
 /* Replaces the materialised dense prefill: kF32ToF16 x3, cuBLAS QK^T,
  * kAttnSoftmaxCausal, cuBLAS PV (GPUComputeForward.cu:3937-4026;
  * include/gpu/GpuAttentionKernels.hpp:323-353): causal attention of seqLen
- * query rows over cache rows [0, seqLen) (cachePos == 0), fp16 operands,
- * f32 accumulation, f32 softmax, probabilities rounded to fp16.  q f32
- * [seqLen][nHeads][hd]; kvK/kvV f32 cache rows; out f32.  No seqLen cap (the
- * reference stops at 512 because it materialises the score matrix). */
+ * query rows at positions cachePos .. cachePos + seqLen - 1 over cache rows
+ * [0, cachePos + seqLen), fp16 operands, f32 accumulation, f32 softmax,
+ * probabilities rounded to fp16.  q f32 [seqLen][nHeads][hd]; kvK/kvV the f32
+ * cache from row 0 (the new rows already appended); out f32.  No seqLen cap
+ * (the reference stops at 512 because it materialises the score matrix), and
+ * no cachePos == 0 condition: the reference takes this path only for the
+ * first chunk of a prompt (GPUComputeForward.cu:3828-3835) and sends the
+ * other 512-token chunks its caller cuts (ModelForward.cpp:115-127) through
+ * the scalar kernel; here every chunk runs on the tensor cores. */
 int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV,
                         float *out, void *scratch, size_t scratchBytes,
-                        uint32_t seqLen, uint32_t nHeads, uint32_t nKV,
-                        uint32_t hd, float invSqrt, tc_stream stream);
+                        uint32_t seqLen, uint32_t cachePos, uint32_t nHeads,
+                        uint32_t nKV, uint32_t hd, float invSqrt,
+                        tc_stream stream);
 
 /* Replaces kWarpAttention / kWarpAttentionPos and kQ35WarpAttention
  * (include/gpu/GpuAttentionKernels.hpp:211-272, 537-599;

@@ -69,3 +69,57 @@ def test_scratch_too_small_is_refused():
     with pytest.raises(capi.TcError) as e:
         ops.prefill_f16(q, k, k, q.clone(), s, 128, 4, 2, 128)
     assert e.value.code == capi.TC_EWORKSPACE
+
+
+def _scratch(S, nH, nKV, cachePos):
+    n = ops.prefill_f16_scratch_bytes(S, nH, nKV, 128, cachePos=cachePos)
+    buf = torch.empty(n + 1024, dtype=torch.uint8, device="cuda")
+    off = (-buf.data_ptr()) % 1024
+    return buf[off:off + n]
+
+
+@pytest.mark.parametrize("cachePos,S,nH,nKV", [(100, 300, 4, 2), (64, 64, 2, 1), (1, 1, 4, 4), (513, 257, 7, 1), (1000, 40, 8, 2)])
+def test_continued_prefill_over_an_existing_cache(cachePos, S, nH, nKV):
+    """Query rows at positions cachePos.. over cache rows [0, cachePos + S): positions that are no
+    multiple of the 64-token KV tile, a diagonal that crosses three tiles, a single row."""
+    hd = 128
+    rng = np.random.default_rng(cachePos + S)
+    total = cachePos + S
+    q = rng.standard_normal((S, nH, hd), dtype=np.float32)
+    k = rng.standard_normal((total, nKV, hd), dtype=np.float32)
+    v = rng.standard_normal((total, nKV, hd), dtype=np.float32)
+    inv = 1.0 / math.sqrt(hd)
+    # rows behind the window of this call: must never be read as data
+    kd = torch.cat([dev(k), torch.full((70, nKV, hd), float("nan"), device="cuda")])
+    vd = torch.cat([dev(v), torch.full((70, nKV, hd), float("nan"), device="cuda")])
+    out = torch.full((S, nH, hd), float("nan"), device="cuda")
+    ops.prefill_f16(dev(q), kd, vd, out, _scratch(S, nH, nKV, cachePos), S, nH, nKV, hd, invSqrt=inv, cachePos=cachePos)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    want = oracle.prefill_f16_rows(q, k, v, np.arange(S), S, nH, nKV, hd, inv, cachePos=cachePos)
+    assert_close(host(out), want, rtol=RTOL16, atol=ATOL16, what=f"continued prefill at {cachePos}+{S}")
+
+
+def test_eight_chunks_of_512_equal_one_prefill_of_4096():
+    """The engine feeds a long prompt in 512-token calls (ModelForward.cpp:115-127).  Every chunk runs on
+    the tensor-core kernel; the chunks together equal the single call and both match the oracle."""
+    nH, nKV, hd, S, C = 28, 4, 128, 4096, 512
+    inv = 1.0 / math.sqrt(hd)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(77)
+    q = torch.randn((S, nH, hd), generator=g, device="cuda")
+    k = torch.randn((S, nKV, hd), generator=g, device="cuda")
+    v = torch.randn((S, nKV, hd), generator=g, device="cuda")
+    whole = torch.full((S, nH, hd), float("nan"), device="cuda")
+    ops.prefill_f16(q, k, v, whole, _scratch(S, nH, nKV, 0), S, nH, nKV, hd, invSqrt=inv)
+    parts = torch.full((S, nH, hd), float("nan"), device="cuda")
+    sc = _scratch(C, nH, nKV, S - C)
+    for c0 in range(0, S, C):
+        ops.prefill_f16(q[c0:c0 + C], k, v, parts[c0:c0 + C], sc, C, nH, nKV, hd, invSqrt=inv, cachePos=c0)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(host(parts), host(whole), rtol=RTOL16, atol=ATOL16, what="8 x 512 against 1 x 4096")
+    rows = np.array(sorted(set(range(0, S, 128)) | {511, 512, 513, 1023, 1024, 2047, 2048, 3583, 3584} | set(range(S - 32, S))), np.uint32)
+    want = oracle.prefill_f16_rows(host(q), host(k), host(v), rows, S, nH, nKV, hd, inv)
+    assert_close(host(parts)[rows], want, rtol=RTOL16, atol=ATOL16, what="chunked prefill against the oracle")
+    assert_close(host(whole)[rows], want, rtol=RTOL16, atol=ATOL16, what="single prefill against the oracle")

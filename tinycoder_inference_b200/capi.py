@@ -186,8 +186,8 @@ SIGNATURES = {
     "tc_attn_merge_exchange": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, C.POINTER(PeerGroup), _u32, _vp]),
     "tc_attn_merge_exchange_local": (_i, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
                                           C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _vp]),
-    "tc_attn_prefill_f16_scratch_bytes": (_i, [_u32, _u32, _u32, _u32, _sz_p]),
-    "tc_attn_prefill_f16": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_size_t, _u32, _u32, _u32, _u32, _f, _vp]),
+    "tc_attn_prefill_f16_scratch_bytes": (_i, [_u32, _u32, _u32, _u32, _u32, _sz_p]),
+    "tc_attn_prefill_f16": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_size_t, _u32, _u32, _u32, _u32, _u32, _f, _vp]),
     "tc_attn_prefill_kv": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _u64, _f, _i, _vp]),
     "tc_attn_prefill_i8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _u64, _f, _vp]),
     "tc_attn_sigmoid_gate": (_i, [_vp, _vp, _u32, _u32, _u32, _vp]),

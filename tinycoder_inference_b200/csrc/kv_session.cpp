@@ -198,12 +198,14 @@ int tc_kv_session_attend(tc_kv_session *s, uint32_t slot, float *q, const float 
         return tc_attn_decode_kv(q, kvK, kvV, attnOut, c.pAcc, c.pM, c.pL, 1, nH, nKV, hd, hostBound, devPos,
                                  c.maxSeqLen, c.numChunks, 0, s->invSqrt, c.kvHalf, nullptr, stream);
     }
-    // a fresh prompt on the f32 cache takes the tensor-core prefill when the caller gave it scratch
-    if (pos == 0 && devPos == nullptr && !graphCapture && !c.kvHalf && hd == 128 && c.prefillScratch != nullptr) {
+    // every multi-row call on the f32 cache -- the first chunk of a prompt and the chunks behind it
+    // (ModelForward.cpp:115-127 cuts prompts into 512-token calls) -- takes the tensor-core prefill
+    // when the caller's scratch holds the fp16 twins of the rows it attends over
+    if (devPos == nullptr && !graphCapture && !c.kvHalf && hd == 128 && c.prefillScratch != nullptr) {
         size_t need = 0;
-        if (tc_attn_prefill_f16_scratch_bytes(seqLen, nH, nKV, hd, &need) == TC_OK && need <= c.prefillScratchBytes)
+        if (tc_attn_prefill_f16_scratch_bytes(seqLen, pos, nH, nKV, hd, &need) == TC_OK && need <= c.prefillScratchBytes)
             return tc_attn_prefill_f16(q, static_cast<const float *>(kvK), static_cast<const float *>(kvV), attnOut,
-                                       c.prefillScratch, c.prefillScratchBytes, seqLen, nH, nKV, hd, s->invSqrt,
+                                       c.prefillScratch, c.prefillScratchBytes, seqLen, pos, nH, nKV, hd, s->invSqrt,
                                        stream);
     }
     return tc_attn_prefill_kv(q, kvK, kvV, attnOut, seqLen, nH, nKV, hd, pos, devPos, c.maxSeqLen, s->invSqrt,

@@ -78,7 +78,8 @@ f32ToF16x3Kernel(const float4 *__restrict__ q, const float4 *__restrict__ k, con
 struct PrefillF16Params {
     float *out;        // [seqLen][nHeads][128] f32
     uint32_t seqLen, nHeads, nKV, group;
-    uint32_t nQTiles;  // 256-row query blocks
+    uint32_t cachePos;  // query row r sits at position cachePos + r and sees K/V rows [0, cachePos + r]
+    uint32_t nQTiles;   // 256-row query blocks
     float scaleLog2;   // invSqrt * log2(e)
     unsigned int *err;
 };
@@ -91,8 +92,8 @@ struct PrefillF16Smem {
     static constexpr int kStage = kK01 + 2 * kKvTile;  // stage s: K slot, then V slot
     static constexpr int kStageBytes = 2 * kKvTile;
     static constexpr int kBars = kStage + kPfStages * kStageBytes;
-    // qFull, k01Full, stage full + empty, sFull[2][2], pFull[2][2], pvDone[2]
-    static constexpr int kNumBars = 2 + 2 * kPfStages + 4 + 4 + 2;
+    // qFull, k01Full, stage full + empty, sFull[2][2], pFull[2][2], pvDone[2], pvBuf[2][2]
+    static constexpr int kNumBars = 2 + 2 * kPfStages + 4 + 4 + 2 + 4;
     static constexpr int kTmemSlot = kBars + kNumBars * 8;
     static constexpr int kTotal = kTmemSlot + 16 + 1024;
 };
@@ -120,9 +121,10 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // never carries out of the field).
 __device__ __forceinline__ uint64_t descAdvance(uint64_t d, uint32_t bytes) { return d + (bytes >> 4); }
 
-// 352 threads: warps 0-3 softmax of query tile A, warps 4-7 softmax of query tile B
-// (rows 128 further down), warp 8 TMA producer, warps 9 and 10 MMA issuers of A and B.
-constexpr int kPfThreads = 352;
+// 416 threads: warps 0-3 softmax of query tile A, warps 4-7 softmax of query tile B
+// (rows 128 further down), warp 8 TMA producer, warps 9 and 10 issue the score products of A and
+// B, warps 11 and 12 their P.V products.
+constexpr int kPfThreads = 416;
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const PrefillF16Params p) {
@@ -132,7 +134,8 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::kBars);
     uint64_t *qFull = bars, *k01Full = bars + 1, *stFull = bars + 2, *stEmpty = stFull + NS,
-             *sFull = stEmpty + NS /* [x][b] */, *pFull = sFull + 4 /* [x][b] */, *pvDone = pFull + 4 /* [x] */;
+             *sFull = stEmpty + NS /* [x][b] */, *pFull = sFull + 4 /* [x][b] */, *pvDone = pFull + 4 /* [x] */,
+             *pvBuf = pvDone + 2 /* [x][b] */;
     uint32_t *tmemSlot = reinterpret_cast<uint32_t *>(smem + L::kTmemSlot);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -141,10 +144,12 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t head = blockIdx.x % p.nHeads;
     const uint32_t kvHead = head / p.group;
     const uint32_t m0 = qb * 2u * kPfBM;
-    // query tile X (0 = A, 1 = B) covers rows m0 + 128 X ..; it sees KV tiles 0 .. nX - 1 (64 tokens
-    // each; the last two straddle its diagonal).  B may lie wholly past the sequence.
+    // query tile X (0 = A, 1 = B) covers rows m0 + 128 X .. at positions cachePos + row; it sees KV
+    // tiles 0 .. nX - 1 (64 tokens each; the last two or three straddle its diagonal).  B may lie
+    // wholly past the sequence.
     const bool activeB = m0 + kPfBM < p.seqLen;
-    const uint32_t nA = 4u * qb + 2u, nB = activeB ? 4u * qb + 4u : 0u;
+    const uint32_t nA = (p.cachePos + m0 + kPfBM + kPfBN - 1u) / kPfBN;
+    const uint32_t nB = activeB ? (p.cachePos + m0 + 2u * kPfBM + kPfBN - 1u) / kPfBN : 0u;
     const uint32_t nTiles = activeB ? nB : nA;
 
     if (threadIdx.x == 0) {
@@ -152,7 +157,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbarInit(k01Full, 1);
         for (uint32_t s = 0; s < NS; ++s) {
             mbarInit(&stFull[s], 1);
-            mbarInit(&stEmpty[s], 2);  // both MMA warps release a stage
+            mbarInit(&stEmpty[s], 4);  // all four MMA warps release a stage
         }
         for (int i = 0; i < 4; ++i) {
             mbarInit(&sFull[i], 1);
@@ -160,6 +165,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         mbarInit(&pvDone[0], 1);
         mbarInit(&pvDone[1], 1);
+        for (int i = 0; i < 4; ++i) mbarInit(&pvBuf[i], 1);
         fenceBarrierInit();
         tmaPrefetchDesc(&tmQ);
         tmaPrefetchDesc(&tmK);
@@ -209,11 +215,15 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
     } else if (warp >= 9) {
         // ------------------------------- MMA issuers -------------------------------
-        // Warp 9 + X issues for query tile X: S_X(0), S_X(1), then per KV tile j:
-        // [wait P_X(j)] O_X += P_X(j) V_j, S_X(j+2) -- the latter into the buffer P_X(j) occupies,
-        // hence behind its PV product (products of one thread execute in issue order).
+        // Issuing one tcgen05.mma costs its thread about a hundred cycles whatever the shape, and
+        // threads of different warps issue concurrently.  So the score products and the P.V products
+        // of a query tile have an issuing warp each: warp 9 + X issues S_X(j) = Q_X K_j^T (M128 N64
+        // K16 x8), warp 11 + X issues O_X += P_X(j) V_j (A from TMEM, B = V MN-major from shared
+        // memory, K16 x4).  S_X(j+2) goes into the buffer P_X(j) occupies: the score warp waits for
+        // the commit of that P.V product (pvBuf) before it issues.
         // All 32 lanes run this warp-uniform code; only lane 0 executes the tcgen05 instructions.
-        const uint32_t x = warp - 9u;
+        const uint32_t x = (warp - 9u) & 1u;
+        const bool pvRole = warp >= 11u;
         const uint32_t issue = lane == 0 ? 1u : 0u;
         const uint32_t myTiles = x == 0 ? nA : nB;
         constexpr uint32_t idQK = umaInstrDescF16(kPfBM, kPfBN, 0, 0);
@@ -232,13 +242,16 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             umaCommitIf(issue, &sFull[2u * x + (j & 1u)]);
         };
-        bool ok = myTiles != 0 && pfWait(qFull, 0, p.err, kDevErrFullWait) && pfWait(k01Full, 0, p.err, kDevErrFullWait);
-        if (ok) {
-            tcFenceAfter();
-            issueQK(dK01, 0);
-            issueQK(descAdvance(dK01, L::kKvTile), 1);
+        bool ok = myTiles != 0;
+        if (!pvRole) {
+            ok = ok && pfWait(qFull, 0, p.err, kDevErrFullWait) && pfWait(k01Full, 0, p.err, kDevErrFullWait);
+            if (ok) {
+                tcFenceAfter();
+                issueQK(dK01, 0);
+                issueQK(descAdvance(dK01, L::kKvTile), 1);
+            }
         }
-        // Every stage is released by both warps, also the ones past this tile's diagonal -- but
+        // Every stage is released by all four warps, also the ones past a tile's diagonal -- but
         // only after the stage has been filled: a warp with nothing to do must not run ahead and
         // hand in the release of a later round, or the barrier would complete without the warp
         // that still reads the stage.
@@ -246,17 +259,26 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (uint32_t j = 0; j < nTiles; ++j) {
             const uint32_t s = j % NS;
             okFull = okFull && pfWait(&stFull[s], (j / NS) & 1u, p.err, kDevErrFullWait);
-            if (ok && okFull && j < myTiles) {
-                ok = pfWait(&pFull[2u * x + (j & 1u)], (j >> 1) & 1u, p.err, kDevErrMmaWait);
-                if (ok) {
-                    tcFenceAfter();
-                    const uint64_t dV = descAdvance(dVs, s * L::kStageBytes);
-                    const uint32_t tP = tS0 + 64u * (j & 1u);
+            if (ok && okFull) {
+                if (pvRole && j < myTiles) {
+                    ok = pfWait(&pFull[2u * x + (j & 1u)], (j >> 1) & 1u, p.err, kDevErrMmaWait);
+                    if (ok) {
+                        tcFenceAfter();
+                        const uint64_t dV = descAdvance(dVs, s * L::kStageBytes);
+                        const uint32_t tP = tS0 + 64u * (j & 1u);
 #pragma unroll
-                    for (uint32_t ks = 0; ks < 4; ++ks)  // 16 tokens per step: 8 columns of fp16 P, 2 KB of V
-                        umaMmaTSIf(issue, tO, tP + ks * 8u, descAdvance(dV, ks * 2048u), idPV, (j > 0 || ks > 0) ? 1u : 0u);
-                    umaCommitIf(issue, &pvDone[x]);
-                    if (j + 2 < myTiles) issueQK(descAdvance(dKs, s * L::kStageBytes), j + 2);
+                        for (uint32_t ks = 0; ks < 4; ++ks)  // 16 tokens per step: 8 columns of fp16 P, 2 KB of V
+                            umaMmaTSIf(issue, tO, tP + ks * 8u, descAdvance(dV, ks * 2048u), idPV, (j > 0 || ks > 0) ? 1u : 0u);
+                        umaCommitIf(issue, &pvDone[x]);
+                        umaCommitIf(issue, &pvBuf[2u * x + (j & 1u)]);
+                    }
+                } else if (!pvRole && j + 2 < myTiles) {
+                    // the buffer S_X(j+2) goes into is the one P_X(j) sits in until its P.V product is done
+                    ok = pfWait(&pvBuf[2u * x + (j & 1u)], (j >> 1) & 1u, p.err, kDevErrMmaWait);
+                    if (ok) {
+                        tcFenceAfter();
+                        issueQK(descAdvance(dKs, s * L::kStageBytes), j + 2);
+                    }
                 }
             }
             umaCommitIf(issue, &stEmpty[s]);
@@ -284,10 +306,11 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tmemLd32(tS + laneBase, r[0]);
             tmemLd32(tS + laneBase + 32u, r[1]);
             tmemLdWait();
-            if (j + 2u >= myTiles) {
-                // causal edge: token 64 j + c is visible iff it is not past the query position;
-                // relative to the block's first row that is 64 (j - 4 qb) + c <= rowInBlock
-                const int32_t first = 64 * (static_cast<int32_t>(j) - 4 * static_cast<int32_t>(qb));
+            if (64u * j + 63u > p.cachePos + m0 + x * kPfBM) {
+                // causal edge (the tile reaches past the position of this tile's first row): token
+                // 64 j + c is visible iff it is not past the query position; relative to the block's
+                // first row that is 64 j - (cachePos + m0) + c <= rowInBlock
+                const int32_t first = static_cast<int32_t>(64u * j) - static_cast<int32_t>(p.cachePos + m0);
 #pragma unroll
                 for (int c = 0; c < 2; ++c)
 #pragma unroll
@@ -401,26 +424,28 @@ static int f16Map(const void *base, uint32_t heads, uint32_t rows, uint32_t boxR
     return getTensorMap(key, out);
 }
 
-static size_t prefillScratchBytes(uint32_t seqLen, uint32_t nHeads, uint32_t nKV) {
-    // fp16 twins: q [seqLen][nHeads][128], k and v [seqLen][nKV][128]; each region 1 KB aligned
+static size_t prefillScratchBytes(uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV) {
+    // fp16 twins: q [seqLen][nHeads][128], k and v [cachePos + seqLen][nKV][128]; each region 1 KB aligned
     auto al = [](size_t x) { return (x + 1023) & ~size_t(1023); };
-    return al(static_cast<size_t>(seqLen) * nHeads * kPfHD * 2) + 2 * al(static_cast<size_t>(seqLen) * nKV * kPfHD * 2);
+    return al(static_cast<size_t>(seqLen) * nHeads * kPfHD * 2) +
+           2 * al((static_cast<size_t>(cachePos) + seqLen) * nKV * kPfHD * 2);
 }
 
 }  // namespace tc
 
 extern "C" {
 
-int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t nHeads, uint32_t nKV, uint32_t hd, size_t *bytes) {
+int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV, uint32_t hd,
+                                      size_t *bytes) {
     TC_REQUIRE(bytes != nullptr, TC_EINVAL, "tc_attn_prefill_f16_scratch_bytes: null output");
     TC_REQUIRE(hd == tc::kPfHD, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 128)", hd);
-    *bytes = tc::prefillScratchBytes(seqLen, nHeads, nKV);
+    *bytes = tc::prefillScratchBytes(seqLen, cachePos, nHeads, nKV);
     return TC_OK;
 }
 
 int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, float *out, void *scratch,
-                        size_t scratchBytes, uint32_t seqLen, uint32_t nHeads, uint32_t nKV, uint32_t hd,
-                        float invSqrt, tc_stream stream) {
+                        size_t scratchBytes, uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV,
+                        uint32_t hd, float invSqrt, tc_stream stream) {
     using namespace tc;
     TC_REQUIRE(q && kvK && kvV && out && scratch, TC_EINVAL, "tc_attn_prefill_f16: null pointer");
     TC_REQUIRE(hd == kPfHD, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 128)", hd);
@@ -430,9 +455,11 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
                  reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(scratch)) & 15u) == 0,
                TC_EINVAL, "tc_attn_prefill_f16: pointers need 16-byte alignment");
     if (seqLen == 0) return TC_OK;
-    TC_REQUIRE(scratchBytes >= prefillScratchBytes(seqLen, nHeads, nKV), TC_EWORKSPACE,
+    TC_REQUIRE(static_cast<uint64_t>(cachePos) + seqLen < (1ull << 31), TC_EUNSUPPORTED,
+               "tc_attn_prefill_f16: %u + %u rows", cachePos, seqLen);
+    TC_REQUIRE(scratchBytes >= prefillScratchBytes(seqLen, cachePos, nHeads, nKV), TC_EWORKSPACE,
                "tc_attn_prefill_f16: scratch of %zu bytes, %zu needed", scratchBytes,
-               prefillScratchBytes(seqLen, nHeads, nKV));
+               prefillScratchBytes(seqLen, cachePos, nHeads, nKV));
     TC_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 1023u) == 0, TC_EINVAL,
                "tc_attn_prefill_f16: scratch needs 1024-byte alignment");
     const uint32_t nQTiles = (seqLen + 2 * kPfBM - 1) / (2 * kPfBM);  // 256-row query blocks
@@ -441,7 +468,8 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     auto al = [](size_t x) { return (x + 1023) & ~size_t(1023); };
     const size_t qElems = static_cast<size_t>(seqLen) * nHeads * kPfHD;
-    const size_t kvElems = static_cast<size_t>(seqLen) * nKV * kPfHD;
+    const uint32_t kvRows = cachePos + seqLen;  // the cache rows this call attends over
+    const size_t kvElems = static_cast<size_t>(kvRows) * nKV * kPfHD;
     uint8_t *sc = static_cast<uint8_t *>(scratch);
     void *q16 = sc, *k16 = sc + al(qElems * 2), *v16 = sc + al(qElems * 2) + al(kvElems * 2);
     const int sms = numSMs();
@@ -456,13 +484,14 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     CUtensorMap tmQ, tmK, tmV;
     int rc = f16Map(q16, nHeads, seqLen, kPfBM, &tmQ);
     if (rc != TC_OK) return rc;
-    rc = f16Map(k16, nKV, seqLen, kPfBN, &tmK);
+    rc = f16Map(k16, nKV, kvRows, kPfBN, &tmK);
     if (rc != TC_OK) return rc;
-    rc = f16Map(v16, nKV, seqLen, kPfBN, &tmV);
+    rc = f16Map(v16, nKV, kvRows, kPfBN, &tmV);
     if (rc != TC_OK) return rc;
     PrefillF16Params prm;
     prm.out = out;
     prm.seqLen = seqLen;
+    prm.cachePos = cachePos;
     prm.nHeads = nHeads;
     prm.nKV = nKV;
     prm.group = nHeads / nKV;

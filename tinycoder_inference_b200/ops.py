@@ -225,18 +225,19 @@ def merge_exchange_local(wss, outs, buffers, nHeads, numChunks, activeChunks, hd
 
 # ---- prefill ------------------------------------------------------------------
 
-def prefill_f16_scratch_bytes(seqLen, nHeads, nKV, hd) -> int:
+def prefill_f16_scratch_bytes(seqLen, nHeads, nKV, hd, cachePos=0) -> int:
     b = C.c_size_t()
-    check(lib.tc_attn_prefill_f16_scratch_bytes(seqLen, nHeads, nKV, hd, C.byref(b)))
+    check(lib.tc_attn_prefill_f16_scratch_bytes(seqLen, cachePos, nHeads, nKV, hd, C.byref(b)))
     return b.value
 
 
-def prefill_f16(q, kvK, kvV, out, scratch, seqLen, nHeads, nKV, hd, invSqrt=None):
+def prefill_f16(q, kvK, kvV, out, scratch, seqLen, nHeads, nKV, hd, invSqrt=None, cachePos=0):
+    """seqLen query rows at positions cachePos.. over cache rows [0, cachePos + seqLen) of kvK / kvV."""
     if invSqrt is None:
         invSqrt = 1.0 / math.sqrt(hd)
     check(lib.tc_attn_prefill_f16(_ptr(q), _ptr(kvK), _ptr(kvV), _ptr(out), _ptr(scratch),
-                                  scratch.numel() * scratch.element_size(), seqLen, nHeads, nKV, hd, invSqrt,
-                                  _stream()))
+                                  scratch.numel() * scratch.element_size(), seqLen, cachePos, nHeads, nKV, hd,
+                                  invSqrt, _stream()))
 
 
 def prefill_kv(q, kvK, kvV, out, seqLen, nHeads, nKV, hd, cachePos, invSqrt=None, dev_pos=None):
@@ -329,7 +330,8 @@ class KvSession:
             self._keep += list(rope)
             cfg.ropeCos, cfg.ropeSin = rope[0].data_ptr(), rope[1].data_ptr()
         if prefill_scratch_rows:
-            n = prefill_f16_scratch_bytes(prefill_scratch_rows, nHeads, nKV, hd)
+            # room for the fp16 twins of `prefill_scratch_rows` query rows over the whole window
+            n = prefill_f16_scratch_bytes(prefill_scratch_rows, nHeads, nKV, hd, cachePos=max(0, max_seq - prefill_scratch_rows))
             buf = torch.empty(n + 1024, dtype=torch.uint8, device=dev)
             off = (-buf.data_ptr()) % 1024
             self._keep.append(buf)
