@@ -2,6 +2,8 @@
 // f32/fp16 cache): the bounded mbarrier wait, the chunk plan, the merge launcher.
 #pragma once
 
+#include <cstdlib>
+
 #include "tc_common.cuh"
 
 namespace tc {
@@ -59,7 +61,8 @@ inline DecodePlan planDecode(uint32_t batch, uint32_t nKV, uint32_t maxLen, uint
     pl.tileTokens = rowsPerStage / pl.hpc;
     const uint32_t tilesMax = (maxLen + pl.tileTokens - 1) / pl.tileTokens;
     const uint32_t sms = static_cast<uint32_t>(numSMs());
-    const uint32_t waves = (batch > 1 && !uniformLengths) ? 4u : 1u;
+    uint32_t waves = (batch > 1 && !uniformLengths) ? 4u : 1u;
+    if (waves > 1u) { const char *e = getenv("TC_WAVES"); if (e) waves = static_cast<uint32_t>(atoi(e)); }
     uint32_t want = (sms * waves) / (batch * pl.headGroups);
     want = want < 1u ? 1u : want;
     want = want > slots ? slots : want;
