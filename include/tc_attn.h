@@ -435,6 +435,33 @@ uint64_t tc_kv_bytes_per_token(const tc_context_request *r, uint32_t kv, uint32_
 uint64_t tc_kv_store_bytes_per_token(const tc_context_request *r, uint32_t kv, uint32_t mirror);
 /* planContext (src/cpp/core/ContextPlan.cpp:80-246). */
 int tc_context_plan_compute(const tc_context_request *r, tc_context_plan *plan);
+
+/* No counterpart in the reference (it plans for one device).  The same ladder for a KV cache
+ * that is partitioned over headParts x ctxParts GPUs: every GPU stores the K/V rows of
+ * ceil(numKVHeads / headParts) kv heads and of a 1 / ctxParts share of the window (the two
+ * partitions of tc_attn_merge_exchange and of the kv-head split).  The request describes ONE
+ * GPU (its free memory, the weight bytes it holds, its fixed overhead); the plan is the one
+ * every GPU can honour.  plan.seqLen / maxAllowed are whole-window rows, plan.kvBytes and the
+ * fields below are per GPU.  headParts == ctxParts == 1 gives tc_context_plan_compute's plan
+ * bit for bit.  A context range shorter than the planner's 1024-row floor is refused like a
+ * window shorter than it. */
+typedef struct tc_context_shard_plan {
+    tc_context_plan plan;
+    uint32_t headParts, ctxParts;
+    uint32_t kvHeadsPerGpu;
+    uint32_t rowsPerGpu;         /* ceil(seqLen / ctxParts), rounded up to 256 rows */
+} tc_context_shard_plan;
+int tc_context_plan_compute_sharded(const tc_context_request *r, uint32_t headParts, uint32_t ctxParts,
+                                    tc_context_shard_plan *out);
+
+/* What this library itself needs next to weights and KV on one GPU, for gpuFixedOverhead (the
+ * reference's 1408 MiB default, include/ContextPlan.hpp:58, was measured on its 11 GB cards with
+ * its own scratch): the split-KV partial buffers of tc_attn_workspace_bytes at the 512-slot
+ * capacity, the exchange buffers of a context split, the fp16 twins of the tensor-core prefill
+ * for `prefillChunk`-row calls over the GPU's rows (f32 / fp16 store only), plus
+ * `runtimeReserve` bytes for the CUDA context and the caller's allocator slack. */
+uint64_t tc_context_overhead_bytes(uint32_t nHeads, uint32_t nKV, uint32_t hd, uint32_t window, uint32_t headParts,
+                                   uint32_t ctxParts, int kvStoreI8, uint32_t prefillChunk, uint64_t runtimeReserve);
 /* probeFreeVramBytes / probeTotalVramBytes (src/cpp/core/ContextPlan.cpp:248-272)
  * for the current device; 0 when there is none. */
 uint64_t tc_probe_free_vram_bytes(void);

@@ -7,7 +7,7 @@ import os
 import pytest
 
 import oracle
-from tinycoder_inference_b200 import ops
+from tinycoder_inference_b200 import capi, ops
 
 MiB = 1 << 20
 GiB = 1 << 30
@@ -178,3 +178,67 @@ def test_pool_geometry():
     assert g.partialAccBytes == 24 * 512 * 256 * 4
     g = ops.kv_pool_geometry(2048, 28, 0, 28, 4, 128)
     assert g.kvSlots == 28 and g.kvLayerStride == 2048 * 4 * 128 * 4 and g.kv8AllocBytes == 0
+
+
+# ---- the partitioned planner (no counterpart in the reference) --------------------------------
+
+def _req32b(**kw):
+    """The 32B-shaped request of the long-context configuration: 64 attention layers, 8 kv heads, head_dim 128."""
+    base = dict(requested=131072, modelMax=131072, numLayers=64, numAttentionLayers=64, numKVHeads=8, headDim=128,
+                ropeDims=128, int8KvSupported=1, weightBytes=0, freeVram=24 << 30, gpuFixedOverhead=900 << 20)
+    base.update(kw)
+    return ops.context_request(**base)
+
+
+def test_sharded_plan_of_one_gpu_is_the_reference_plan():
+    with open(os.path.join(os.path.dirname(__file__), "golden", "planner_golden.json")) as f:
+        cases = json.load(f)
+    for c in cases[:160]:
+        req = ops.context_request(**c["request"])
+        assert {k: v for k, v in ops.plan_context_sharded(req, 1, 1).items()
+                if k in c["plan"]} == ops.plan_context(req)
+
+
+def test_long_context_fits_a_partition_where_one_gpu_cannot():
+    one = ops.plan_context(_req32b())
+    per_token_i8 = 64 * (2 * 8 * 128 + 2 * 8 * 4) + 4 * 128          # 135,680 bytes: 131072 rows = 17.8 GB
+    assert ops.kv_bytes_per_token(_req32b(), capi.TC_KV_I8, 0) == per_token_i8
+    assert one["seqLen"] == 131072 and one["kv"] == capi.TC_KV_I8    # 24 GB: only the int8 store holds the window
+    tight = ops.plan_context(_req32b(freeVram=12 << 30))
+    assert tight["reduced"] == 1 and tight["seqLen"] < 131072        # 12 GB: not even int8
+    for hp, cp in ((8, 1), (4, 2), (2, 4), (1, 8)):
+        p = ops.plan_context_sharded(_req32b(freeVram=12 << 30), hp, cp)
+        assert p["seqLen"] == 131072 and p["reduced"] == 0, (hp, cp, p)
+        assert p["kvHeadsPerGpu"] == 8 // hp and p["rowsPerGpu"] == 131072 // cp
+        # what one GPU stores: its heads of its rows
+        req_g = _req32b(numKVHeads=8 // hp)
+        assert p["kvBytes"] == p["rowsPerGpu"] * ops.kv_bytes_per_token(req_g, p["kv"], p["kvMirror"])
+    # with 8 GPUs by heads even the f32 store with its int8 decode pool fits in 24 GB per GPU
+    best = ops.plan_context_sharded(_req32b(), 8, 1)
+    assert best["kv"] == capi.TC_KV_F32 and best["kvMirror"] == 1 and best["seqLen"] == 131072
+
+
+def test_sharded_plan_edges():
+    # an auto request keeps the single-device window, the ceiling grows with the context ranges
+    auto = ops.plan_context_sharded(_req32b(requested=0, freeVram=12 << 30), 1, 4)
+    assert auto["seqLen"] == 2048 and auto["maxAllowed"] >= ops.plan_context(_req32b(requested=0, freeVram=12 << 30))["maxAllowed"]
+    # a context range below the 1024-row floor is refused like a window below it
+    tiny = ops.plan_context_sharded(_req32b(requested=4096), 1, 8)
+    assert tiny["seqLen"] == 0 and "floor" in tiny["reason"]
+    # ragged division: 7 ranges of a 100000-row window, 256-row units
+    rag = ops.plan_context_sharded(_req32b(requested=100000), 2, 7)
+    assert rag["seqLen"] == 100000 and rag["rowsPerGpu"] == 14336 and rag["rowsPerGpu"] * 7 >= 100000
+    with pytest.raises(capi.TcError):
+        ops.plan_context_sharded(_req32b(), 0, 1)
+
+
+def test_overhead_follows_the_library_scratch():
+    base = ops.context_overhead_bytes(40, 8, 128, 131072, runtime_reserve=0)
+    assert base == 40 * 512 * 130 * 4                                # partial buffers only (int8 store, one GPU)
+    split = ops.context_overhead_bytes(40, 8, 128, 131072, head_parts=2, ctx_parts=4, runtime_reserve=0)
+    assert split > 20 * 512 * 130 * 4 and split < base                # half the heads, plus exchange buffers
+    f32 = ops.context_overhead_bytes(28, 4, 128, 32768, kv_store_i8=False, runtime_reserve=0)
+    twins = 512 * 28 * 128 * 2 + 2 * 32768 * 4 * 128 * 2               # q of a 512-row chunk, K/V of the window, fp16
+    assert f32 == 28 * 512 * 130 * 4 + twins
+    assert ops.context_overhead_bytes(28, 4, 128, 32768, runtime_reserve=1 << 20) - ops.context_overhead_bytes(
+        28, 4, 128, 32768, runtime_reserve=0) == 1 << 20

@@ -78,6 +78,11 @@ class ContextPlan(C.Structure):
         }
 
 
+class ContextShardPlan(C.Structure):
+    _fields_ = [("plan", ContextPlan), ("headParts", C.c_uint32), ("ctxParts", C.c_uint32),
+                ("kvHeadsPerGpu", C.c_uint32), ("rowsPerGpu", C.c_uint32)]
+
+
 class KvPoolGeometry(C.Structure):
     _fields_ = [
         ("kvLayerStride", C.c_uint64),
@@ -195,6 +200,8 @@ SIGNATURES = {
     "tc_kv_bytes_per_token": (_u64, [C.POINTER(ContextRequest), _u32, _u32]),
     "tc_kv_store_bytes_per_token": (_u64, [C.POINTER(ContextRequest), _u32, _u32]),
     "tc_context_plan_compute": (_i, [C.POINTER(ContextRequest), C.POINTER(ContextPlan)]),
+    "tc_context_plan_compute_sharded": (_i, [C.POINTER(ContextRequest), _u32, _u32, C.POINTER(ContextShardPlan)]),
+    "tc_context_overhead_bytes": (_u64, [_u32, _u32, _u32, _u32, _u32, _u32, _i, _u32, _u64]),
     "tc_probe_free_vram_bytes": (_u64, []),
     "tc_probe_total_vram_bytes": (_u64, []),
     "tc_kv_pool_geometry_compute": (_i, [_u32, _u32, _u32, _u32, _u32, _u32, _i, _i, _i,

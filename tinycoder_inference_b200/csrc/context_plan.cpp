@@ -148,6 +148,71 @@ int tc_context_plan_compute(const tc_context_request *r, tc_context_plan *plan) 
     return TC_OK;
 }
 
+int tc_context_plan_compute_sharded(const tc_context_request *r, uint32_t headParts, uint32_t ctxParts,
+                                    tc_context_shard_plan *out) {
+    if (!r || !out || headParts == 0 || ctxParts == 0) return TC_EINVAL;
+    std::memset(out, 0, sizeof(*out));
+    out->headParts = headParts;
+    out->ctxParts = ctxParts;
+    // one GPU's view: its share of the kv heads, and -- for an explicit request -- its share of the rows
+    tc_context_request g = *r;
+    g.numKVHeads = (r->numKVHeads + headParts - 1) / headParts;
+    out->kvHeadsPerGpu = g.numKVHeads;
+    auto share = [&](uint32_t rows) -> uint32_t {
+        const uint64_t per = (static_cast<uint64_t>(rows) + ctxParts - 1) / ctxParts;
+        return static_cast<uint32_t>((per + 255ull) / 256ull * 256ull);
+    };
+    const bool split = ctxParts > 1 && r->requested != 0;   // an auto window (2048 rows) is not worth a context split
+    if (split) {
+        g.requested = share(r->requested);
+        if (r->modelMax) g.modelMax = share(r->modelMax);
+    }
+    const int rc = tc_context_plan_compute(&g, &out->plan);
+    if (rc != TC_OK) return rc;
+    tc_context_plan &p = out->plan;
+    const uint64_t ceiling = r->modelMax ? r->modelMax : 4096u;
+    if (split) {
+        // back to whole-window rows; a GPU's rows stay what the ladder granted it
+        out->rowsPerGpu = p.seqLen;
+        uint64_t whole = static_cast<uint64_t>(p.seqLen) * ctxParts;
+        const uint64_t want = r->requested < ceiling ? r->requested : ceiling;
+        if (whole > want) whole = want;
+        p.seqLen = static_cast<uint32_t>(whole);
+        uint64_t mx = static_cast<uint64_t>(p.maxAllowed) * ctxParts;
+        p.maxAllowed = static_cast<uint32_t>(mx < ceiling ? mx : ceiling);
+    } else {
+        out->rowsPerGpu = (p.seqLen + 255u) / 256u * 256u;
+        if (ctxParts > 1) {
+            uint64_t mx = static_cast<uint64_t>(p.maxAllowed) * ctxParts;
+            p.maxAllowed = static_cast<uint32_t>(mx < ceiling ? mx : ceiling);
+        }
+    }
+    return TC_OK;
+}
+
+uint64_t tc_context_overhead_bytes(uint32_t nHeads, uint32_t nKV, uint32_t hd, uint32_t window, uint32_t headParts,
+                                   uint32_t ctxParts, int kvStoreI8, uint32_t prefillChunk, uint64_t runtimeReserve) {
+    if (headParts == 0 || ctxParts == 0 || nKV == 0) return runtimeReserve;
+    const uint64_t kvLocal = (nKV + headParts - 1) / headParts;
+    const uint64_t qLocal = kvLocal * (nHeads / nKV);
+    const uint64_t rows = ((static_cast<uint64_t>(window) + ctxParts - 1) / ctxParts + 255ull) / 256ull * 256ull;
+    uint64_t total = runtimeReserve;
+    total += qLocal * 512ull * (hd + 2ull) * 4ull;                       // split-KV partials: acc, m, l at 512 chunk slots
+    if (ctxParts > 1) {
+        size_t ex = 0;
+        if (tc_attn_exchange_bytes(static_cast<uint32_t>(qLocal), hd, ctxParts, &ex) == TC_OK) total += ex;
+        total += qLocal * 64ull * (hd + 2ull) * 4ull;                    // the context split's own 64-slot partial block
+    }
+    if (!kvStoreI8 && prefillChunk != 0 && hd == 128) {
+        size_t tw = 0;                                                   // fp16 twins: q of a chunk, K/V of the GPU's rows
+        const uint32_t chunk = prefillChunk < rows ? prefillChunk : static_cast<uint32_t>(rows);
+        if (tc_attn_prefill_f16_scratch_bytes(chunk, static_cast<uint32_t>(rows) - chunk, static_cast<uint32_t>(qLocal),
+                                              static_cast<uint32_t>(kvLocal), hd, &tw) == TC_OK)
+            total += tw;
+    }
+    return total;
+}
+
 uint64_t tc_probe_free_vram_bytes(void) {
     size_t f = 0, t = 0;
     if (cudaMemGetInfo(&f, &t) != cudaSuccess) {

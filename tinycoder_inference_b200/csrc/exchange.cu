@@ -7,8 +7,9 @@
 //   1. merge the rank's own chunks into ONE partial (M, L, A[hd]) -- the rule of merge.cu,
 //      left unnormalised;
 //   2. store that partial into the exchange buffer of every rank (peer stores over NVLink,
-//      about 1 KB per head and peer).  Every 16-byte store carries two floats and two copies
-//      of the step number, so the data is its own arrival flag: no fence and no separate
+//      about 1 KB per head and peer).  Every 16-byte store carries two 64-bit words, each a
+//      float with the step number in its upper half, so the data is its own arrival flag
+//      (a 64-bit word is written and read as one piece): no fence and no separate
 //      flag store sit between a rank's arithmetic and its peers (system-scope fences and
 //      release/acquire pairs cost several microseconds each here, more than the merge);
 //   3. poll (bounded) this rank's own buffer until every 16-byte unit of every source rank
@@ -62,17 +63,21 @@ struct ExParams {
     unsigned int *err;
 };
 
+// A unit is two 64-bit words, each {value (low half), step (high half)}.  Loads and stores move a
+// unit as a vector of two 64-bit ELEMENTS: the memory model treats a vector access as separate
+// accesses of its elements, and an aligned 64-bit scalar element is single-copy atomic -- a value
+// can therefore never be seen with another step's tag, which a vector of four 32-bit elements
+// (the same bytes) would not promise.
 __device__ __forceinline__ uint4 ldVolatileV4(const void *p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p)
-                 : "memory");
-    return v;
+    unsigned long long a, b;
+    asm volatile("ld.volatile.global.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    return make_uint4(static_cast<uint32_t>(a), static_cast<uint32_t>(a >> 32), static_cast<uint32_t>(b),
+                      static_cast<uint32_t>(b >> 32));
 }
 __device__ __forceinline__ void stVolatileV4(void *p, uint4 v) {
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                 : "memory");
+    const unsigned long long a = (static_cast<unsigned long long>(v.y) << 32) | v.x;
+    const unsigned long long b = (static_cast<unsigned long long>(v.w) << 32) | v.z;
+    asm volatile("st.volatile.global.v2.u64 [%0], {%1,%2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
 
 template <int NV4>

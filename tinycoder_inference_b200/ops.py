@@ -277,6 +277,21 @@ def plan_context(req: capi.ContextRequest) -> dict:
     return p.as_dict()
 
 
+def plan_context_sharded(req: capi.ContextRequest, head_parts: int, ctx_parts: int) -> dict:
+    """The plan every GPU of a head_parts x ctx_parts partition can honour (req describes one GPU)."""
+    p = capi.ContextShardPlan()
+    check(lib.tc_context_plan_compute_sharded(C.byref(req), head_parts, ctx_parts, C.byref(p)))
+    d = p.plan.as_dict()
+    d.update(headParts=p.headParts, ctxParts=p.ctxParts, kvHeadsPerGpu=p.kvHeadsPerGpu, rowsPerGpu=p.rowsPerGpu)
+    return d
+
+
+def context_overhead_bytes(nHeads, nKV, hd, window, head_parts=1, ctx_parts=1, kv_store_i8=True, prefill_chunk=512,
+                           runtime_reserve=512 << 20) -> int:
+    return int(lib.tc_context_overhead_bytes(nHeads, nKV, hd, window, head_parts, ctx_parts, int(kv_store_i8),
+                                             prefill_chunk, runtime_reserve))
+
+
 def kv_bytes_per_token(req, kv, mirror) -> int:
     return int(lib.tc_kv_bytes_per_token(C.byref(req), int(kv), int(mirror)))
 
