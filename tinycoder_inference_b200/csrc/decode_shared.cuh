@@ -65,6 +65,9 @@ inline DecodePlan planDecode(uint32_t batch, uint32_t nKV, uint32_t maxLen, uint
     const uint32_t waves = (batch > 1 && !uniformLengths) ? 4u * (4u / pl.hpc) : 1u;
     uint32_t want = (sms * waves) / (batch * pl.headGroups);
     want = want < 1u ? 1u : want;
+    // ragged batches: never cut a sequence finer than about 24 stages per block -- with few sequences per
+    // GPU the wave rule alone leaves blocks of a few tiles whose set-up costs more than their work
+    if (waves > 1u && want > (tilesMax + 23u) / 24u) want = (tilesMax + 23u) / 24u;
     want = want > slots ? slots : want;
     want = want > tilesMax ? tilesMax : want;
     want = want < 1u ? 1u : want;
