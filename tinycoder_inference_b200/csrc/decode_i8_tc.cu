@@ -19,14 +19,19 @@
 //     unsigned base-256 digit planes -- into the B operand tile in shared memory.
 //   * O^T[128 dims x 32] = V^T[128 x 128 tokens] . Pd (A = the V tile as stored, MN-major;
 //     B unsigned digits): int32 per tile in TMEM, folded into f32 registers (thread = dim)
-//     with the tile's scale.  Integer accumulation never spans more than one 128-token tile.
+//     with the tile's scale and reference point.  Integer accumulation never spans more than
+//     one 128-token tile.
 // Every product is exact; the only roundings are the 21-bit q digits, the 2^-24 fixed-point
 // step of p * sv, and the f32 folds -- below the f32 arithmetic noise of the reference.
 //
-// CTA = one kv head x one token range (grid: chunks, kv heads, sequences), 10 warps:
-// warps 0-3 / 4-7 two softmax warpgroups taking alternate tiles, warp 8 TMA producer
-// (six-stage ring of K, V and their scales), warp 9 issues the MMAs.  Partials leave in the
-// reference's layout for the merge kernel (merge.cu).
+// CTA = one kv head x one token range (grid: chunks, kv heads, sequences), 17 warps:
+// warps 0-3 / 4-7 two softmax warpgroups taking alternate tiles (scores -> probabilities only),
+// warps 8-11 the fold warpgroup (thread = head dimension: every tile's integer P.V out of TMEM into
+// one f32 accumulator per head, so a softmax warpgroup's next tile does not wait for the previous
+// one's fold), warp 12 TMA producer (six-stage ring of K, V and their scales), warps 13-16 issue the
+// MMAs (score / P.V products of even / odd tiles: a tcgen05.mma costs its issuing thread about a
+// hundred cycles whatever its shape, threads of different warps issue concurrently).  Partials
+// leave in the reference's layout for the merge kernel (merge.cu).
 #include <cstdlib>
 
 #include "tc_tcgen05.cuh"
@@ -78,16 +83,17 @@ constexpr float kTcLazyLog2 = 8.0f;
 // four MMA issuers.
 template <int NWG, int NS>
 struct DecodeTcSmem {
-    static constexpr int kThreads = (4 * NWG + 5) * 32;
+    static constexpr int kThreads = (4 * NWG + 4 + 5) * 32;   // softmax warpgroups, the fold warpgroup, producer, 4 MMA issuers
     static constexpr int kTileBytes = kTcTile * 128;              // K (or V) tile: 128 rows x 128 B
     static constexpr int kStageBytes = 2 * kTileBytes + 1024;     // + 128 K scales + 128 V scales
     static constexpr int kQd = NS * kStageBytes;                  // 32 rows x 128 B digit planes of q
     static constexpr int kP = kQd + 4096;                         // 2 NWG probability tiles of 128 x 32 B
     static constexpr int kRed = kP + 2 * NWG * 4096;              // [NWG warpgroups][4 warps][12] floats
     static constexpr int kHs = kRed + NWG * 4 * 12 * 4;           // head scales [8]
-    static constexpr int kBars = kHs + 64;
-    // full[NS], empty[NS], sFull[2 NWG], pFull[2 NWG], oFull[2 NWG], qFull
-    static constexpr int kNumBars = 2 * NS + 6 * NWG + 1;
+    static constexpr int kMeta = kHs + 64;                        // per (warpgroup, buffer): reference points [8], tile scale
+    static constexpr int kBars = kMeta + 2 * NWG * 12 * 4;
+    // full[NS], empty[NS], sFull[2 NWG], pFull[2 NWG], oFull[2 NWG], oFree[2 NWG], qFull
+    static constexpr int kNumBars = 2 * NS + 8 * NWG + 1;
     static constexpr int kTmemCols = 128 * NWG;                   // S and O buffers of 32 columns each
     static constexpr int kTmemSlot = kBars + kNumBars * 8;
     static constexpr int kTotal = kTmemSlot + 16 + 1024;
@@ -152,13 +158,14 @@ __device__ __forceinline__ bool barOr(uint32_t id, uint32_t threads, bool pred) 
 __device__ __forceinline__ float i2f(uint32_t x) { return __int2float_rn(static_cast<int>(x)); }
 
 template <int NWG, int NS>
-__global__ void __launch_bounds__((4 * NWG + 5) * 32, 1)
+__global__ void __launch_bounds__((4 * NWG + 9) * 32, 1)
 decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                  const __grid_constant__ CUtensorMap tmKn, const __grid_constant__ CUtensorMap tmVn,
                  const DecodeTcParams p) {
     using L = DecodeTcSmem<NWG, NS>;
-    constexpr uint32_t kWG = NWG, kSoftThreads = 128u * NWG, kAllBar = NWG + 1u;
-    constexpr uint32_t kProducerWarp = 4u * NWG, kMmaWarp0 = 4u * NWG + 1u;
+    constexpr uint32_t kWG = NWG, kSoftThreads = 128u * NWG, kAllBar = NWG + 1u, kEndBar = NWG + 2u;
+    constexpr uint32_t kFoldWarp0 = 4u * NWG, kProducerWarp = 4u * NWG + 4u, kMmaWarp0 = 4u * NWG + 5u;
+    constexpr uint32_t kEndThreads = 32u * kProducerWarp;   // softmax + fold threads
     constexpr uint32_t T = kTcTile;
     const uint32_t chunk = blockIdx.x, kvHead = blockIdx.y, b = blockIdx.z;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -167,7 +174,7 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::kBars);
     uint64_t *fullBar = bars, *emptyBar = bars + NS, *sFull = bars + 2 * NS, *pFull = sFull + 2 * NWG,
-             *oFull = pFull + 2 * NWG, *qFull = oFull + 2 * NWG;
+             *oFull = pFull + 2 * NWG, *oFree = oFull + 2 * NWG, *qFull = oFree + 2 * NWG;
     uint32_t *tmemSlot = reinterpret_cast<uint32_t *>(smem + L::kTmemSlot);
     float *sHs = reinterpret_cast<float *>(smem + L::kHs);
 
@@ -181,6 +188,7 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             mbarInit(&sFull[i], 1);
             mbarInit(&pFull[i], 128);
             mbarInit(&oFull[i], 1);
+            mbarInit(&oFree[i], 128);
         }
         mbarInit(qFull, 256);
         fenceBarrierInit();
@@ -304,9 +312,11 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             bool ok = true;
             for (uint32_t j = par; ok && j < nTiles; j += 2u) {
                 const uint32_t s = j % NS, w = j % kWG, bb = (j / kWG) & 1u;
-                // P of tile j published: the O buffer's previous contents (tile j - 2 NWG) were folded
-                // before these threads started on tile j
+                // P of tile j published
                 ok = mbarWaitClock(&pFull[2u * w + bb], (j / (2u * kWG)) & 1u, p.err, kDevErrMmaWait);
+                // and the fold warpgroup has read the O buffer's previous contents (tile j - 2 NWG)
+                if (ok && j >= 2u * kWG)
+                    ok = mbarWaitClock(&oFree[2u * w + bb], ((j - 2u * kWG) / (2u * kWG)) & 1u, p.err, kDevErrMmaWait);
                 if (!ok) break;
                 tcFenceAfter();
                 const uint64_t dV = tcDesc(smemAddr(smem + s * L::kStageBytes + L::kTileBytes), 16, 1024, 2);
@@ -322,14 +332,65 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 if (lane == 0) TC_STAMP(16);
             }
         }
+    } else if (warp >= kFoldWarp0) {
+        // ------------------------------ fold warpgroup ------------------------------
+        // thread = one head dimension: takes every tile's integer P.V out of TMEM in tile order and
+        // folds it into ONE f32 accumulator per head, against a running reference point of its own
+        // (the two softmax warpgroups keep separate ones; a tile arrives with the reference it was
+        // exponentiated against and with its fixed-point scale)
+        const uint32_t wq = warp & 3u;
+        const uint32_t row = wq * 32u + lane;
+        const uint32_t laneBase = (wq * 32u) << 16;
+        const float *meta = reinterpret_cast<const float *>(smem + L::kMeta);
+        float o[8], M[8];
+#pragma unroll
+        for (int h = 0; h < 8; ++h) o[h] = 0.0f, M[h] = kNegBig;
+        bool ok = true;
+        for (uint32_t j = 0; ok && j < nTiles; ++j) {
+            const uint32_t w = j % kWG, bb = (j / kWG) & 1u, par = (j / (2u * kWG)) & 1u;
+            ok = mbarWaitClock(&oFull[2u * w + bb], par, p.err, kDevErrMmaWait);
+            if (!ok) break;
+            tcFenceAfter();
+            uint32_t r[32];
+            tmemLd32(tmemBase + 64u * kWG + 32u * (2u * w + bb) + laneBase, r);
+            const float *mt = meta + (2u * w + bb) * 12u;
+            float tmr[8];
+#pragma unroll
+            for (int h = 0; h < 8; ++h) tmr[h] = mt[h];
+            const float esc = mt[8];
+            tmemLdWait();
+            tcFenceBefore();
+            mbarArrive(&oFree[2u * w + bb]);   // the buffer and its meta slot may be reused
+#pragma unroll
+            for (int h = 0; h < 8; ++h) {
+                // column 4h + i carries byte i of the fixed-point probability: weight 256^i
+                const float c = fmaf(fmaf(fmaf(i2f(r[4 * h + 3]), 256.0f, i2f(r[4 * h + 2])), 256.0f, i2f(r[4 * h + 1])),
+                                     256.0f, i2f(r[4 * h]));
+                const float mn = fmaxf(M[h], tmr[h]);
+                o[h] = fmaf(c, esc * fastExp2(tmr[h] - mn), o[h] * fastExp2(M[h] - mn));
+                M[h] = mn;
+            }
+            if (threadIdx.x == kFoldWarp0 * 32u && j + 1u == nTiles) TC_STAMP(10);
+        }
+        // every P tile has been consumed (its O was waited for above): their space is the scratch
+        float *scr = reinterpret_cast<float *>(smem + L::kP);
+        namedBarSync(kEndBar, kEndThreads);
+#pragma unroll
+        for (int h = 0; h < 8; ++h) scr[h * 128u + row] = o[h];
+        if (threadIdx.x == kFoldWarp0 * 32u) {
+#pragma unroll
+            for (int h = 0; h < 8; ++h) scr[8 * 128 + h] = M[h];
+        }
+        namedBarSync(kEndBar, kEndThreads);
     } else {
         // ---------------------------- softmax warpgroups ----------------------------
         const uint32_t w = warp >> 2;                       // warpgroup: tiles j = w, w + NWG, ...
         const uint32_t wq = warp & 3u;                      // TMEM lane quarter of this warp
-        const uint32_t row = wq * 32u + lane;               // token of the tile (S phase) / dim (O phase)
+        const uint32_t row = wq * 32u + lane;               // token of the tile
         const uint32_t laneBase = (wq * 32u) << 16;
         const uint32_t wgBar = 1u + w;                      // named barrier of the warpgroup
         float *red = reinterpret_cast<float *>(smem + L::kRed) + w * 48u;
+        float *meta = reinterpret_cast<float *>(smem + L::kMeta);
 
         // pull q towards L2 while waiting (harmless if the kernel in front is still writing it)
         if (lane == 0 && warp < 8u && p.colBase + warp < p.group)
@@ -388,44 +449,21 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 #pragma unroll
         for (int h = 0; h < 8; ++h) hs[h] = sHs[h];
 
-        float mref[8], l[8], o[8], pend[8];
+        float mref[8], l[8];
 #pragma unroll
-        for (int h = 0; h < 8; ++h) mref[h] = kNegBig, l[h] = 0.0f, o[h] = 0.0f, pend[h] = 0.0f;
+        for (int h = 0; h < 8; ++h) mref[h] = kNegBig, l[h] = 0.0f;
         float Eref = 0.0f, invW = 0.0f;  // power of two above every V scale seen; 2^24 / Eref
         bool ok = true;
 
-        // O phase of tile j (dim = row): fold the tile's integer P.V into the f32 accumulators
-        auto foldO = [&](uint32_t j) -> bool {
-            const uint32_t bb = (j / kWG) & 1u;
-            if (!mbarWaitClock(&oFull[2u * w + bb], (j / (2u * kWG)) & 1u, p.err, kDevErrMmaWait)) return false;
-            if (threadIdx.x == 0 && j == 2) TC_STAMP(9);
-            tcFenceAfter();
-            uint32_t r[32];
-            tmemLd32(tmemBase + 64u * kWG + 32u * (2u * w + bb) + laneBase, r);
-            tmemLdWait();
-#pragma unroll
-            for (int h = 0; h < 8; ++h) {
-                // column 4h + i carries byte i of the fixed-point probability: weight 256^i
-                const float c = fmaf(fmaf(fmaf(i2f(r[4 * h + 3]), 256.0f, i2f(r[4 * h + 2])), 256.0f, i2f(r[4 * h + 1])),
-                                     256.0f, i2f(r[4 * h]));
-                o[h] = fmaf(c, pend[h], o[h]);
-            }
-            if (threadIdx.x == 0 && j == 2) TC_STAMP(19);
-            return true;
-        };
-
         for (uint32_t j = w; j < nTiles; j += kWG) {
             const uint32_t s = j % NS, bb = (j / kWG) & 1u;
-            // ---- S phase: this thread's token against the 8 heads ----
-            if (threadIdx.x == 0 && j == 4) TC_STAMP(27);
+            // ---- this thread's token against the 8 heads ----
             if (!mbarWaitClock(&sFull[2u * w + bb], (j / (2u * kWG)) & 1u, p.err, kDevErrMmaWait)) {
                 ok = false;
                 break;
             }
             tcFenceAfter();
             if (threadIdx.x == 0 && j == 0) TC_STAMP(4);
-            if (threadIdx.x == 0 && j == 4) TC_STAMP(28);
-            if (threadIdx.x == 128 && j == 1) TC_STAMP(17);
             uint32_t ra[16], rb[8];
             const uint32_t tS = tmemBase + 32u * (2u * w + bb) + laneBase;
             tmemLd16(tS, ra);
@@ -435,7 +473,6 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             const float skr = sK[row];
             const float svr = valid ? sK[T + row] : 0.0f;
             tmemLdWait();
-            if (threadIdx.x == 0 && j == 4) TC_STAMP(29);
             float sc[8];
             bool need = svr >= Eref;
 #pragma unroll
@@ -466,20 +503,16 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 #pragma unroll
                 for (int h = 0; h < 8; ++h) {
                     const float mn = fmaxf(mref[h], tm[h]);
-                    const float f = fastExp2(mref[h] - mn);
-                    o[h] *= f;
-                    l[h] *= f;
-                    pend[h] *= f;   // the tile still in the tensor pipe was exponentiated against the old point
+                    l[h] *= fastExp2(mref[h] - mn);
                     mref[h] = mn;
                 }
                 if (tm[8] >= Eref) {
                     uint32_t eb = (__float_as_uint(tm[8]) & 0x7f800000u) + 0x00800000u;  // 2^(floor(log2) + 1)
-                    eb = min(max(eb, 1u << 23), 253u << 23);
+                    eb = min(max(eb, 24u << 23), 253u << 23);
                     Eref = __uint_as_float(eb);
                     invW = __uint_as_float((127u + 24u + 127u) * (1u << 23) - eb);  // 2^24 / Eref
                 }
             }
-            if (threadIdx.x == 0 && j == 4) TC_STAMP(30);
             // p, l, and p * sv as 32-bit fixed point (8.24 against Eref): its bytes are the digit planes
             const float wv = svr * invW;
             uint32_t X[8];
@@ -489,42 +522,43 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 l[h] += pr;
                 X[h] = __float2uint_rn(pr * wv);
             }
+            // The P tile and the meta slot of this buffer were last used by tile j - 2 NWG: that tile's
+            // P.V product is complete and folded once the fold warpgroup has said so on oFree (long
+            // ago, as a rule: two tiles of this warpgroup lie in between).
+            if (j >= 2u * kWG &&
+                !mbarWaitClock(&oFree[2u * w + bb], ((j - 2u * kWG) / (2u * kWG)) & 1u, p.err, kDevErrMmaWait)) {
+                ok = false;
+                break;
+            }
             uint8_t *pt = smem + L::kP + (2u * w + bb) * 4096u + row * 32u;
             const uint32_t sw = (row >> 2) & 1u;  // 32-byte swizzle: 16-byte halves swap on rows 4..7 of every 8
             *reinterpret_cast<uint4 *>(pt + ((0u ^ sw) << 4)) = make_uint4(X[0], X[1], X[2], X[3]);
             *reinterpret_cast<uint4 *>(pt + ((1u ^ sw) << 4)) = make_uint4(X[4], X[5], X[6], X[7]);
+            if (row == 0) {
+                // what the fold warpgroup needs with this tile: the reference points its probabilities
+                // were taken against and the scale of their fixed-point form
+                float *mt = meta + (2u * w + bb) * 12u;
+#pragma unroll
+                for (int h = 0; h < 8; ++h) mt[h] = mref[h];
+                mt[8] = Eref * 5.9604644775390625e-8f;  // Eref * 2^-24
+            }
             fenceProxyAsync();
             tcFenceBefore();
             mbarArrive(&pFull[2u * w + bb]);
             if (threadIdx.x == 0 && j / kWG < 4u) TC_STAMP(5 + j / kWG);
-            if (threadIdx.x == 0 && j == 4) TC_STAMP(31);
-            // ---- O phase of this warpgroup's previous tile, then this tile's scale becomes pending ----
-            if (j >= kWG && !foldO(j - kWG)) {
-                ok = false;
-                break;
-            }
-            const float pn = Eref * 5.9604644775390625e-8f;  // Eref * 2^-24
-#pragma unroll
-            for (int h = 0; h < 8; ++h) pend[h] = pn;
         }
-        const uint32_t myTiles = nTiles > w ? (nTiles - w + kWG - 1u) / kWG : 0u;
-        if (ok && myTiles > 0) ok = foldO(w + kWG * (myTiles - 1u));
-        if (threadIdx.x == 0) TC_STAMP(10);
-        if (threadIdx.x == 128) TC_STAMP(18);
 
-        // ---- fold the two warpgroups, write the chunk partial (or the output itself) ----
-        // every P tile has been consumed (its O was waited for above): their space is the scratch
+        // ---- row sums of this warpgroup, then the end of the block ----
 #pragma unroll
         for (int h = 0; h < 8; ++h)
 #pragma unroll
             for (int off = 16; off; off >>= 1) l[h] += __shfl_xor_sync(0xffffffffu, l[h], off);
         float *scr = reinterpret_cast<float *>(smem + L::kP);
-        float *oS = scr;                          // [NWG][8][128]
-        float *mS = scr + NWG * 8 * 128;          // [NWG][8]
+        float *oS = scr;                          // [8][128] from the fold warpgroup, then its reference points [8]
+        float *mF = scr + 8 * 128;
+        float *mS = mF + 8;                       // [NWG][8]
         float *lS = mS + NWG * 8;                 // [4 NWG warps][8]
-        namedBarSync(kAllBar, kSoftThreads);
-#pragma unroll
-        for (int h = 0; h < 8; ++h) oS[(w * 8u + h) * 128u + row] = o[h];
+        namedBarSync(kEndBar, kEndThreads);       // the fold warpgroup is through: every P tile has been consumed
         if (lane == 0) {
 #pragma unroll
             for (int h = 0; h < 8; ++h) {
@@ -532,25 +566,20 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 if (wq == 0) mS[w * 8u + h] = mref[h];
             }
         }
-        namedBarSync(kAllBar, kSoftThreads);
+        namedBarSync(kEndBar, kEndThreads);
         if (threadIdx.x == 0) TC_STAMP(11);
         if (warp < 8u) {
             const uint32_t tid = threadIdx.x;  // 0..255: head tid / 32, dims 4 (tid % 32) ..
             const uint32_t h = tid >> 5, d4 = tid & 31u;
             if (p.colBase + h < p.group) {
-                float M = mS[h];
-#pragma unroll
-                for (int g = 1; g < NWG; ++g) M = fmaxf(M, mS[g * 8 + h]);
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                // the accumulator is relative to the fold warpgroup's reference point, which is the
+                // largest of the warpgroups' (a reference only ever grows)
+                const float M = mF[h];
+                const float4 acc = *reinterpret_cast<const float4 *>(oS + h * 128u + 4u * d4);
                 float lsum = 0.0f;
 #pragma unroll
                 for (int g = 0; g < NWG; ++g) {
                     const float a = fastExp2(mS[g * 8 + h] - M);   // a warpgroup without tiles: exp2(-1e30) = 0
-                    const float4 x = *reinterpret_cast<const float4 *>(oS + (g * 8u + h) * 128u + 4u * d4);
-                    acc.x = fmaf(a, x.x, acc.x);
-                    acc.y = fmaf(a, x.y, acc.y);
-                    acc.z = fmaf(a, x.z, acc.z);
-                    acc.w = fmaf(a, x.w, acc.w);
                     const float lg = (lS[(4 * g) * 8 + h] + lS[(4 * g + 1) * 8 + h]) +
                                      (lS[(4 * g + 2) * 8 + h] + lS[(4 * g + 3) * 8 + h]);
                     lsum = fmaf(a, lg, lsum);

@@ -82,7 +82,22 @@ struct PrefillF16Params {
     uint32_t nQTiles;   // 256-row query blocks
     float scaleLog2;   // invSqrt * log2(e)
     unsigned int *err;
+#ifdef TC_TRACE
+    unsigned long long *trace;  // [8 roles][64 steps][4 stamps] of block 0
+#endif
 };
+
+#ifdef TC_TRACE
+unsigned long long *g_pfTrace = nullptr;
+__device__ __forceinline__ unsigned long long pfTime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define PF_STAMP(role, step, k) do { if (p.trace && blockIdx.x == 0 && (step) < 64u) p.trace[((role) * 64u + (step)) * 4u + (k)] = pfTime(); } while (0)
+#else
+#define PF_STAMP(role, step, k) do { } while (0)
+#endif
 
 struct PrefillF16Smem {
     static constexpr int kQTile = kPfBM * kPfHD * 2;   // 32 KB: 128 x 128 fp16 as two 64-column halves
@@ -261,7 +276,9 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             okFull = okFull && pfWait(&stFull[s], (j / NS) & 1u, p.err, kDevErrFullWait);
             if (ok && okFull) {
                 if (pvRole && j < myTiles) {
+                    if (lane == 0) PF_STAMP(4u + x, j, 0);
                     ok = pfWait(&pFull[2u * x + (j & 1u)], (j >> 1) & 1u, p.err, kDevErrMmaWait);
+                    if (lane == 0) PF_STAMP(4u + x, j, 1);
                     if (ok) {
                         tcFenceAfter();
                         const uint64_t dV = descAdvance(dVs, s * L::kStageBytes);
@@ -271,13 +288,17 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                             umaMmaTSIf(issue, tO, tP + ks * 8u, descAdvance(dV, ks * 2048u), idPV, (j > 0 || ks > 0) ? 1u : 0u);
                         umaCommitIf(issue, &pvDone[x]);
                         umaCommitIf(issue, &pvBuf[2u * x + (j & 1u)]);
+                        if (lane == 0) PF_STAMP(4u + x, j, 2);
                     }
                 } else if (!pvRole && j + 2 < myTiles) {
                     // the buffer S_X(j+2) goes into is the one P_X(j) sits in until its P.V product is done
+                    if (lane == 0) PF_STAMP(2u + x, j, 0);
                     ok = pfWait(&pvBuf[2u * x + (j & 1u)], (j >> 1) & 1u, p.err, kDevErrMmaWait);
+                    if (lane == 0) PF_STAMP(2u + x, j, 1);
                     if (ok) {
                         tcFenceAfter();
                         issueQK(descAdvance(dKs, s * L::kStageBytes), j + 2);
+                        if (lane == 0) PF_STAMP(2u + x, j, 2);
                     }
                 }
             }
@@ -297,15 +318,18 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (uint32_t j = 0; j < myTiles; ++j) {
             const uint32_t b = j & 1u;
             const uint32_t tS = tmemBase + 256u + 128u * x + 64u * b;
+            if (row == 0) PF_STAMP(x, j, 0);
             if (!pfWait(&sFull[2u * x + b], (j >> 1) & 1u, p.err, kDevErrMmaWait)) {
                 ok = false;
                 break;
             }
+            if (row == 0) PF_STAMP(x, j, 1);
             tcFenceAfter();
             uint32_t r[2][32];  // the 64 scores of this row
             tmemLd32(tS + laneBase, r[0]);
             tmemLd32(tS + laneBase + 32u, r[1]);
             tmemLdWait();
+            if (row == 0 && x == 0) PF_STAMP(6u, j, 0);
             if (64u * j + 63u > p.cachePos + m0 + x * kPfBM) {
                 // causal edge (the tile reaches past the position of this tile's first row): token
                 // 64 j + c is visible iff it is not past the query position; relative to the block's
@@ -329,6 +353,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float mNew = mx > m + kPfLazyLog2 ? mx : m;
             const float alpha = fastExp2(m - mNew);
             const bool rescale = j > 0 && __any_sync(0xffffffffu, mNew != m);
+            if (row == 0 && x == 0) PF_STAMP(6u, j, 1);
             // O may only be touched between two of its PV products: the previous one has to be
             // complete (the next one cannot start before this thread publishes P).  The last
             // step takes the wait in any case: a parity wait can only tell the current phase from
@@ -358,26 +383,34 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // Pairs of elements with packed f32x2 arithmetic (scale-and-shift, row sum).  Evaluating
             // part of the exponentials on the FMA pipe (round-to-integer trick + cubic) was measured
             // at 25 / 50 / 75 % of the pairs: 716 / 699 / 694 TFLOP/s against 732 with all of them on
-            // the special-function unit -- that unit is not what bounds the kernel.
-            float2 sum2 = make_float2(0.0f, 0.0f);
+            // the special-function unit.  Exponentials of fp16 PAIRS (ex2.approx.f16x2 on the rounded
+            // exponent, row sum over fp16 partial sums) pass the parity tests but are slower still:
+            // 673 TFLOP/s.
             const float2 scale2 = make_float2(p.scaleLog2, p.scaleLog2), negM2 = make_float2(-m, -m);
+            float psum = 0.0f;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t h[16];
+                {
+                    float2 sum2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])),
-                                                 scale2, negM2);
-                    const float2 p2 = make_float2(fastExp2(x2.x), fastExp2(x2.y));
-                    sum2 = __fadd2_rn(sum2, p2);
-                    h[i] = packHalf2(p2.x, p2.y);
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])),
+                                                     scale2, negM2);
+                        const float2 p2 = make_float2(fastExp2(x2.x), fastExp2(x2.y));
+                        sum2 = __fadd2_rn(sum2, p2);
+                        h[i] = packHalf2(p2.x, p2.y);
+                    }
+                    psum += sum2.x + sum2.y;
                 }
                 tmemSt16(tS + laneBase + c * 16u, h);
+                if (row == 0 && x == 0) PF_STAMP(6u, j, 2 + c);
             }
-            l = l * alpha + (sum2.x + sum2.y);
+            l = l * alpha + psum;
             tmemStWait();
             tcFenceBefore();
             mbarArrive(&pFull[2u * x + b]);
+            if (row == 0) PF_STAMP(x, j, 2);
         }
         if (ok && pfWait(&pvDone[x], (myTiles - 1u) & 1u, p.err, kDevErrMmaWait)) {
             tcFenceAfter();
@@ -432,6 +465,10 @@ static size_t prefillScratchBytes(uint32_t seqLen, uint32_t cachePos, uint32_t n
 }
 
 }  // namespace tc
+
+#ifdef TC_TRACE
+extern "C" void tc_debug_trace_prefill(unsigned long long *buf) { tc::g_pfTrace = buf; }
+#endif
 
 extern "C" {
 
@@ -499,6 +536,9 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     prm.scaleLog2 = invSqrt * kLog2e;
     prm.err = devErrorWord();
     TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "tc_attn_prefill_f16: no device error word");
+#ifdef TC_TRACE
+    prm.trace = tc::g_pfTrace;
+#endif
     static bool attrDone[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
