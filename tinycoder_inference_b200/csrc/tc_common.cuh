@@ -62,6 +62,7 @@ int getTensorMap(const TensorMapKey &key, CUtensorMap *out);
 #ifdef __CUDACC__
 
 // ---- mbarrier ----------------------------------------------------------------
+constexpr uint32_t kMbarSuspendNs = 20000u;  // upper bound of one hardware-parked poll
 __device__ __forceinline__ uint32_t smemAddr(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -75,14 +76,18 @@ __device__ __forceinline__ void mbarExpectTx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbarArrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(bar)) : "memory");
 }
+// One poll of a phase.  The suspend-time hint lets the hardware park the thread until the phase
+// completes (or the hint runs out) instead of returning at once: a block here has a dozen warps
+// waiting for one another most of the time, and warps that spin through an unhinted try_wait
+// take the issue slots of the few warps that have work (measured on the int8 decode kernel).
 __device__ __forceinline__ bool mbarTryWait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.b32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(smemAddr(bar)), "r"(parity)
+            : "r"(smemAddr(bar)), "r"(parity), "r"(kMbarSuspendNs)
             : "memory");
     return ok != 0;
 }
