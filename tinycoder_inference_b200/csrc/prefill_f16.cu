@@ -94,9 +94,11 @@ __device__ __forceinline__ unsigned long long pfTime() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
+#define PF_BLK(k) do { if (p.trace) p.trace[8u * 64u * 4u + blockIdx.x * 8u + (k)] = pfTime(); } while (0)
 #define PF_STAMP(role, step, k) do { if (p.trace && blockIdx.x == 0 && (step) < 64u) p.trace[((role) * 64u + (step)) * 4u + (k)] = pfTime(); } while (0)
 #else
 #define PF_STAMP(role, step, k) do { } while (0)
+#define PF_BLK(k) do { } while (0)
 #endif
 
 struct PrefillF16Smem {
@@ -168,6 +170,10 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t nTiles = activeB ? nB : nA;
 
     if (threadIdx.x == 0) {
+        PF_BLK(0);
+#ifdef TC_TRACE
+        if (p.trace) { unsigned sm; asm("mov.u32 %0, %%smid;" : "=r"(sm)); p.trace[8u * 64u * 4u + blockIdx.x * 8u + 6] = sm; }
+#endif
         mbarInit(qFull, 1);
         mbarInit(k01Full, 1);
         for (uint32_t s = 0; s < NS; ++s) {
@@ -194,6 +200,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncthreads();
     tcFenceAfter();
     const uint32_t tmemBase = *reinterpret_cast<volatile uint32_t *>(tmemSlot);
+    if (threadIdx.x == 0) PF_BLK(1);
     // O of tile X at columns 128 X; S buffer b of tile X at 256 + 128 X + 64 b (its fp16
     // probabilities overwrite the first 32 of those columns)
 
@@ -324,6 +331,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 break;
             }
             if (row == 0) PF_STAMP(x, j, 1);
+            if (row == 0 && x == 0 && j == 0) PF_BLK(2);
             tcFenceAfter();
             uint32_t r[2][32];  // the 64 scores of this row
             tmemLd32(tS + laneBase, r[0]);
@@ -383,9 +391,13 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // Pairs of elements with packed f32x2 arithmetic (scale-and-shift, row sum).  Evaluating
             // part of the exponentials on the FMA pipe (round-to-integer trick + cubic) was measured
             // at 25 / 50 / 75 % of the pairs: 716 / 699 / 694 TFLOP/s against 732 with all of them on
-            // the special-function unit.  Exponentials of fp16 PAIRS (ex2.approx.f16x2 on the rounded
-            // exponent, row sum over fp16 partial sums) pass the parity tests but are slower still:
-            // 673 TFLOP/s.
+            // the special-function unit; a second implementation (magic-constant integer split, cubic
+            // with relative error 7.5e-5, exponent patched by an integer add, selected per pair at run
+            // time) lost a fifth from 0 to 4 of every 4 pairs.  Exponentials of fp16 PAIRS
+            // (ex2.approx.f16x2 on the rounded exponent, row sum over fp16 partial sums) pass the
+            // parity tests but are slower too: 673 TFLOP/s.  Per 64-token step a softmax thread is busy
+            // for 0.9 us, 0.8 of them in these two loops; more instructions cost time in proportion,
+            // whichever pipe they run on.
             const float2 scale2 = make_float2(p.scaleLog2, p.scaleLog2), negM2 = make_float2(-m, -m);
             float psum = 0.0f;
 #pragma unroll
@@ -411,6 +423,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tcFenceBefore();
             mbarArrive(&pFull[2u * x + b]);
             if (row == 0) PF_STAMP(x, j, 2);
+            if (row == 0 && j + 1u == myTiles) PF_BLK(3u + x);
         }
         if (ok && pfWait(&pvDone[x], (myTiles - 1u) & 1u, p.err, kDevErrMmaWait)) {
             tcFenceAfter();
@@ -433,6 +446,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     tcFenceBefore();
     __syncthreads();
+    if (threadIdx.x == 0) PF_BLK(5);
     if (warp == 0) {
         tcFenceAfter();
         tmemDealloc(tmemBase, 512);
