@@ -52,7 +52,10 @@ constexpr float kPfLazyLog2 = 8.0f;
 // concatenation of the three arrays, in units of four floats.
 __global__ void __launch_bounds__(256)
 f32ToF16x3Kernel(const float4 *__restrict__ q, const float4 *__restrict__ k, const float4 *__restrict__ v,
-                 uint2 *__restrict__ q16, uint2 *__restrict__ k16, uint2 *__restrict__ v16, size_t nq4, size_t nkv4) {
+                 uint2 *__restrict__ q16, uint2 *__restrict__ k16, uint2 *__restrict__ v16, size_t nq4, size_t nkv4,
+                 unsigned int *__restrict__ workCounter) {
+    // the attention launch that follows in the stream hands out its work items through this counter
+    if (blockIdx.x == 0 && threadIdx.x == 0) *workCounter = 0u;
     size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     const size_t total = nq4 + 2 * nkv4;
@@ -82,6 +85,9 @@ struct PrefillF16Params {
     uint32_t nQTiles;   // 256-row query blocks
     float scaleLog2;   // invSqrt * log2(e)
     unsigned int *err;
+    unsigned int *workCounter;  // zero at launch; item gridDim.x + n goes to the n-th request
+    uint32_t totalItems;        // nQTiles * nHeads (query block, head) pairs, heavy blocks first
+    uint32_t out32;             // out is 32-byte aligned: rows can be written with 32-byte stores
 #ifdef TC_TRACE
     unsigned long long *trace;  // [8 roles][64 steps][4 stamps] of block 0
 #endif
@@ -94,8 +100,8 @@ __device__ __forceinline__ unsigned long long pfTime() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-#define PF_BLK(k) do { if (p.trace) p.trace[8u * 64u * 4u + blockIdx.x * 8u + (k)] = pfTime(); } while (0)
-#define PF_STAMP(role, step, k) do { if (p.trace && blockIdx.x == 0 && (step) < 64u) p.trace[((role) * 64u + (step)) * 4u + (k)] = pfTime(); } while (0)
+#define PF_BLK(k) do { if (p.trace) p.trace[8u * 64u * 4u + item * 8u + (k)] = pfTime(); } while (0)
+#define PF_STAMP(role, step, k) do { if (p.trace && item == 0u && (step) < 64u) p.trace[((role) * 64u + (step)) * 4u + (k)] = pfTime(); } while (0)
 #else
 #define PF_STAMP(role, step, k) do { } while (0)
 #define PF_BLK(k) do { } while (0)
@@ -109,10 +115,11 @@ struct PrefillF16Smem {
     static constexpr int kStage = kK01 + 2 * kKvTile;  // stage s: K slot, then V slot
     static constexpr int kStageBytes = 2 * kKvTile;
     static constexpr int kBars = kStage + kPfStages * kStageBytes;
-    // qFull, k01Full, stage full + empty, sFull[2][2], pFull[2][2], pvDone[2], pvBuf[2][2]
-    static constexpr int kNumBars = 2 + 2 * kPfStages + 4 + 4 + 2 + 4;
+    // qFull, k01Full, stage full + empty, sFull[2][2], pFull[2][2], pvDone[2], pvBuf[2][2], qFree[2], itemFull[4]
+    static constexpr int kNumBars = 2 + 2 * kPfStages + 4 + 4 + 2 + 4 + 2 + 4;
     static constexpr int kTmemSlot = kBars + kNumBars * 8;
-    static constexpr int kTotal = kTmemSlot + 16 + 1024;
+    static constexpr int kItemSlots = kTmemSlot + 16;  // four work item indices
+    static constexpr int kTotal = kItemSlots + 16 + 1024;
 };
 
 __device__ __forceinline__ bool pfWait(uint64_t *bar, uint32_t parity, unsigned int *err, uint32_t bit) {
@@ -127,6 +134,14 @@ __device__ __forceinline__ bool pfWait(uint64_t *bar, uint32_t parity, unsigned 
     return false;
 }
 
+// one 32-byte store (the address has to be 32-byte aligned)
+__device__ __forceinline__ void stGlobalV8(float *dst, float a, float b, float c, float d, float e, float f, float g,
+                                           float h) {
+    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d),
+                 "f"(e), "f"(f), "f"(g), "f"(h)
+                 : "memory");
+}
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -138,9 +153,36 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // never carries out of the field).
 __device__ __forceinline__ uint64_t descAdvance(uint64_t d, uint32_t bytes) { return d + (bytes >> 4); }
 
+// What one work item (a 256-row query block of one head) covers.  Query tile X (0 = A, 1 = B) holds
+// rows m0 + 128 X .. at positions cachePos + row; it sees KV tiles 0 .. nX - 1 (64 tokens each; the
+// last two or three straddle its diagonal).  B may lie wholly past the sequence.
+struct PfItem {
+    uint32_t head, kvHead, m0, nA, nB, nTiles;
+};
+__device__ __forceinline__ PfItem pfItem(const PrefillF16Params &p, uint32_t item) {
+    PfItem it;
+    const uint32_t qb = p.nQTiles - 1u - item / p.nHeads;  // heavy query blocks (long causal prefixes) first
+    it.head = item % p.nHeads;
+    it.kvHead = it.head / p.group;
+    it.m0 = qb * 2u * kPfBM;
+    const bool activeB = it.m0 + kPfBM < p.seqLen;
+    it.nA = (p.cachePos + it.m0 + kPfBM + kPfBN - 1u) / kPfBN;
+    it.nB = activeB ? (p.cachePos + it.m0 + 2u * kPfBM + kPfBN - 1u) / kPfBN : 0u;
+    it.nTiles = activeB ? it.nB : it.nA;
+    return it;
+}
+
 // 416 threads: warps 0-3 softmax of query tile A, warps 4-7 softmax of query tile B
-// (rows 128 further down), warp 8 TMA producer, warps 9 and 10 issue the score products of A and
-// B, warps 11 and 12 their P.V products.
+// (rows 128 further down), warp 8 TMA producer and scheduler, warps 9 and 10 issue the score
+// products of A and B, warps 11 and 12 their P.V products.
+//
+// One block per SM works through (query block, head) items: its first is blockIdx.x, the following
+// ones come from a counter, so the heavy items start first and the light ones fill in behind them.
+// The roles walk the item list independently and meet only at the mbarriers, which are never
+// initialised again: every ring (K/V stages, score buffers, P.V commits) is indexed by a count that
+// runs on from item to item.  So the next item's query tiles load as soon as this item's last score
+// product has been issued, its first scores are in TMEM while the softmax threads still write this
+// item's output, and tile A moves on while tile B finishes its two extra diagonal tiles.
 constexpr int kPfThreads = 416;
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -152,28 +194,12 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::kBars);
     uint64_t *qFull = bars, *k01Full = bars + 1, *stFull = bars + 2, *stEmpty = stFull + NS,
              *sFull = stEmpty + NS /* [x][b] */, *pFull = sFull + 4 /* [x][b] */, *pvDone = pFull + 4 /* [x] */,
-             *pvBuf = pvDone + 2 /* [x][b] */;
+             *pvBuf = pvDone + 2 /* [x][b] */, *qFree = pvBuf + 4 /* [x] */, *itemFull = qFree + 2 /* [4] */;
     uint32_t *tmemSlot = reinterpret_cast<uint32_t *>(smem + L::kTmemSlot);
-
+    volatile uint32_t *itemSlots = reinterpret_cast<volatile uint32_t *>(smem + L::kItemSlots);  // [4]
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    // heavy query blocks (long causal prefixes) first
-    const uint32_t qb = p.nQTiles - 1u - blockIdx.x / p.nHeads;  // 256-row query block
-    const uint32_t head = blockIdx.x % p.nHeads;
-    const uint32_t kvHead = head / p.group;
-    const uint32_t m0 = qb * 2u * kPfBM;
-    // query tile X (0 = A, 1 = B) covers rows m0 + 128 X .. at positions cachePos + row; it sees KV
-    // tiles 0 .. nX - 1 (64 tokens each; the last two or three straddle its diagonal).  B may lie
-    // wholly past the sequence.
-    const bool activeB = m0 + kPfBM < p.seqLen;
-    const uint32_t nA = (p.cachePos + m0 + kPfBM + kPfBN - 1u) / kPfBN;
-    const uint32_t nB = activeB ? (p.cachePos + m0 + 2u * kPfBM + kPfBN - 1u) / kPfBN : 0u;
-    const uint32_t nTiles = activeB ? nB : nA;
 
     if (threadIdx.x == 0) {
-        PF_BLK(0);
-#ifdef TC_TRACE
-        if (p.trace) { unsigned sm; asm("mov.u32 %0, %%smid;" : "=r"(sm)); p.trace[8u * 64u * 4u + blockIdx.x * 8u + 6] = sm; }
-#endif
         mbarInit(qFull, 1);
         mbarInit(k01Full, 1);
         for (uint32_t s = 0; s < NS; ++s) {
@@ -183,10 +209,13 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 4; ++i) {
             mbarInit(&sFull[i], 1);
             mbarInit(&pFull[i], 128);
+            mbarInit(&pvBuf[i], 1);
+            mbarInit(&itemFull[i], 1);
         }
         mbarInit(&pvDone[0], 1);
         mbarInit(&pvDone[1], 1);
-        for (int i = 0; i < 4; ++i) mbarInit(&pvBuf[i], 1);
+        mbarInit(&qFree[0], 1);  // score warp X is done with the query tiles and K_0, K_1
+        mbarInit(&qFree[1], 1);
         fenceBarrierInit();
         tmaPrefetchDesc(&tmQ);
         tmaPrefetchDesc(&tmK);
@@ -200,54 +229,95 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     __syncthreads();
     tcFenceAfter();
     const uint32_t tmemBase = *reinterpret_cast<volatile uint32_t *>(tmemSlot);
-    if (threadIdx.x == 0) PF_BLK(1);
     // O of tile X at columns 128 X; S buffer b of tile X at 256 + 128 X + 64 b (its fp16
     // probabilities overwrite the first 32 of those columns)
 
+    // The n-th item of this block: the producer publishes it in slot n % 4 (the end of the list as
+    // an index past the last item); the other roles pick it up there.
+    auto takeItem = [&](uint32_t n, uint32_t &item) -> bool {
+        if (!pfWait(&itemFull[n & 3u], (n >> 2) & 1u, p.err, kDevErrFullWait)) return false;
+        item = itemSlots[n & 3u];
+        return item < p.totalItems;
+    };
+
     if (warp == 8) {
-        // ------------------------------ TMA producer ------------------------------
+        // ------------------------ TMA producer and scheduler ------------------------
         if (lane == 0) {
-            mbarExpectTx(qFull, 2 * L::kQTile);
-#pragma unroll
-            for (int x = 0; x < 2; ++x) {
-                tmaLoad3D(smem + L::kQ + x * L::kQTile, &tmQ, qFull, 0, head, m0 + x * kPfBM);
-                tmaLoad3D(smem + L::kQ + x * L::kQTile + L::kQTile / 2, &tmQ, qFull, 64, head, m0 + x * kPfBM);
-            }
-            // K_0 and K_1 feed the products issued ahead of the loop (nTiles >= 2 always)
-            mbarExpectTx(k01Full, 2 * L::kKvTile);
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                uint8_t *kd = smem + L::kK01 + j * L::kKvTile;
-                tmaLoad3D(kd, &tmK, k01Full, 0, kvHead, j * kPfBN);
-                tmaLoad3D(kd + L::kKvTile / 2, &tmK, k01Full, 64, kvHead, j * kPfBN);
-            }
-            for (uint32_t j = 0; j < nTiles; ++j) {
-                const uint32_t s = j % NS;
-                if (j >= NS && !pfWait(&stEmpty[s], ((j / NS) - 1u) & 1u, p.err, kDevErrEmptyWait)) break;
-                uint8_t *kd = smem + L::kStage + s * L::kStageBytes, *vd = kd + L::kKvTile;
-                const bool withK = j + 2 < nTiles;
-                mbarExpectTx(&stFull[s], withK ? 2 * L::kKvTile : L::kKvTile);
-                if (withK) {
-                    tmaLoad3D(kd, &tmK, &stFull[s], 0, kvHead, (j + 2) * kPfBN);
-                    tmaLoad3D(kd + L::kKvTile / 2, &tmK, &stFull[s], 64, kvHead, (j + 2) * kPfBN);
+            uint32_t item = blockIdx.x, g = 0;  // g: K/V tiles requested so far, over all items
+            itemSlots[0] = item;
+            mbarArrive(&itemFull[0]);
+            bool ok = true;
+            for (uint32_t n = 0; ok && item < p.totalItems; ++n) {
+                const PfItem it = pfItem(p, item);
+                PF_BLK(0);
+#ifdef TC_TRACE
+                if (p.trace) { unsigned sm; asm("mov.u32 %0, %%smid;" : "=r"(sm)); p.trace[8u * 64u * 4u + item * 8u + 6] = sm; }
+#endif
+                // a wait that ran out anywhere ends the launch: the flag is the caller's to read
+                constexpr unsigned int kWaitBits = kDevErrFullWait | kDevErrEmptyWait | kDevErrMmaWait;
+                const bool failed = (*reinterpret_cast<volatile unsigned int *>(p.err) & kWaitBits) != 0u;
+                const uint32_t drawn = gridDim.x + atomicAdd(p.workCounter, 1u);
+                const uint32_t next = failed ? p.totalItems : drawn;
+                // the query tiles and K_0, K_1 are free once both score warps have issued the last
+                // product of the previous item that reads them, and those products are complete
+                if (n > 0 && !(pfWait(&qFree[0], (n - 1u) & 1u, p.err, kDevErrEmptyWait) &&
+                               pfWait(&qFree[1], (n - 1u) & 1u, p.err, kDevErrEmptyWait))) {
+                    ok = false;
+                    break;
                 }
-                tmaLoad3D(vd, &tmV, &stFull[s], 0, kvHead, j * kPfBN);
-                tmaLoad3D(vd + L::kKvTile / 2, &tmV, &stFull[s], 64, kvHead, j * kPfBN);
+                mbarExpectTx(qFull, 2 * L::kQTile);
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    tmaLoad3D(smem + L::kQ + x * L::kQTile, &tmQ, qFull, 0, it.head, it.m0 + x * kPfBM);
+                    tmaLoad3D(smem + L::kQ + x * L::kQTile + L::kQTile / 2, &tmQ, qFull, 64, it.head, it.m0 + x * kPfBM);
+                }
+                // K_0 and K_1 feed the products issued ahead of the loop (nTiles >= 2 always)
+                mbarExpectTx(k01Full, 2 * L::kKvTile);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    uint8_t *kd = smem + L::kK01 + j * L::kKvTile;
+                    tmaLoad3D(kd, &tmK, k01Full, 0, it.kvHead, j * kPfBN);
+                    tmaLoad3D(kd + L::kKvTile / 2, &tmK, k01Full, 64, it.kvHead, j * kPfBN);
+                }
+                itemSlots[(n + 1u) & 3u] = next;
+                mbarArrive(&itemFull[(n + 1u) & 3u]);
+                for (uint32_t j = 0; j < it.nTiles; ++j, ++g) {
+                    const uint32_t s = g % NS;
+                    if (g >= NS && !pfWait(&stEmpty[s], ((g / NS) - 1u) & 1u, p.err, kDevErrEmptyWait)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *kd = smem + L::kStage + s * L::kStageBytes, *vd = kd + L::kKvTile;
+                    const bool withK = j + 2 < it.nTiles;
+                    mbarExpectTx(&stFull[s], withK ? 2 * L::kKvTile : L::kKvTile);
+                    if (withK) {
+                        tmaLoad3D(kd, &tmK, &stFull[s], 0, it.kvHead, (j + 2) * kPfBN);
+                        tmaLoad3D(kd + L::kKvTile / 2, &tmK, &stFull[s], 64, it.kvHead, (j + 2) * kPfBN);
+                    }
+                    tmaLoad3D(vd, &tmV, &stFull[s], 0, it.kvHead, j * kPfBN);
+                    tmaLoad3D(vd + L::kKvTile / 2, &tmV, &stFull[s], 64, it.kvHead, j * kPfBN);
+                }
+                item = next;
+            }
+            // the last release of every stage has to have arrived before the block leaves
+            for (uint32_t back = 0; ok && back < NS && back < g; ++back) {
+                const uint32_t gg = g - 1u - back;
+                ok = pfWait(&stEmpty[gg % NS], (gg / NS) & 1u, p.err, kDevErrEmptyWait);
             }
         }
     } else if (warp >= 9) {
         // ------------------------------- MMA issuers -------------------------------
         // Issuing one tcgen05.mma costs its thread about a hundred cycles whatever the shape, and
         // threads of different warps issue concurrently.  So the score products and the P.V products
-        // of a query tile have an issuing warp each: warp 9 + X issues S_X(j) = Q_X K_j^T (M128 N64
-        // K16 x8), warp 11 + X issues O_X += P_X(j) V_j (A from TMEM, B = V MN-major from shared
-        // memory, K16 x4).  S_X(j+2) goes into the buffer P_X(j) occupies: the score warp waits for
-        // the commit of that P.V product (pvBuf) before it issues.
+        // of a query tile have an issuing warp each: warp 9 + X issues S_X(t) = Q_X K^T (M128 N64
+        // K16 x8), warp 11 + X issues O_X += P_X(t) V (A from TMEM, B = V MN-major from shared
+        // memory, K16 x4).  t counts the tiles of X over all items; tile t uses score buffer t % 2,
+        // and S_X(t+2) goes into the buffer P_X(t) occupies: the score warp waits for the commit of
+        // that P.V product (pvBuf) before it issues.
         // All 32 lanes run this warp-uniform code; only lane 0 executes the tcgen05 instructions.
         const uint32_t x = (warp - 9u) & 1u;
         const bool pvRole = warp >= 11u;
         const uint32_t issue = lane == 0 ? 1u : 0u;
-        const uint32_t myTiles = x == 0 ? nA : nB;
         constexpr uint32_t idQK = umaInstrDescF16(kPfBM, kPfBN, 0, 0);
         constexpr uint32_t idPV = umaInstrDescF16(kPfBM, kPfHD, 0, 1);
         const uint64_t dQ = umaSmemDesc(smemAddr(smem + L::kQ + x * L::kQTile), 16, 1024);
@@ -255,61 +325,71 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint64_t dKs = umaSmemDesc(smemAddr(smem + L::kStage), 16, 1024);
         const uint64_t dVs = umaSmemDesc(smemAddr(smem + L::kStage + L::kKvTile), L::kKvTile / 2, 1024);
         const uint32_t tO = tmemBase + 128u * x, tS0 = tmemBase + 256u + 128u * x;
-        auto issueQK = [&](uint64_t dK, uint32_t j) {
+        // score product of running tile tt from the K tile at descriptor dK; tt >= 2 first waits
+        // until the P.V product of tile tt - 2 has left the buffer
+        auto issueQK = [&](uint64_t dK, uint32_t tt) -> bool {
+            if (tt >= 2u && !pfWait(&pvBuf[2u * x + (tt & 1u)], ((tt - 2u) >> 1) & 1u, p.err, kDevErrMmaWait)) return false;
+            tcFenceAfter();
 #pragma unroll
             for (uint32_t ks = 0; ks < 8; ++ks) {
                 // k step ks: dims 16 ks .. +15 = 32 bytes inside the (ks >> 2)-th 64-dim half
-                umaMmaSSIf(issue, tS0 + 64u * (j & 1u), descAdvance(dQ, (ks >> 2) * (L::kQTile / 2) + (ks & 3u) * 32u),
+                umaMmaSSIf(issue, tS0 + 64u * (tt & 1u), descAdvance(dQ, (ks >> 2) * (L::kQTile / 2) + (ks & 3u) * 32u),
                            descAdvance(dK, (ks >> 2) * (L::kKvTile / 2) + (ks & 3u) * 32u), idQK, ks > 0 ? 1u : 0u);
             }
-            umaCommitIf(issue, &sFull[2u * x + (j & 1u)]);
+            umaCommitIf(issue, &sFull[2u * x + (tt & 1u)]);
+            return true;
         };
-        bool ok = myTiles != 0;
-        if (!pvRole) {
-            ok = ok && pfWait(qFull, 0, p.err, kDevErrFullWait) && pfWait(k01Full, 0, p.err, kDevErrFullWait);
-            if (ok) {
-                tcFenceAfter();
-                issueQK(dK01, 0);
-                issueQK(descAdvance(dK01, L::kKvTile), 1);
-            }
-        }
-        // Every stage is released by all four warps, also the ones past a tile's diagonal -- but
-        // only after the stage has been filled: a warp with nothing to do must not run ahead and
-        // hand in the release of a later round, or the barrier would complete without the warp
-        // that still reads the stage.
-        bool okFull = true;
-        for (uint32_t j = 0; j < nTiles; ++j) {
-            const uint32_t s = j % NS;
-            okFull = okFull && pfWait(&stFull[s], (j / NS) & 1u, p.err, kDevErrFullWait);
-            if (ok && okFull) {
-                if (pvRole && j < myTiles) {
-                    if (lane == 0) PF_STAMP(4u + x, j, 0);
-                    ok = pfWait(&pFull[2u * x + (j & 1u)], (j >> 1) & 1u, p.err, kDevErrMmaWait);
-                    if (lane == 0) PF_STAMP(4u + x, j, 1);
-                    if (ok) {
-                        tcFenceAfter();
-                        const uint64_t dV = descAdvance(dVs, s * L::kStageBytes);
-                        const uint32_t tP = tS0 + 64u * (j & 1u);
-#pragma unroll
-                        for (uint32_t ks = 0; ks < 4; ++ks)  // 16 tokens per step: 8 columns of fp16 P, 2 KB of V
-                            umaMmaTSIf(issue, tO, tP + ks * 8u, descAdvance(dV, ks * 2048u), idPV, (j > 0 || ks > 0) ? 1u : 0u);
-                        umaCommitIf(issue, &pvDone[x]);
-                        umaCommitIf(issue, &pvBuf[2u * x + (j & 1u)]);
-                        if (lane == 0) PF_STAMP(4u + x, j, 2);
-                    }
-                } else if (!pvRole && j + 2 < myTiles) {
-                    // the buffer S_X(j+2) goes into is the one P_X(j) sits in until its P.V product is done
-                    if (lane == 0) PF_STAMP(2u + x, j, 0);
-                    ok = pfWait(&pvBuf[2u * x + (j & 1u)], (j >> 1) & 1u, p.err, kDevErrMmaWait);
-                    if (lane == 0) PF_STAMP(2u + x, j, 1);
-                    if (ok) {
-                        tcFenceAfter();
-                        issueQK(descAdvance(dKs, s * L::kStageBytes), j + 2);
-                        if (lane == 0) PF_STAMP(2u + x, j, 2);
-                    }
+        uint32_t g = 0, t = 0, item = 0;  // K/V tiles consumed, tiles of X done, over all items
+        bool ok = true;
+        for (uint32_t n = 0; ok && takeItem(n, item); ++n) {
+            const PfItem it = pfItem(p, item);
+            const uint32_t myTiles = x == 0 ? it.nA : it.nB;
+            if (!pvRole) {
+                if (myTiles != 0) {
+                    ok = pfWait(qFull, n & 1u, p.err, kDevErrFullWait) && pfWait(k01Full, n & 1u, p.err, kDevErrFullWait);
+                    ok = ok && issueQK(dK01, t) && issueQK(descAdvance(dK01, L::kKvTile), t + 1u);
                 }
+                if (myTiles <= 2u) umaCommitIf(issue, &qFree[x]);
             }
-            umaCommitIf(issue, &stEmpty[s]);
+            // Every stage is released by all four warps, also the ones past a tile's diagonal -- but
+            // only after the stage has been filled: a warp with nothing to do must not run ahead and
+            // hand in the release of a later round, or the barrier would complete without the warp
+            // that still reads the stage.
+            for (uint32_t j = 0; ok && j < it.nTiles; ++j, ++g) {
+                const uint32_t s = g % NS;
+                ok = pfWait(&stFull[s], (g / NS) & 1u, p.err, kDevErrFullWait);
+                if (!ok) break;
+                if (pvRole && j < myTiles) {
+                    const uint32_t tt = t + j;
+                    if (lane == 0) PF_STAMP(4u + x, j, 0);
+                    ok = pfWait(&pFull[2u * x + (tt & 1u)], (tt >> 1) & 1u, p.err, kDevErrMmaWait);
+                    if (lane == 0) PF_STAMP(4u + x, j, 1);
+                    if (!ok) break;
+                    tcFenceAfter();
+                    const uint64_t dV = descAdvance(dVs, s * L::kStageBytes);
+                    const uint32_t tP = tS0 + 64u * (tt & 1u);
+#pragma unroll
+                    for (uint32_t ks = 0; ks < 4; ++ks)  // 16 tokens per step: 8 columns of fp16 P, 2 KB of V
+                        umaMmaTSIf(issue, tO, tP + ks * 8u, descAdvance(dV, ks * 2048u), idPV, (j > 0 || ks > 0) ? 1u : 0u);
+                    umaCommitIf(issue, &pvDone[x]);
+                    umaCommitIf(issue, &pvBuf[2u * x + (tt & 1u)]);
+                    if (lane == 0) PF_STAMP(4u + x, j, 2);
+                } else if (!pvRole && j + 2 < myTiles) {
+                    if (lane == 0) PF_STAMP(2u + x, j, 0);
+                    ok = issueQK(descAdvance(dKs, s * L::kStageBytes), t + j + 2u);
+                    if (!ok) break;
+                    if (lane == 0) PF_STAMP(2u + x, j, 2);
+                    // the item's last score product: the query tiles may be replaced once it is complete
+                    if (j + 3u == myTiles) umaCommitIf(issue, &qFree[x]);
+                }
+                umaCommitIf(issue, &stEmpty[s]);
+            }
+            t += myTiles;
+        }
+        if (pvRole && ok) {
+            // nobody waits for the last two buffer commits; they have to land before the block leaves
+            for (uint32_t tt = t >= 2u ? t - 2u : 0u; tt < t; ++tt)
+                if (!pfWait(&pvBuf[2u * x + (tt & 1u)], (tt >> 1) & 1u, p.err, kDevErrMmaWait)) break;
         }
     } else {
         // --------------------------------- softmax ---------------------------------
@@ -317,115 +397,124 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t row = (warp & 3u) * 32u + lane;        // row of that tile = TMEM lane
         const uint32_t laneBase = ((warp & 3u) * 32u) << 16;  // TMEM lane field
         const uint32_t rowInBlock = x * kPfBM + row;          // row inside the 256-row block
-        const uint32_t rq = m0 + rowInBlock;                  // query position
         const uint32_t tO = tmemBase + 128u * x;
-        float m = kNegBig, l = 0.0f;
-        const uint32_t myTiles = x == 0 ? nA : nB;
-        bool ok = myTiles != 0;
-        for (uint32_t j = 0; j < myTiles; ++j) {
-            const uint32_t b = j & 1u;
-            const uint32_t tS = tmemBase + 256u + 128u * x + 64u * b;
-            if (row == 0) PF_STAMP(x, j, 0);
-            if (!pfWait(&sFull[2u * x + b], (j >> 1) & 1u, p.err, kDevErrMmaWait)) {
-                ok = false;
-                break;
-            }
-            if (row == 0) PF_STAMP(x, j, 1);
-            if (row == 0 && x == 0 && j == 0) PF_BLK(2);
-            tcFenceAfter();
-            uint32_t r[2][32];  // the 64 scores of this row
-            tmemLd32(tS + laneBase, r[0]);
-            tmemLd32(tS + laneBase + 32u, r[1]);
-            tmemLdWait();
-            if (row == 0 && x == 0) PF_STAMP(6u, j, 0);
-            if (64u * j + 63u > p.cachePos + m0 + x * kPfBM) {
-                // causal edge (the tile reaches past the position of this tile's first row): token
-                // 64 j + c is visible iff it is not past the query position; relative to the block's
-                // first row that is 64 j - (cachePos + m0) + c <= rowInBlock
-                const int32_t first = static_cast<int32_t>(64u * j) - static_cast<int32_t>(p.cachePos + m0);
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (first + c * 32 + i > static_cast<int32_t>(rowInBlock)) r[c][i] = 0xff800000u;  // -inf
-            }
-            float mxa = -INFINITY, mxb = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    mxa = max3(mxa, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
-                    mxb = max3(mxb, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
-                }
-            const float mx = fmaxf(mxa, mxb) * p.scaleLog2;  // scale > 0: max commutes with it
-            const float mNew = mx > m + kPfLazyLog2 ? mx : m;
-            const float alpha = fastExp2(m - mNew);
-            const bool rescale = j > 0 && __any_sync(0xffffffffu, mNew != m);
-            if (row == 0 && x == 0) PF_STAMP(6u, j, 1);
-            // O may only be touched between two of its PV products: the previous one has to be
-            // complete (the next one cannot start before this thread publishes P).  The last
-            // step takes the wait in any case: a parity wait can only tell the current phase from
-            // the one before it, and the final wait below must not find the barrier two behind.
-            if (j > 0 && (rescale || j + 1u == myTiles)) {
-                if (!pfWait(&pvDone[x], (j - 1u) & 1u, p.err, kDevErrMmaWait)) {
+        uint32_t t = 0, item = 0;  // tiles of X done over all items
+        bool ok = true;
+        for (uint32_t n = 0; ok && takeItem(n, item); ++n) {
+            const PfItem it = pfItem(p, item);
+            const uint32_t m0 = it.m0, head = it.head;
+            const uint32_t rq = m0 + rowInBlock;  // query position
+            const uint32_t myTiles = x == 0 ? it.nA : it.nB;
+            if (myTiles == 0) continue;
+            float m = kNegBig, l = 0.0f;
+            for (uint32_t j = 0; j < myTiles; ++j) {
+                const uint32_t tt = t + j, b = tt & 1u;
+                const uint32_t tS = tmemBase + 256u + 128u * x + 64u * b;
+                if (row == 0) PF_STAMP(x, j, 0);
+                if (!pfWait(&sFull[2u * x + b], (tt >> 1) & 1u, p.err, kDevErrMmaWait)) {
                     ok = false;
                     break;
                 }
+                if (row == 0) PF_STAMP(x, j, 1);
+                if (row == 0 && x == 0 && j == 0) PF_BLK(2);
                 tcFenceAfter();
-            }
-            if (rescale) {
-#pragma unroll 1
-                for (uint32_t c = 0; c < 4; ++c) {
-                    uint32_t o[32];
-                    tmemLd32(tO + laneBase + c * 32u, o);
-                    tmemLdWait();
+                uint32_t r[2][32];  // the 64 scores of this row
+                tmemLd32(tS + laneBase, r[0]);
+                tmemLd32(tS + laneBase + 32u, r[1]);
+                tmemLdWait();
+                if (row == 0 && x == 0) PF_STAMP(6u, j, 0);
+                if (64u * j + 63u > p.cachePos + m0 + x * kPfBM) {
+                    // causal edge (the tile reaches past the position of this tile's first row): token
+                    // 64 j + c is visible iff it is not past the query position; relative to the block's
+                    // first row that is 64 j - (cachePos + m0) + c <= rowInBlock
+                    const int32_t first = static_cast<int32_t>(64u * j) - static_cast<int32_t>(p.cachePos + m0);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmemSt32(tO + laneBase + c * 32u, o);
+                    for (int c = 0; c < 2; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (first + c * 32 + i > static_cast<int32_t>(rowInBlock)) r[c][i] = 0xff800000u;  // -inf
                 }
-                tmemStWait();
-            }
-            m = mNew;
-            // probabilities as fp16 pairs over the first 32 columns of this S buffer: the A
-            // operand of the PV product (every score of the row is already in registers)
-            // Pairs of elements with packed f32x2 arithmetic (scale-and-shift, row sum).  Evaluating
-            // part of the exponentials on the FMA pipe (round-to-integer trick + cubic) was measured
-            // at 25 / 50 / 75 % of the pairs: 716 / 699 / 694 TFLOP/s against 732 with all of them on
-            // the special-function unit; a second implementation (magic-constant integer split, cubic
-            // with relative error 7.5e-5, exponent patched by an integer add, selected per pair at run
-            // time) lost a fifth from 0 to 4 of every 4 pairs.  Exponentials of fp16 PAIRS
-            // (ex2.approx.f16x2 on the rounded exponent, row sum over fp16 partial sums) pass the
-            // parity tests but are slower too: 673 TFLOP/s.  Per 64-token step a softmax thread is busy
-            // for 0.9 us, 0.8 of them in these two loops; more instructions cost time in proportion,
-            // whichever pipe they run on.
-            const float2 scale2 = make_float2(p.scaleLog2, p.scaleLog2), negM2 = make_float2(-m, -m);
-            float psum = 0.0f;
+                float mxa = -INFINITY, mxb = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t h[16];
-                {
-                    float2 sum2 = make_float2(0.0f, 0.0f);
+                for (int c = 0; c < 2; ++c)
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])),
-                                                     scale2, negM2);
-                        const float2 p2 = make_float2(fastExp2(x2.x), fastExp2(x2.y));
-                        sum2 = __fadd2_rn(sum2, p2);
-                        h[i] = packHalf2(p2.x, p2.y);
+                    for (int i = 0; i < 32; i += 4) {
+                        mxa = max3(mxa, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+                        mxb = max3(mxb, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
                     }
-                    psum += sum2.x + sum2.y;
+                const float mx = fmaxf(mxa, mxb) * p.scaleLog2;  // scale > 0: max commutes with it
+                const float mNew = mx > m + kPfLazyLog2 ? mx : m;
+                const float alpha = fastExp2(m - mNew);
+                const bool rescale = j > 0 && __any_sync(0xffffffffu, mNew != m);
+                if (row == 0 && x == 0) PF_STAMP(6u, j, 1);
+                // O may only be touched between two of its PV products: the previous one has to be
+                // complete (the next one cannot start before this thread publishes P).  The last
+                // step takes the wait in any case: a parity wait can only tell the current phase from
+                // the one before it, and the final wait below must not find the barrier two behind.
+                // (pvDone completes one phase per tile, so its parity follows the running count.)
+                if (j > 0 && (rescale || j + 1u == myTiles)) {
+                    if (!pfWait(&pvDone[x], (tt - 1u) & 1u, p.err, kDevErrMmaWait)) {
+                        ok = false;
+                        break;
+                    }
+                    tcFenceAfter();
                 }
-                tmemSt16(tS + laneBase + c * 16u, h);
-                if (row == 0 && x == 0) PF_STAMP(6u, j, 2 + c);
+                if (rescale) {
+#pragma unroll 1
+                    for (uint32_t c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmemLd32(tO + laneBase + c * 32u, o);
+                        tmemLdWait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmemSt32(tO + laneBase + c * 32u, o);
+                    }
+                    tmemStWait();
+                }
+                m = mNew;
+                // probabilities as fp16 pairs over the first 32 columns of this S buffer: the A
+                // operand of the PV product (every score of the row is already in registers)
+                // Pairs of elements with packed f32x2 arithmetic (scale-and-shift, row sum).  Evaluating
+                // part of the exponentials on the FMA pipe (round-to-integer trick + cubic) was measured
+                // at 25 / 50 / 75 % of the pairs: 716 / 699 / 694 TFLOP/s against 732 with all of them on
+                // the special-function unit; a second implementation (magic-constant integer split, cubic
+                // with relative error 7.5e-5, exponent patched by an integer add, selected per pair at run
+                // time) lost a fifth from 0 to 4 of every 4 pairs.  Exponentials of fp16 PAIRS
+                // (ex2.approx.f16x2 on the rounded exponent, row sum over fp16 partial sums) pass the
+                // parity tests but are slower too: 673 TFLOP/s.  Per 64-token step a softmax thread is busy
+                // for 0.9 us, 0.8 of them in these two loops; more instructions cost time in proportion,
+                // whichever pipe they run on.
+                const float2 scale2 = make_float2(p.scaleLog2, p.scaleLog2), negM2 = make_float2(-m, -m);
+                float psum = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t h[16];
+                    {
+                        float2 sum2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])),
+                                                         scale2, negM2);
+                            const float2 p2 = make_float2(fastExp2(x2.x), fastExp2(x2.y));
+                            sum2 = __fadd2_rn(sum2, p2);
+                            h[i] = packHalf2(p2.x, p2.y);
+                        }
+                        psum += sum2.x + sum2.y;
+                    }
+                    tmemSt16(tS + laneBase + c * 16u, h);
+                    if (row == 0 && x == 0) PF_STAMP(6u, j, 2 + c);
+                }
+                l = l * alpha + psum;
+                tmemStWait();
+                tcFenceBefore();
+                mbarArrive(&pFull[2u * x + b]);
+                if (row == 0) PF_STAMP(x, j, 2);
+                if (row == 0 && j + 1u == myTiles) PF_BLK(3u + x);
             }
-            l = l * alpha + psum;
-            tmemStWait();
-            tcFenceBefore();
-            mbarArrive(&pFull[2u * x + b]);
-            if (row == 0) PF_STAMP(x, j, 2);
-            if (row == 0 && j + 1u == myTiles) PF_BLK(3u + x);
-        }
-        if (ok && pfWait(&pvDone[x], (myTiles - 1u) & 1u, p.err, kDevErrMmaWait)) {
+            if (!ok || !pfWait(&pvDone[x], (t + myTiles - 1u) & 1u, p.err, kDevErrMmaWait)) {
+                ok = false;
+                break;
+            }
             tcFenceAfter();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             float *orow = p.out + (static_cast<size_t>(rq) * p.nHeads + head) * kPfHD;
@@ -434,19 +523,29 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 uint32_t o[32];
                 tmemLd32(tO + laneBase + c * 32u, o);
                 tmemLdWait();
-                if (rq < p.seqLen) {
+                if (rq < p.seqLen && !p.out32) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         *reinterpret_cast<float4 *>(orow + c * 32 + 4 * i) =
                                 make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
                                             __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
+                } else if (rq < p.seqLen) {
+                    // 32 bytes per store: a thread owns its row, so a warp's store touches 32 rows, and
+                    // whole sectors halve the number of transactions against 16-byte stores
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        stGlobalV8(orow + c * 32 + 8 * i, __uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv,
+                                   __uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv,
+                                   __uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv,
+                                   __uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
                 }
             }
+            if (threadIdx.x == 0) PF_BLK(5);
+            t += myTiles;
         }
     }
     tcFenceBefore();
     __syncthreads();
-    if (threadIdx.x == 0) PF_BLK(5);
     if (warp == 0) {
         tcFenceAfter();
         tmemDealloc(tmemBase, 512);
@@ -472,10 +571,11 @@ static int f16Map(const void *base, uint32_t heads, uint32_t rows, uint32_t boxR
 }
 
 static size_t prefillScratchBytes(uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV) {
-    // fp16 twins: q [seqLen][nHeads][128], k and v [cachePos + seqLen][nKV][128]; each region 1 KB aligned
+    // fp16 twins: q [seqLen][nHeads][128], k and v [cachePos + seqLen][nKV][128]; each region 1 KB aligned;
+    // then the work counter of the attention launch
     auto al = [](size_t x) { return (x + 1023) & ~size_t(1023); };
     return al(static_cast<size_t>(seqLen) * nHeads * kPfHD * 2) +
-           2 * al((static_cast<size_t>(cachePos) + seqLen) * nKV * kPfHD * 2);
+           2 * al((static_cast<size_t>(cachePos) + seqLen) * nKV * kPfHD * 2) + 1024;  // + the work counter
 }
 
 }  // namespace tc
@@ -523,13 +623,14 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     const size_t kvElems = static_cast<size_t>(kvRows) * nKV * kPfHD;
     uint8_t *sc = static_cast<uint8_t *>(scratch);
     void *q16 = sc, *k16 = sc + al(qElems * 2), *v16 = sc + al(qElems * 2) + al(kvElems * 2);
+    unsigned int *workCounter = reinterpret_cast<unsigned int *>(sc + al(qElems * 2) + 2 * al(kvElems * 2));
     const int sms = numSMs();
     {
         const size_t nq4 = qElems / 4, nkv4 = kvElems / 4, total = nq4 + 2 * nkv4;
         const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((total + 255) / 256, static_cast<size_t>(sms) * 16));
         f32ToF16x3Kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float4 *>(q), reinterpret_cast<const float4 *>(kvK),
                                                  reinterpret_cast<const float4 *>(kvV), static_cast<uint2 *>(q16),
-                                                 static_cast<uint2 *>(k16), static_cast<uint2 *>(v16), nq4, nkv4);
+                                                 static_cast<uint2 *>(k16), static_cast<uint2 *>(v16), nq4, nkv4, workCounter);
     }
     TC_CUDA_OK(cudaGetLastError());
     CUtensorMap tmQ, tmK, tmV;
@@ -550,6 +651,9 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     prm.scaleLog2 = invSqrt * kLog2e;
     prm.err = devErrorWord();
     TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "tc_attn_prefill_f16: no device error word");
+    prm.workCounter = workCounter;
+    prm.totalItems = nQTiles * nHeads;
+    prm.out32 = (reinterpret_cast<uintptr_t>(out) & 31u) == 0 ? 1u : 0u;
 #ifdef TC_TRACE
     prm.trace = tc::g_pfTrace;
 #endif
@@ -561,7 +665,8 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
                                         PrefillF16Smem::kTotal));
         attrDone[dev] = true;
     }
-    prefillF16Kernel<<<nQTiles * nHeads, kPfThreads, PrefillF16Smem::kTotal, st>>>(tmQ, tmK, tmV, prm);
+    const uint32_t grid = std::min<uint32_t>(prm.totalItems, static_cast<uint32_t>(sms));  // one block per SM
+    prefillF16Kernel<<<grid, kPfThreads, PrefillF16Smem::kTotal, st>>>(tmQ, tmK, tmV, prm);
     TC_CUDA_OK(cudaGetLastError());
     return TC_OK;
 }
