@@ -253,11 +253,6 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #ifdef TC_TRACE
                 if (p.trace) { unsigned sm; asm("mov.u32 %0, %%smid;" : "=r"(sm)); p.trace[8u * 64u * 4u + item * 8u + 6] = sm; }
 #endif
-                // a wait that ran out anywhere ends the launch: the flag is the caller's to read
-                constexpr unsigned int kWaitBits = kDevErrFullWait | kDevErrEmptyWait | kDevErrMmaWait;
-                const bool failed = (*reinterpret_cast<volatile unsigned int *>(p.err) & kWaitBits) != 0u;
-                const uint32_t drawn = gridDim.x + atomicAdd(p.workCounter, 1u);
-                const uint32_t next = failed ? p.totalItems : drawn;
                 // the query tiles and K_0, K_1 are free once both score warps have issued the last
                 // product of the previous item that reads them, and those products are complete
                 if (n > 0 && !(pfWait(&qFree[0], (n - 1u) & 1u, p.err, kDevErrEmptyWait) &&
@@ -279,9 +274,16 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     tmaLoad3D(kd, &tmK, k01Full, 0, it.kvHead, j * kPfBN);
                     tmaLoad3D(kd + L::kKvTile / 2, &tmK, k01Full, 64, it.kvHead, j * kPfBN);
                 }
-                itemSlots[(n + 1u) & 3u] = next;
-                mbarArrive(&itemFull[(n + 1u) & 3u]);
+                // The next item is drawn late -- with the third last tile request, some six tiles before
+                // the consumers finish this item -- so that the blocks which finish first take the
+                // heavier of the remaining items.
+                const uint32_t drawAt = it.nTiles >= 3u ? it.nTiles - 3u : 0u;
+                uint32_t drawn = 0, flags = 0;
                 for (uint32_t j = 0; j < it.nTiles; ++j, ++g) {
+                    if (j == drawAt) {
+                        flags = *reinterpret_cast<volatile unsigned int *>(p.err);
+                        drawn = gridDim.x + atomicAdd(p.workCounter, 1u);
+                    }
                     const uint32_t s = g % NS;
                     if (g >= NS && !pfWait(&stEmpty[s], ((g / NS) - 1u) & 1u, p.err, kDevErrEmptyWait)) {
                         ok = false;
@@ -297,6 +299,12 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     tmaLoad3D(vd, &tmV, &stFull[s], 0, it.kvHead, j * kPfBN);
                     tmaLoad3D(vd + L::kKvTile / 2, &tmV, &stFull[s], 64, it.kvHead, j * kPfBN);
                 }
+                if (!ok) break;
+                // a wait that ran out anywhere ends the launch: the flag is the caller's to read
+                constexpr unsigned int kWaitBits = kDevErrFullWait | kDevErrEmptyWait | kDevErrMmaWait;
+                const uint32_t next = (flags & kWaitBits) != 0u ? p.totalItems : drawn;
+                itemSlots[(n + 1u) & 3u] = next;
+                mbarArrive(&itemFull[(n + 1u) & 3u]);
                 item = next;
             }
             // the last release of every stage has to have arrived before the block leaves
