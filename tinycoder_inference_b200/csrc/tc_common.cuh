@@ -66,9 +66,6 @@ constexpr uint32_t kMbarSuspendNs = 20000u;  // upper bound of one hardware-park
 __device__ __forceinline__ uint32_t smemAddr(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ void mbarInval(uint64_t *bar) {
-    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smemAddr(bar)) : "memory");
-}
 __device__ __forceinline__ void mbarInit(uint64_t *bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smemAddr(bar)), "r"(count));
 }
