@@ -128,6 +128,9 @@ __device__ __forceinline__ bool pfWait(uint64_t *bar, uint32_t parity, unsigned 
 #pragma unroll 1
         for (int i = 0; i < 128; ++i)
             if (mbarTryWait(bar, parity)) return true;
+        // somebody has already given up: what this thread waits for will not come either
+        if ((*reinterpret_cast<volatile unsigned int *>(err) & (kDevErrFullWait | kDevErrEmptyWait | kDevErrMmaWait)) != 0u)
+            return false;
         if (clock64() - t0 > (1ll << 31)) break;
     }
     atomicOr(err, bit);
