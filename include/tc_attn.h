@@ -312,7 +312,9 @@ int tc_attn_merge_exchange_local(const float *const *pAcc, const float *const *p
 
 /* Scratch bytes tc_attn_prefill_f16 needs (fp16 twins of q and of the K/V
  * rows [0, cachePos + seqLen); the reference keeps attnQ16 / attnKV16 for the
- * same purpose, GPUComputeForward.cu:3952-3968). */
+ * same purpose, GPUComputeForward.cu:3952-3968; plus the counter the blocks
+ * of the attention launch draw their work from).  The scratch belongs to one
+ * call at a time: calls that share it have to be ordered on one stream. */
 int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t cachePos,
                                       uint32_t nHeads, uint32_t nKV,
                                       uint32_t hd, size_t *bytes);
