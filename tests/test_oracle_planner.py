@@ -238,7 +238,7 @@ def test_overhead_follows_the_library_scratch():
     split = ops.context_overhead_bytes(40, 8, 128, 131072, head_parts=2, ctx_parts=4, runtime_reserve=0)
     assert split > 20 * 512 * 130 * 4 and split < base                # half the heads, plus exchange buffers
     f32 = ops.context_overhead_bytes(28, 4, 128, 32768, kv_store_i8=False, runtime_reserve=0)
-    twins = 512 * 28 * 128 * 2 + 2 * 32768 * 4 * 128 * 2               # q of a 512-row chunk, K/V of the window, fp16
+    twins = 512 * 28 * 128 * 2 + 2 * 32768 * 4 * 128 * 2 + 1024        # q of a 512-row chunk, K/V of the window, fp16; work counter
     assert f32 == 28 * 512 * 130 * 4 + twins
     assert ops.context_overhead_bytes(28, 4, 128, 32768, runtime_reserve=1 << 20) - ops.context_overhead_bytes(
         28, 4, 128, 32768, runtime_reserve=0) == 1 << 20

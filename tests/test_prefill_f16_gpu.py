@@ -17,8 +17,7 @@ pytestmark = pytest.mark.gpu
 RTOL16, ATOL16 = 2e-2, 2e-3
 
 
-def _run(S, nH, nKV, seed, scale=1.0):
-    hd = 128
+def _run(S, nH, nKV, seed, scale=1.0, hd=128):
     rng = np.random.default_rng(seed)
     q = rng.standard_normal((S, nH, hd), dtype=np.float32) * scale
     k = rng.standard_normal((S, nKV, hd), dtype=np.float32)
@@ -47,6 +46,28 @@ def test_against_materialised_reference_path(S, nH, nKV):
     assert_close(got, exact, rtol=RTOL16, atol=ATOL16, what="vs f64 on fp16 operands")
 
 
+@pytest.mark.parametrize("S,nH,nKV", [(128, 1, 1), (300, 14, 2), (1, 4, 4), (129, 7, 1), (1100, 4, 2)])
+def test_head_dim_64(S, nH, nKV):
+    # the 14 / 2 / 64 shape of the smallest model, ragged ends, more than one item per block
+    q, k, v, got, inv = _run(S, nH, nKV, seed=64 + S + nH, hd=64)
+    want = oracle.prefill_f16(q, k, v, S, nH, nKV, 64, inv)
+    assert_close(got, want, rtol=RTOL16, atol=ATOL16, what=f"prefill_f16 hd 64 S={S} nH={nH}")
+
+
+def test_head_dim_64_peaked_scores_and_continued_rows():
+    q, k, v, got, inv = _run(900, 4, 2, seed=11, scale=6.0, hd=64)
+    q16, k16, v16 = (x.astype(np.float16) for x in (q, k, v))
+    exact = oracle.attention_f64(q16.astype(np.float32), k16, v16, None, None, 900, 4, 2, 64, 0, inv)
+    assert_close(got, exact, rtol=RTOL16, atol=ATOL16, what="hd 64, peaked scores")
+    # query rows 600 .. 899 over the same cache in a call of their own
+    out = torch.full((300, 4, 64), float("nan"), device="cuda")
+    sc = _scratch(300, 4, 2, 600, hd=64)
+    ops.prefill_f16(dev(q[600:]), dev(k), dev(v), out, sc, 300, 4, 2, 64, invSqrt=inv, cachePos=600)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(host(out), got[600:], rtol=RTOL16, atol=ATOL16, what="hd 64: continued rows against the single call")
+
+
 def test_long_rows_and_peaked_scores():
     # 1536 rows: 12 query tiles, lazy rescale exercised by scores with a wide range
     q, k, v, got, inv = _run(1536, 4, 2, seed=5, scale=6.0)
@@ -71,8 +92,8 @@ def test_scratch_too_small_is_refused():
     assert e.value.code == capi.TC_EWORKSPACE
 
 
-def _scratch(S, nH, nKV, cachePos):
-    n = ops.prefill_f16_scratch_bytes(S, nH, nKV, 128, cachePos=cachePos)
+def _scratch(S, nH, nKV, cachePos, hd=128):
+    n = ops.prefill_f16_scratch_bytes(S, nH, nKV, hd, cachePos=cachePos)
     buf = torch.empty(n + 1024, dtype=torch.uint8, device="cuda")
     off = (-buf.data_ptr()) % 1024
     return buf[off:off + n]

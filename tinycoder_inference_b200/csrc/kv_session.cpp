@@ -201,7 +201,7 @@ int tc_kv_session_attend(tc_kv_session *s, uint32_t slot, float *q, const float 
     // every multi-row call on the f32 cache -- the first chunk of a prompt and the chunks behind it
     // (ModelForward.cpp:115-127 cuts prompts into 512-token calls) -- takes the tensor-core prefill
     // when the caller's scratch holds the fp16 twins of the rows it attends over
-    if (devPos == nullptr && !graphCapture && !c.kvHalf && hd == 128 && c.prefillScratch != nullptr) {
+    if (devPos == nullptr && !graphCapture && !c.kvHalf && (hd == 64 || hd == 128) && c.prefillScratch != nullptr) {
         size_t need = 0;
         if (tc_attn_prefill_f16_scratch_bytes(seqLen, pos, nH, nKV, hd, &need) == TC_OK && need <= c.prefillScratchBytes)
             return tc_attn_prefill_f16(q, static_cast<const float *>(kvK), static_cast<const float *>(kvV), attnOut,

@@ -41,7 +41,6 @@
 
 namespace tc {
 
-constexpr int kPfHD = 128;    // head_dim the kernel is built for
 constexpr int kPfBM = 128;    // query rows per tile (two tiles per CTA)
 constexpr int kPfBN = 64;     // tokens per KV tile
 constexpr int kPfStages = 4;  // K and V ring depth
@@ -107,9 +106,14 @@ __device__ __forceinline__ unsigned long long pfTime() {
 #define PF_BLK(k) do { } while (0)
 #endif
 
+// HD = head_dim, 64 or 128: a tile is HD / 64 halves of 64 columns (128 bytes, one swizzle span) each
+template <int HD>
 struct PrefillF16Smem {
-    static constexpr int kQTile = kPfBM * kPfHD * 2;   // 32 KB: 128 x 128 fp16 as two 64-column halves
-    static constexpr int kKvTile = kPfBN * kPfHD * 2;  // 16 KB: 64 x 128 fp16 as two 64-column halves
+    static constexpr int kHalves = HD / 64;
+    static constexpr int kQHalf = kPfBM * 128;         // 16 KB: 128 rows x 64 fp16
+    static constexpr int kKvHalf = kPfBN * 128;        // 8 KB: 64 rows x 64 fp16
+    static constexpr int kQTile = kHalves * kQHalf;    // head_dim 128: 32 KB
+    static constexpr int kKvTile = kHalves * kKvHalf;  // head_dim 128: 16 KB
     static constexpr int kQ = 0;                       // two query tiles
     static constexpr int kK01 = 2 * kQTile;            // K_0, K_1 (the products issued before the loop)
     static constexpr int kStage = kK01 + 2 * kKvTile;  // stage s: K slot, then V slot
@@ -187,10 +191,11 @@ __device__ __forceinline__ PfItem pfItem(const PrefillF16Params &p, uint32_t ite
 // product has been issued, its first scores are in TMEM while the softmax threads still write this
 // item's output, and tile A moves on while tile B finishes its two extra diagonal tiles.
 constexpr int kPfThreads = 416;
+template <int HD>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const PrefillF16Params p) {
-    using L = PrefillF16Smem;
+    using L = PrefillF16Smem<HD>;
     constexpr uint32_t NS = kPfStages;
     extern __shared__ uint8_t smemRaw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
@@ -265,17 +270,19 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
                 mbarExpectTx(qFull, 2 * L::kQTile);
 #pragma unroll
-                for (int x = 0; x < 2; ++x) {
-                    tmaLoad3D(smem + L::kQ + x * L::kQTile, &tmQ, qFull, 0, it.head, it.m0 + x * kPfBM);
-                    tmaLoad3D(smem + L::kQ + x * L::kQTile + L::kQTile / 2, &tmQ, qFull, 64, it.head, it.m0 + x * kPfBM);
-                }
+                for (int x = 0; x < 2; ++x)
+#pragma unroll
+                    for (int h = 0; h < L::kHalves; ++h)
+                        tmaLoad3D(smem + L::kQ + x * L::kQTile + h * L::kQHalf, &tmQ, qFull, 64 * h, it.head,
+                                  it.m0 + x * kPfBM);
                 // K_0 and K_1 feed the products issued ahead of the loop (nTiles >= 2 always)
                 mbarExpectTx(k01Full, 2 * L::kKvTile);
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     uint8_t *kd = smem + L::kK01 + j * L::kKvTile;
-                    tmaLoad3D(kd, &tmK, k01Full, 0, it.kvHead, j * kPfBN);
-                    tmaLoad3D(kd + L::kKvTile / 2, &tmK, k01Full, 64, it.kvHead, j * kPfBN);
+#pragma unroll
+                    for (int h = 0; h < L::kHalves; ++h)
+                        tmaLoad3D(kd + h * L::kKvHalf, &tmK, k01Full, 64 * h, it.kvHead, j * kPfBN);
                 }
                 // The next item is drawn late -- with the third last tile request, some six tiles before
                 // the consumers finish this item -- so that the blocks which finish first take the
@@ -295,12 +302,11 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     uint8_t *kd = smem + L::kStage + s * L::kStageBytes, *vd = kd + L::kKvTile;
                     const bool withK = j + 2 < it.nTiles;
                     mbarExpectTx(&stFull[s], withK ? 2 * L::kKvTile : L::kKvTile);
-                    if (withK) {
-                        tmaLoad3D(kd, &tmK, &stFull[s], 0, it.kvHead, (j + 2) * kPfBN);
-                        tmaLoad3D(kd + L::kKvTile / 2, &tmK, &stFull[s], 64, it.kvHead, (j + 2) * kPfBN);
+#pragma unroll
+                    for (int h = 0; h < L::kHalves; ++h) {
+                        if (withK) tmaLoad3D(kd + h * L::kKvHalf, &tmK, &stFull[s], 64 * h, it.kvHead, (j + 2) * kPfBN);
+                        tmaLoad3D(vd + h * L::kKvHalf, &tmV, &stFull[s], 64 * h, it.kvHead, j * kPfBN);
                     }
-                    tmaLoad3D(vd, &tmV, &stFull[s], 0, it.kvHead, j * kPfBN);
-                    tmaLoad3D(vd + L::kKvTile / 2, &tmV, &stFull[s], 64, it.kvHead, j * kPfBN);
                 }
                 if (!ok) break;
                 // a wait that ran out anywhere ends the launch: the flag is the caller's to read
@@ -330,11 +336,11 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const bool pvRole = warp >= 11u;
         const uint32_t issue = lane == 0 ? 1u : 0u;
         constexpr uint32_t idQK = umaInstrDescF16(kPfBM, kPfBN, 0, 0);
-        constexpr uint32_t idPV = umaInstrDescF16(kPfBM, kPfHD, 0, 1);
+        constexpr uint32_t idPV = umaInstrDescF16(kPfBM, HD, 0, 1);
         const uint64_t dQ = umaSmemDesc(smemAddr(smem + L::kQ + x * L::kQTile), 16, 1024);
         const uint64_t dK01 = umaSmemDesc(smemAddr(smem + L::kK01), 16, 1024);
         const uint64_t dKs = umaSmemDesc(smemAddr(smem + L::kStage), 16, 1024);
-        const uint64_t dVs = umaSmemDesc(smemAddr(smem + L::kStage + L::kKvTile), L::kKvTile / 2, 1024);
+        const uint64_t dVs = umaSmemDesc(smemAddr(smem + L::kStage + L::kKvTile), L::kKvHalf, 1024);
         const uint32_t tO = tmemBase + 128u * x, tS0 = tmemBase + 256u + 128u * x;
         // score product of running tile tt from the K tile at descriptor dK; tt >= 2 first waits
         // until the P.V product of tile tt - 2 has left the buffer
@@ -342,10 +348,10 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             if (tt >= 2u && !pfWait(&pvBuf[2u * x + (tt & 1u)], ((tt - 2u) >> 1) & 1u, p.err, kDevErrMmaWait)) return false;
             tcFenceAfter();
 #pragma unroll
-            for (uint32_t ks = 0; ks < 8; ++ks) {
+            for (uint32_t ks = 0; ks < HD / 16; ++ks) {
                 // k step ks: dims 16 ks .. +15 = 32 bytes inside the (ks >> 2)-th 64-dim half
-                umaMmaSSIf(issue, tS0 + 64u * (tt & 1u), descAdvance(dQ, (ks >> 2) * (L::kQTile / 2) + (ks & 3u) * 32u),
-                           descAdvance(dK, (ks >> 2) * (L::kKvTile / 2) + (ks & 3u) * 32u), idQK, ks > 0 ? 1u : 0u);
+                umaMmaSSIf(issue, tS0 + 64u * (tt & 1u), descAdvance(dQ, (ks >> 2) * L::kQHalf + (ks & 3u) * 32u),
+                           descAdvance(dK, (ks >> 2) * L::kKvHalf + (ks & 3u) * 32u), idQK, ks > 0 ? 1u : 0u);
             }
             umaCommitIf(issue, &sFull[2u * x + (tt & 1u)]);
             return true;
@@ -472,7 +478,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
                 if (rescale) {
 #pragma unroll 1
-                    for (uint32_t c = 0; c < 4; ++c) {
+                    for (uint32_t c = 0; c < HD / 32; ++c) {
                         uint32_t o[32];
                         tmemLd32(tO + laneBase + c * 32u, o);
                         tmemLdWait();
@@ -528,9 +534,9 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             tcFenceAfter();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            float *orow = p.out + (static_cast<size_t>(rq) * p.nHeads + head) * kPfHD;
+            float *orow = p.out + (static_cast<size_t>(rq) * p.nHeads + head) * HD;
 #pragma unroll 1
-            for (uint32_t c = 0; c < 4; ++c) {
+            for (uint32_t c = 0; c < HD / 32; ++c) {
                 uint32_t o[32];
                 tmemLd32(tO + laneBase + c * 32u, o);
                 tmemLdWait();
@@ -563,30 +569,30 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
 }
 
-static int f16Map(const void *base, uint32_t heads, uint32_t rows, uint32_t boxRows, CUtensorMap *out) {
+static int f16Map(const void *base, uint32_t hd, uint32_t heads, uint32_t rows, uint32_t boxRows, CUtensorMap *out) {
     TensorMapKey key;
     memset(&key, 0, sizeof(key));
     key.base = base;
     key.rank = 3;
     key.elemBytes = 2;
     key.swizzle = 3;
-    key.dims[0] = kPfHD;
+    key.dims[0] = hd;
     key.dims[1] = heads;
     key.dims[2] = rows;
-    key.strides[0] = kPfHD * 2;
-    key.strides[1] = static_cast<uint64_t>(heads) * kPfHD * 2;
+    key.strides[0] = hd * 2;
+    key.strides[1] = static_cast<uint64_t>(heads) * hd * 2;
     key.box[0] = 64;  // 128 bytes: one swizzle span
     key.box[1] = 1;
     key.box[2] = boxRows;
     return getTensorMap(key, out);
 }
 
-static size_t prefillScratchBytes(uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV) {
-    // fp16 twins: q [seqLen][nHeads][128], k and v [cachePos + seqLen][nKV][128]; each region 1 KB aligned;
+static size_t prefillScratchBytes(uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV, uint32_t hd) {
+    // fp16 twins: q [seqLen][nHeads][hd], k and v [cachePos + seqLen][nKV][hd]; each region 1 KB aligned;
     // then the work counter of the attention launch
     auto al = [](size_t x) { return (x + 1023) & ~size_t(1023); };
-    return al(static_cast<size_t>(seqLen) * nHeads * kPfHD * 2) +
-           2 * al((static_cast<size_t>(cachePos) + seqLen) * nKV * kPfHD * 2) + 1024;  // + the work counter
+    return al(static_cast<size_t>(seqLen) * nHeads * hd * 2) +
+           2 * al((static_cast<size_t>(cachePos) + seqLen) * nKV * hd * 2) + 1024;  // + the work counter
 }
 
 }  // namespace tc
@@ -600,8 +606,8 @@ extern "C" {
 int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV, uint32_t hd,
                                       size_t *bytes) {
     TC_REQUIRE(bytes != nullptr, TC_EINVAL, "tc_attn_prefill_f16_scratch_bytes: null output");
-    TC_REQUIRE(hd == tc::kPfHD, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 128)", hd);
-    *bytes = tc::prefillScratchBytes(seqLen, cachePos, nHeads, nKV);
+    TC_REQUIRE(hd == 64 || hd == 128, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 64 and 128)", hd);
+    *bytes = tc::prefillScratchBytes(seqLen, cachePos, nHeads, nKV, hd);
     return TC_OK;
 }
 
@@ -610,7 +616,7 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
                         uint32_t hd, float invSqrt, tc_stream stream) {
     using namespace tc;
     TC_REQUIRE(q && kvK && kvV && out && scratch, TC_EINVAL, "tc_attn_prefill_f16: null pointer");
-    TC_REQUIRE(hd == kPfHD, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 128)", hd);
+    TC_REQUIRE(hd == 64 || hd == 128, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 64 and 128)", hd);
     TC_REQUIRE(nKV > 0 && nHeads % nKV == 0, TC_EINVAL, "tc_attn_prefill_f16: nHeads %u not a multiple of nKV %u",
                nHeads, nKV);
     TC_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kvK) | reinterpret_cast<uintptr_t>(kvV) |
@@ -619,9 +625,9 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     if (seqLen == 0) return TC_OK;
     TC_REQUIRE(static_cast<uint64_t>(cachePos) + seqLen < (1ull << 31), TC_EUNSUPPORTED,
                "tc_attn_prefill_f16: %u + %u rows", cachePos, seqLen);
-    TC_REQUIRE(scratchBytes >= prefillScratchBytes(seqLen, cachePos, nHeads, nKV), TC_EWORKSPACE,
+    TC_REQUIRE(scratchBytes >= prefillScratchBytes(seqLen, cachePos, nHeads, nKV, hd), TC_EWORKSPACE,
                "tc_attn_prefill_f16: scratch of %zu bytes, %zu needed", scratchBytes,
-               prefillScratchBytes(seqLen, cachePos, nHeads, nKV));
+               prefillScratchBytes(seqLen, cachePos, nHeads, nKV, hd));
     TC_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 1023u) == 0, TC_EINVAL,
                "tc_attn_prefill_f16: scratch needs 1024-byte alignment");
     const uint32_t nQTiles = (seqLen + 2 * kPfBM - 1) / (2 * kPfBM);  // 256-row query blocks
@@ -629,9 +635,9 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
                "tc_attn_prefill_f16: grid too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     auto al = [](size_t x) { return (x + 1023) & ~size_t(1023); };
-    const size_t qElems = static_cast<size_t>(seqLen) * nHeads * kPfHD;
+    const size_t qElems = static_cast<size_t>(seqLen) * nHeads * hd;
     const uint32_t kvRows = cachePos + seqLen;  // the cache rows this call attends over
-    const size_t kvElems = static_cast<size_t>(kvRows) * nKV * kPfHD;
+    const size_t kvElems = static_cast<size_t>(kvRows) * nKV * hd;
     uint8_t *sc = static_cast<uint8_t *>(scratch);
     void *q16 = sc, *k16 = sc + al(qElems * 2), *v16 = sc + al(qElems * 2) + al(kvElems * 2);
     unsigned int *workCounter = reinterpret_cast<unsigned int *>(sc + al(qElems * 2) + 2 * al(kvElems * 2));
@@ -645,11 +651,11 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     }
     TC_CUDA_OK(cudaGetLastError());
     CUtensorMap tmQ, tmK, tmV;
-    int rc = f16Map(q16, nHeads, seqLen, kPfBM, &tmQ);
+    int rc = f16Map(q16, hd, nHeads, seqLen, kPfBM, &tmQ);
     if (rc != TC_OK) return rc;
-    rc = f16Map(k16, nKV, kvRows, kPfBN, &tmK);
+    rc = f16Map(k16, hd, nKV, kvRows, kPfBN, &tmK);
     if (rc != TC_OK) return rc;
-    rc = f16Map(v16, nKV, kvRows, kPfBN, &tmV);
+    rc = f16Map(v16, hd, nKV, kvRows, kPfBN, &tmV);
     if (rc != TC_OK) return rc;
     PrefillF16Params prm;
     prm.out = out;
@@ -672,12 +678,17 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attrDone[dev]) {
-        TC_CUDA_OK(cudaFuncSetAttribute(prefillF16Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        PrefillF16Smem::kTotal));
+        TC_CUDA_OK(cudaFuncSetAttribute(prefillF16Kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        PrefillF16Smem<64>::kTotal));
+        TC_CUDA_OK(cudaFuncSetAttribute(prefillF16Kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        PrefillF16Smem<128>::kTotal));
         attrDone[dev] = true;
     }
     const uint32_t grid = std::min<uint32_t>(prm.totalItems, static_cast<uint32_t>(sms));  // one block per SM
-    prefillF16Kernel<<<grid, kPfThreads, PrefillF16Smem::kTotal, st>>>(tmQ, tmK, tmV, prm);
+    if (hd == 64)
+        prefillF16Kernel<64><<<grid, kPfThreads, PrefillF16Smem<64>::kTotal, st>>>(tmQ, tmK, tmV, prm);
+    else
+        prefillF16Kernel<128><<<grid, kPfThreads, PrefillF16Smem<128>::kTotal, st>>>(tmQ, tmK, tmV, prm);
     TC_CUDA_OK(cudaGetLastError());
     return TC_OK;
 }
