@@ -81,7 +81,8 @@ struct PrefillF16Params {
     float *out;        // [seqLen][nHeads][128] f32
     uint32_t seqLen, nHeads, nKV, group;
     uint32_t cachePos;  // query row r sits at position cachePos + r and sees K/V rows [0, cachePos + r]
-    uint32_t nQTiles;   // 256-row query blocks
+    uint32_t nQTiles;   // query blocks of itemRows rows
+    uint32_t itemRows;  // 256: two query tiles per work item; 128: one (short calls, so that every SM gets an item)
     float scaleLog2;   // invSqrt * log2(e)
     unsigned int *err;
     unsigned int *workCounter;  // zero at launch; item gridDim.x + n goes to the n-th request
@@ -162,7 +163,8 @@ __device__ __forceinline__ uint64_t descAdvance(uint64_t d, uint32_t bytes) { re
 
 // What one work item (a 256-row query block of one head) covers.  Query tile X (0 = A, 1 = B) holds
 // rows m0 + 128 X .. at positions cachePos + row; it sees KV tiles 0 .. nX - 1 (64 tokens each; the
-// last two or three straddle its diagonal).  B may lie wholly past the sequence.
+// last two or three straddle its diagonal).  B may lie wholly past the sequence; a call with fewer
+// 256-row items than SMs is cut into 128-row items instead, which have no tile B.
 struct PfItem {
     uint32_t head, kvHead, m0, nA, nB, nTiles;
 };
@@ -171,8 +173,8 @@ __device__ __forceinline__ PfItem pfItem(const PrefillF16Params &p, uint32_t ite
     const uint32_t qb = p.nQTiles - 1u - item / p.nHeads;  // heavy query blocks (long causal prefixes) first
     it.head = item % p.nHeads;
     it.kvHead = it.head / p.group;
-    it.m0 = qb * 2u * kPfBM;
-    const bool activeB = it.m0 + kPfBM < p.seqLen;
+    it.m0 = qb * p.itemRows;
+    const bool activeB = p.itemRows > kPfBM && it.m0 + kPfBM < p.seqLen;
     it.nA = (p.cachePos + it.m0 + kPfBM + kPfBN - 1u) / kPfBN;
     it.nB = activeB ? (p.cachePos + it.m0 + 2u * kPfBM + kPfBN - 1u) / kPfBN : 0u;
     it.nTiles = activeB ? it.nB : it.nA;
@@ -630,7 +632,12 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
                prefillScratchBytes(seqLen, cachePos, nHeads, nKV, hd));
     TC_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 1023u) == 0, TC_EINVAL,
                "tc_attn_prefill_f16: scratch needs 1024-byte alignment");
-    const uint32_t nQTiles = (seqLen + 2 * kPfBM - 1) / (2 * kPfBM);  // 256-row query blocks
+    const int sms = numSMs();
+    // two query tiles per item keep both softmax warpgroups of a block busy; a call too short to give
+    // every SM such an item (a 512-row chunk of a prompt: 2 x nHeads items) is cut into one-tile items
+    const uint32_t itemRows =
+            static_cast<uint64_t>((seqLen + 2 * kPfBM - 1) / (2 * kPfBM)) * nHeads < static_cast<uint64_t>(sms) ? kPfBM : 2 * kPfBM;
+    const uint32_t nQTiles = (seqLen + itemRows - 1) / itemRows;
     TC_REQUIRE(static_cast<uint64_t>(nQTiles) * nHeads < (1ull << 31), TC_EUNSUPPORTED,
                "tc_attn_prefill_f16: grid too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -641,7 +648,6 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     uint8_t *sc = static_cast<uint8_t *>(scratch);
     void *q16 = sc, *k16 = sc + al(qElems * 2), *v16 = sc + al(qElems * 2) + al(kvElems * 2);
     unsigned int *workCounter = reinterpret_cast<unsigned int *>(sc + al(qElems * 2) + 2 * al(kvElems * 2));
-    const int sms = numSMs();
     {
         const size_t nq4 = qElems / 4, nkv4 = kvElems / 4, total = nq4 + 2 * nkv4;
         const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((total + 255) / 256, static_cast<size_t>(sms) * 16));
@@ -665,6 +671,7 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     prm.nKV = nKV;
     prm.group = nHeads / nKV;
     prm.nQTiles = nQTiles;
+    prm.itemRows = itemRows;
     prm.scaleLog2 = invSqrt * kLog2e;
     prm.err = devErrorWord();
     TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "tc_attn_prefill_f16: no device error word");
