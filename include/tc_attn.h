@@ -338,6 +338,22 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV,
                         uint32_t nKV, uint32_t hd, float invSqrt,
                         tc_stream stream);
 
+/* The same call for an engine that keeps an int8 decode pool beside its f32
+ * store (kv8Rows_ and its rebuild before the first decode step,
+ * GPUComputeMoE.cu:3049-3063; include/GPUCompute.hpp:869-872): the launch that makes the fp16 twins has
+ * every K/V row in registers and also writes the int8 rows of the call's new
+ * positions -- cache rows [cachePos, cachePos + seqLen) become pool rows
+ * [kv8Row, kv8Row + seqLen), bit-identical to tc_kv_quantize_i8 on those
+ * rows -- so no second pass over the cache is needed.  TC_ECONTEXT_FULL when
+ * the rows pass kv8MaxRows. */
+int tc_attn_prefill_f16_kv8(const float *q, const float *kvK, const float *kvV,
+                            float *out, void *scratch, size_t scratchBytes,
+                            uint32_t seqLen, uint32_t cachePos,
+                            uint32_t nHeads, uint32_t nKV, uint32_t hd,
+                            float invSqrt, int8_t *k8, int8_t *v8, float *ks,
+                            float *vs, uint64_t kv8Row, uint64_t kv8MaxRows,
+                            tc_stream stream);
+
 /* Replaces kWarpAttention / kWarpAttentionPos and kQ35WarpAttention
  * (include/gpu/GpuAttentionKernels.hpp:211-272, 537-599;
  * include/gpu/GpuQwen35Kernels.hpp:2437-2492): causal attention of seqLen query

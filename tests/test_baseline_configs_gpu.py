@@ -137,13 +137,13 @@ def test_c3_prefill_4096_rows_and_the_int8_mirror():
     n = ops.prefill_f16_scratch_bytes(S, nH, nKV, hd)
     buf = torch.empty(n + 1024, dtype=torch.uint8, device="cuda")
     off = (-buf.data_ptr()) % 1024
-    ops.prefill_f16(q, k, v, out, buf[off:off + n], S, nH, nKV, hd, invSqrt=inv)
-    # the int8 mirror of all 4096 positions, as the configuration asks
-    k8 = torch.empty((S + 16, nKV, hd), dtype=torch.int8, device="cuda")
-    v8 = torch.empty_like(k8)
-    ks = torch.empty((S + 16, nKV), device="cuda")
-    vs = torch.empty_like(ks)
-    ops.kv_quantize_i8(k, v, k8, v8, ks, vs, S, nKV, hd)
+    # the int8 mirror of all 4096 positions, as the configuration asks: written by the launch that
+    # makes the fp16 twins
+    k8 = torch.zeros((S + 16, nKV, hd), dtype=torch.int8, device="cuda")
+    v8 = torch.zeros_like(k8)
+    ks = torch.zeros((S + 16, nKV), device="cuda")
+    vs = torch.zeros_like(ks)
+    ops.prefill_f16(q, k, v, out, buf[off:off + n], S, nH, nKV, hd, invSqrt=inv, kv8=(k8, v8, ks, vs))
     torch.cuda.synchronize()
     assert ops.device_status() == 0
     hq, hk, hv, got = host(q), host(k), host(v), host(out)

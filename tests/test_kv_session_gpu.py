@@ -85,7 +85,7 @@ def test_prefill_then_decode_then_a_second_conversation(mode):
     _check(*e.forward(37), f"{mode}: prompt")
     assert e.s.pos == 37
     if mode == "f32+i8":
-        assert e.s.rows8(0) == 0 and e.s.rows8(1) == 0, "a prefill writes f32 rows only"
+        assert e.s.rows8(0) == 0 and e.s.rows8(1) == 0, "a prefill without scratch writes f32 rows only"
     for t in range(3):
         _check(*e.forward(1), f"{mode}: decode {t}")
     if mode in ("f32+i8", "i8"):
@@ -146,6 +146,19 @@ def test_chunked_prompt_stays_on_the_tensor_core_prefill(hd):
     for n in (96, 70, 33):
         _check(*e.forward(n), f"tcgen05 prefill chunk of {n}", tol=(2e-2, 2e-3))
     _check(*e.forward(1), "decode after the chunks")
+
+
+def test_mirror_stays_current_through_tensor_core_prefill_chunks():
+    """f32 store + int8 decode pool, scratch given: the launch that makes the fp16 twins of a chunk
+    also writes the chunk's pool rows, so the first decode step finds the pool complete."""
+    e = Engine("f32+i8", seed=21, scratch_rows=96)
+    pos = 0
+    for n in (96, 50):
+        _check(*e.forward(n), f"mirror: tcgen05 prefill chunk of {n}", tol=(2e-2, 2e-3))
+        pos += n
+        assert e.s.rows8(0) == pos and e.s.rows8(1) == pos
+    _check(*e.forward(1), "mirror: decode over a pool written by the prefill launches")
+    assert e.s.rows8(0) == pos + 1
 
 
 def test_graph_capture_and_device_position_choose_host_free_paths():

@@ -68,6 +68,44 @@ def test_head_dim_64_peaked_scores_and_continued_rows():
     assert_close(host(out), got[600:], rtol=RTOL16, atol=ATOL16, what="hd 64: continued rows against the single call")
 
 
+@pytest.mark.parametrize("hd,nH,nKV", [(128, 8, 2), (64, 14, 2)])
+def test_int8_mirror_from_the_twins_launch_equals_the_quantise_kernel(hd, nH, nKV):
+    """tc_attn_prefill_f16_kv8: the pool rows of the call's new positions, bit-identical to
+    tc_kv_quantize_i8 and to the oracle; rows before cachePos and after the call stay untouched;
+    the attention output is the one of the plain call."""
+    total, c0, S = 700, 300, 400
+    rng = np.random.default_rng(hd)
+    q = rng.standard_normal((S, nH, hd), dtype=np.float32)
+    k = rng.standard_normal((total, nKV, hd), dtype=np.float32)
+    v = rng.standard_normal((total, nKV, hd), dtype=np.float32)
+    k[c0 + 5, 1] = 0.0                                   # an all-zero row: scale 1, bytes 0
+    dq, dk, dv = dev(q), dev(k), dev(v)
+    sc = _scratch(S, nH, nKV, c0, hd=hd)
+    plain = torch.empty((S, nH, hd), device="cuda")
+    ops.prefill_f16(dq, dk, dv, plain, sc, S, nH, nKV, hd, cachePos=c0)
+    pool_rows = total + 16
+    k8 = torch.full((pool_rows, nKV, hd), 77, dtype=torch.int8, device="cuda")
+    v8 = torch.full_like(k8, 77)
+    ks = torch.full((pool_rows, nKV), -3.0, device="cuda")
+    vs = torch.full_like(ks, -3.0)
+    out = torch.empty_like(plain)
+    ops.prefill_f16(dq, dk, dv, out, sc, S, nH, nKV, hd, cachePos=c0, kv8=(k8, v8, ks, vs))
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert torch.equal(out, plain)
+    r8 = [torch.empty_like(k8), torch.empty_like(v8), torch.empty_like(ks), torch.empty_like(vs)]
+    ops.kv_quantize_i8(dk, dv, *r8, S, nKV, hd, dst_base=c0, src_base=c0)
+    w8 = oracle.quant_kv8(k[c0:], v[c0:], nKV, hd)
+    for got, ref, want, name in zip((k8, v8, ks, vs), r8, w8, ("k8", "v8", "ks", "vs")):
+        assert torch.equal(got[c0:c0 + S], ref[c0:c0 + S]), f"{name}: fused against the quantise kernel"
+        assert np.array_equal(host(got[c0:c0 + S]), want), f"{name}: fused against the oracle"
+    assert bool((k8[:c0] == 77).all()) and bool((k8[c0 + S:] == 77).all()) and bool((ks[:c0] == -3.0).all())
+    # a pool too small for the rows is refused on the host
+    with pytest.raises(capi.TcError) as e:
+        ops.prefill_f16(dq, dk, dv, out, sc, S, nH, nKV, hd, cachePos=c0, kv8=(k8[:c0 + 10], v8[:c0 + 10], ks[:c0 + 10], vs[:c0 + 10]))
+    assert e.value.code == capi.TC_ECONTEXT_FULL
+
+
 def test_long_rows_and_peaked_scores():
     # 1536 rows: 12 query tiles, lazy rescale exercised by scores with a wide range
     q, k, v, got, inv = _run(1536, 4, 2, seed=5, scale=6.0)

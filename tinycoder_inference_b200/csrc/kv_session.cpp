@@ -203,10 +203,21 @@ int tc_kv_session_attend(tc_kv_session *s, uint32_t slot, float *q, const float 
     // when the caller's scratch holds the fp16 twins of the rows it attends over
     if (devPos == nullptr && !graphCapture && !c.kvHalf && (hd == 64 || hd == 128) && c.prefillScratch != nullptr) {
         size_t need = 0;
-        if (tc_attn_prefill_f16_scratch_bytes(seqLen, pos, nH, nKV, hd, &need) == TC_OK && need <= c.prefillScratchBytes)
+        if (tc_attn_prefill_f16_scratch_bytes(seqLen, pos, nH, nKV, hd, &need) == TC_OK && need <= c.prefillScratchBytes) {
+            // With a decode pool that is current up to this call's first row, the launch that makes
+            // the fp16 twins writes the pool's rows of the new positions too: the mirror stays
+            // current through the chunks of a prompt and the first decode step has nothing to rebuild.
+            if (c.kvMirror && s->rows8[slot] == pos) {
+                rc = tc_attn_prefill_f16_kv8(q, static_cast<const float *>(kvK), static_cast<const float *>(kvV),
+                                             attnOut, c.prefillScratch, c.prefillScratchBytes, seqLen, pos, nH, nKV, hd,
+                                             s->invSqrt, k8, v8, ks, vs, pos, rows8Cap, stream);
+                if (rc == TC_OK) s->rows8[slot] = pos + seqLen;
+                return rc;
+            }
             return tc_attn_prefill_f16(q, static_cast<const float *>(kvK), static_cast<const float *>(kvV), attnOut,
                                        c.prefillScratch, c.prefillScratchBytes, seqLen, pos, nH, nKV, hd, s->invSqrt,
                                        stream);
+        }
     }
     return tc_attn_prefill_kv(q, kvK, kvV, attnOut, seqLen, nH, nKV, hd, pos, devPos, c.maxSeqLen, s->invSqrt,
                               c.kvHalf, stream);

@@ -46,34 +46,82 @@ constexpr int kPfBN = 64;     // tokens per KV tile
 constexpr int kPfStages = 4;  // K and V ring depth
 constexpr float kPfLazyLog2 = 8.0f;
 
+// Where the int8 mirror of the call's new K/V rows goes (the reference keeps such a pool beside its
+// f32 store and rebuilds it before the first decode step, GPUComputeMoE.cu:3049-3063): rows
+// [cachePos, cachePos + seqLen) of the cache become pool rows dstRow ..; null k8 = no mirror.
+struct PrefillMirror {
+    int8_t *k8, *v8;   // [rows][nKV][hd]
+    float *ks, *vs;    // [rows][nKV]
+    uint64_t dstRow;   // pool row of cache row cachePos
+    uint64_t maxRows;  // rows the pool holds
+};
+
 // f32 -> fp16 twins of q, K and V in ONE launch (the reference's kF32ToF16 x3,
-// GpuElementwiseKernels.hpp:92-101; GPUComputeForward.cu:3957-3968): the index space is the
-// concatenation of the three arrays, in units of four floats.
+// GpuElementwiseKernels.hpp:92-101; GPUComputeForward.cu:3957-3968), and -- the K/V rows being in
+// registers anyway -- the int8 rows of the new positions (one scale per row and kv head, amax / 127,
+// round-half-even: the arithmetic of kvQuantKernel, bit for bit).  q goes float4 by float4; a K/V
+// row of one kv head goes to a warp, lane i holding dims 4 i .. 4 i + 3 (head_dim <= 128).
 __global__ void __launch_bounds__(256)
-f32ToF16x3Kernel(const float4 *__restrict__ q, const float4 *__restrict__ k, const float4 *__restrict__ v,
-                 uint2 *__restrict__ q16, uint2 *__restrict__ k16, uint2 *__restrict__ v16, size_t nq4, size_t nkv4,
-                 unsigned int *__restrict__ workCounter) {
+f32ToF16MirrorKernel(const float4 *__restrict__ q, const float4 *__restrict__ k, const float4 *__restrict__ v,
+                     uint2 *__restrict__ q16, uint2 *__restrict__ k16, uint2 *__restrict__ v16, size_t nq4,
+                     size_t kvRowHeads, uint32_t nvec, size_t mirrorFrom, PrefillMirror mir, uint32_t nKV,
+                     unsigned int *__restrict__ err, unsigned int *__restrict__ workCounter) {
     // the attention launch that follows in the stream hands out its work items through this counter
     if (blockIdx.x == 0 && threadIdx.x == 0) *workCounter = 0u;
-    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    const size_t total = nq4 + 2 * nkv4;
-    for (; i < total; i += stride) {
-        const float4 *src;
-        uint2 *dst;
-        size_t j;
-        if (i < nq4) {
-            src = q, dst = q16, j = i;
-        } else if (i < nq4 + nkv4) {
-            src = k, dst = k16, j = i - nq4;
-        } else {
-            src = v, dst = v16, j = i - nq4 - nkv4;
-        }
-        const float4 x = __ldg(src + j);
+    for (size_t i = tid; i < nq4; i += stride) {
+        const float4 x = __ldg(q + i);
         uint2 o;
         o.x = packHalf2(x.x, x.y);
         o.y = packHalf2(x.z, x.w);
-        dst[j] = o;
+        q16[i] = o;
+    }
+    const uint32_t lane = threadIdx.x & 31u;
+    const bool active = lane < nvec;
+    for (size_t rh = tid >> 5; rh < kvRowHeads; rh += stride >> 5) {
+        float4 kx = make_float4(0.f, 0.f, 0.f, 0.f), vx = kx;
+        if (active) {
+            kx = __ldg(k + rh * nvec + lane);
+            vx = __ldg(v + rh * nvec + lane);
+            uint2 o;
+            o.x = packHalf2(kx.x, kx.y);
+            o.y = packHalf2(kx.z, kx.w);
+            k16[rh * nvec + lane] = o;
+            o.x = packHalf2(vx.x, vx.y);
+            o.y = packHalf2(vx.z, vx.w);
+            v16[rh * nvec + lane] = o;
+        }
+        if (mir.k8 == nullptr || rh < mirrorFrom) continue;  // warp-uniform
+        const size_t dst = mir.dstRow * nKV + (rh - mirrorFrom);
+        if (dst >= mir.maxRows * nKV) {
+            if (lane == 0) atomicOr(err, kDevErrRowBound);
+            continue;
+        }
+        float mk = fmaxf(fmaxf(fabsf(kx.x), fabsf(kx.y)), fmaxf(fabsf(kx.z), fabsf(kx.w)));
+        float mv = fmaxf(fmaxf(fabsf(vx.x), fabsf(vx.y)), fmaxf(fabsf(vx.z), fabsf(vx.w)));
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            mk = fmaxf(mk, __shfl_xor_sync(0xffffffffu, mk, o));
+            mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, o));
+        }
+        const float sk = mk > 0.0f ? __fdiv_rn(mk, 127.0f) : 1.0f;
+        const float sv = mv > 0.0f ? __fdiv_rn(mv, 127.0f) : 1.0f;
+        if (lane == 0) {
+            mir.ks[dst] = sk;
+            mir.vs[dst] = sv;
+        }
+        auto q8 = [](float x, float sc) -> uint32_t {
+            int qv = __float2int_rn(__fdiv_rn(x, sc));
+            qv = qv < -128 ? -128 : (qv > 127 ? 127 : qv);
+            return static_cast<uint32_t>(qv) & 0xffu;
+        };
+        if (active) {
+            reinterpret_cast<uint32_t *>(mir.k8)[dst * nvec + lane] =
+                    q8(kx.x, sk) | (q8(kx.y, sk) << 8) | (q8(kx.z, sk) << 16) | (q8(kx.w, sk) << 24);
+            reinterpret_cast<uint32_t *>(mir.v8)[dst * nvec + lane] =
+                    q8(vx.x, sv) | (q8(vx.y, sv) << 8) | (q8(vx.z, sv) << 16) | (q8(vx.w, sv) << 24);
+        }
     }
 }
 
@@ -613,9 +661,9 @@ int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t cachePos, uint32
     return TC_OK;
 }
 
-int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, float *out, void *scratch,
-                        size_t scratchBytes, uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV,
-                        uint32_t hd, float invSqrt, tc_stream stream) {
+static int prefillF16Impl(const float *q, const float *kvK, const float *kvV, float *out, void *scratch,
+                          size_t scratchBytes, uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV,
+                          uint32_t hd, float invSqrt, const tc::PrefillMirror &mir, tc_stream stream) {
     using namespace tc;
     TC_REQUIRE(q && kvK && kvV && out && scratch, TC_EINVAL, "tc_attn_prefill_f16: null pointer");
     TC_REQUIRE(hd == 64 || hd == 128, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 64 and 128)", hd);
@@ -648,12 +696,17 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     uint8_t *sc = static_cast<uint8_t *>(scratch);
     void *q16 = sc, *k16 = sc + al(qElems * 2), *v16 = sc + al(qElems * 2) + al(kvElems * 2);
     unsigned int *workCounter = reinterpret_cast<unsigned int *>(sc + al(qElems * 2) + 2 * al(kvElems * 2));
+    unsigned int *err = devErrorWord();
+    TC_REQUIRE(err != nullptr, TC_ECUDA, "tc_attn_prefill_f16: no device error word");
     {
-        const size_t nq4 = qElems / 4, nkv4 = kvElems / 4, total = nq4 + 2 * nkv4;
-        const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((total + 255) / 256, static_cast<size_t>(sms) * 16));
-        f32ToF16x3Kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float4 *>(q), reinterpret_cast<const float4 *>(kvK),
-                                                 reinterpret_cast<const float4 *>(kvV), static_cast<uint2 *>(q16),
-                                                 static_cast<uint2 *>(k16), static_cast<uint2 *>(v16), nq4, nkv4, workCounter);
+        const size_t nq4 = qElems / 4, kvRowHeads = static_cast<size_t>(kvRows) * nKV;
+        const size_t threads = std::max(nq4, kvRowHeads * 32);
+        const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((threads + 255) / 256, static_cast<size_t>(sms) * 16));
+        f32ToF16MirrorKernel<<<blocks, 256, 0, st>>>(
+                reinterpret_cast<const float4 *>(q), reinterpret_cast<const float4 *>(kvK),
+                reinterpret_cast<const float4 *>(kvV), static_cast<uint2 *>(q16), static_cast<uint2 *>(k16),
+                static_cast<uint2 *>(v16), nq4, kvRowHeads, hd / 4, static_cast<size_t>(cachePos) * nKV, mir, nKV, err,
+                workCounter);
     }
     TC_CUDA_OK(cudaGetLastError());
     CUtensorMap tmQ, tmK, tmV;
@@ -673,8 +726,7 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
     prm.nQTiles = nQTiles;
     prm.itemRows = itemRows;
     prm.scaleLog2 = invSqrt * kLog2e;
-    prm.err = devErrorWord();
-    TC_REQUIRE(prm.err != nullptr, TC_ECUDA, "tc_attn_prefill_f16: no device error word");
+    prm.err = err;
     prm.workCounter = workCounter;
     prm.totalItems = nQTiles * nHeads;
     prm.out32 = (reinterpret_cast<uintptr_t>(out) & 31u) == 0 ? 1u : 0u;
@@ -698,6 +750,33 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
         prefillF16Kernel<128><<<grid, kPfThreads, PrefillF16Smem<128>::kTotal, st>>>(tmQ, tmK, tmV, prm);
     TC_CUDA_OK(cudaGetLastError());
     return TC_OK;
+}
+
+int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, float *out, void *scratch,
+                        size_t scratchBytes, uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV,
+                        uint32_t hd, float invSqrt, tc_stream stream) {
+    tc::PrefillMirror none;
+    memset(&none, 0, sizeof(none));
+    return prefillF16Impl(q, kvK, kvV, out, scratch, scratchBytes, seqLen, cachePos, nHeads, nKV, hd, invSqrt, none,
+                          stream);
+}
+
+int tc_attn_prefill_f16_kv8(const float *q, const float *kvK, const float *kvV, float *out, void *scratch,
+                            size_t scratchBytes, uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV,
+                            uint32_t hd, float invSqrt, int8_t *k8, int8_t *v8, float *ks, float *vs,
+                            uint64_t kv8Row, uint64_t kv8MaxRows, tc_stream stream) {
+    TC_REQUIRE(k8 && v8 && ks && vs, TC_EINVAL, "tc_attn_prefill_f16_kv8: null pool pointer");
+    TC_REQUIRE(((reinterpret_cast<uintptr_t>(k8) | reinterpret_cast<uintptr_t>(v8)) & 3u) == 0, TC_EINVAL,
+               "tc_attn_prefill_f16_kv8: k8/v8 need 4-byte alignment");
+    if (kv8Row + seqLen > kv8MaxRows) {
+        tc::setError("tc_attn_prefill_f16_kv8: rows [%llu, %llu) pass the pool's %llu rows", (unsigned long long) kv8Row,
+                     (unsigned long long) kv8Row + seqLen, (unsigned long long) kv8MaxRows);
+        return TC_ECONTEXT_FULL;
+    }
+    tc::PrefillMirror mir;
+    mir.k8 = k8, mir.v8 = v8, mir.ks = ks, mir.vs = vs, mir.dstRow = kv8Row, mir.maxRows = kv8MaxRows;
+    return prefillF16Impl(q, kvK, kvV, out, scratch, scratchBytes, seqLen, cachePos, nHeads, nKV, hd, invSqrt, mir,
+                          stream);
 }
 
 }  // extern "C"

@@ -231,10 +231,19 @@ def prefill_f16_scratch_bytes(seqLen, nHeads, nKV, hd, cachePos=0) -> int:
     return b.value
 
 
-def prefill_f16(q, kvK, kvV, out, scratch, seqLen, nHeads, nKV, hd, invSqrt=None, cachePos=0):
-    """seqLen query rows at positions cachePos.. over cache rows [0, cachePos + seqLen) of kvK / kvV."""
+def prefill_f16(q, kvK, kvV, out, scratch, seqLen, nHeads, nKV, hd, invSqrt=None, cachePos=0, kv8=None, kv8_row=None):
+    """seqLen query rows at positions cachePos.. over cache rows [0, cachePos + seqLen) of kvK / kvV.
+    kv8 = (k8, v8, ks, vs): also write the int8 rows of the new positions into that pool, from row
+    kv8_row (default cachePos) on."""
     if invSqrt is None:
         invSqrt = 1.0 / math.sqrt(hd)
+    if kv8 is not None:
+        k8, v8, ks, vs = kv8
+        check(lib.tc_attn_prefill_f16_kv8(_ptr(q), _ptr(kvK), _ptr(kvV), _ptr(out), _ptr(scratch),
+                                          scratch.numel() * scratch.element_size(), seqLen, cachePos, nHeads, nKV, hd,
+                                          invSqrt, _ptr(k8), _ptr(v8), _ptr(ks), _ptr(vs),
+                                          cachePos if kv8_row is None else kv8_row, ks.numel() // nKV, _stream()))
+        return
     check(lib.tc_attn_prefill_f16(_ptr(q), _ptr(kvK), _ptr(kvV), _ptr(out), _ptr(scratch),
                                   scratch.numel() * scratch.element_size(), seqLen, cachePos, nHeads, nKV, hd,
                                   invSqrt, _stream()))
