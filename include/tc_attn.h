@@ -354,6 +354,27 @@ int tc_attn_prefill_f16_kv8(const float *q, const float *kvK, const float *kvV,
                             float *vs, uint64_t kv8Row, uint64_t kv8MaxRows,
                             tc_stream stream);
 
+/* The same kernel over the other two stores (tolerance of the fp16 prefill in
+ * both cases: q and the probabilities are rounded to fp16):
+ *  - _kvhalf: the fp16 store (kWarpAttention<HD, __half>,
+ *    include/gpu/GpuAttentionKernels.hpp:211-272) is read in place -- its layout
+ *    is the one the twins have -- so the scratch holds only q's twin
+ *    (tc_attn_prefill_f16_scratch_bytes with nKV = 0 says how much);
+ *  - _i8: the int8 store (kQ35WarpAttention8Prefill / kQ35PrefillAttnSharedKV8,
+ *    include/gpu/GpuQwen35Kernels.hpp:2306-2435): the twins are byte x row scale,
+ *    scratch as for the f32 store.  The rows [0, cachePos + seqLen) have to be
+ *    in the pool already (tc_kv_quantize_i8 first). */
+int tc_attn_prefill_f16_kvhalf(const float *q, const void *kvK16,
+                               const void *kvV16, float *out, void *scratch,
+                               size_t scratchBytes, uint32_t seqLen,
+                               uint32_t cachePos, uint32_t nHeads, uint32_t nKV,
+                               uint32_t hd, float invSqrt, tc_stream stream);
+int tc_attn_prefill_f16_i8(const float *q, const int8_t *k8, const int8_t *v8,
+                           const float *ks, const float *vs, float *out,
+                           void *scratch, size_t scratchBytes, uint32_t seqLen,
+                           uint32_t cachePos, uint32_t nHeads, uint32_t nKV,
+                           uint32_t hd, float invSqrt, tc_stream stream);
+
 /* Replaces kWarpAttention / kWarpAttentionPos and kQ35WarpAttention
  * (include/gpu/GpuAttentionKernels.hpp:211-272, 537-599;
  * include/gpu/GpuQwen35Kernels.hpp:2437-2492): causal attention of seqLen query

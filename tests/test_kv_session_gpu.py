@@ -148,6 +148,14 @@ def test_chunked_prompt_stays_on_the_tensor_core_prefill(hd):
     _check(*e.forward(1), "decode after the chunks")
 
 
+@pytest.mark.parametrize("mode", ["f16", "i8"])
+def test_fp16_and_int8_stores_take_the_tensor_core_prefill_with_scratch(mode):
+    e = Engine(mode, seed=31, scratch_rows=96)
+    for n in (96, 41):
+        _check(*e.forward(n), f"{mode} store: tcgen05 prefill chunk of {n}", tol=(2e-2, 2e-3))
+    _check(*e.forward(1), f"{mode} store: decode after the chunks")
+
+
 def test_mirror_stays_current_through_tensor_core_prefill_chunks():
     """f32 store + int8 decode pool, scratch given: the launch that makes the fp16 twins of a chunk
     also writes the chunk's pool rows, so the first decode step finds the pool complete."""

@@ -106,6 +106,37 @@ def test_int8_mirror_from_the_twins_launch_equals_the_quantise_kernel(hd, nH, nK
     assert e.value.code == capi.TC_ECONTEXT_FULL
 
 
+@pytest.mark.parametrize("hd,nH,nKV,total,c0", [(128, 8, 2, 700, 300), (64, 14, 2, 520, 0), (128, 4, 4, 130, 129)])
+def test_fp16_store_and_int8_store_as_the_kv_source(hd, nH, nKV, total, c0):
+    """tc_attn_prefill_f16_kvhalf reads the fp16 store in place, tc_attn_prefill_f16_i8 makes its twins
+    from bytes x row scale; both against the oracle's kernels for those stores."""
+    S = total - c0
+    inv = 1.0 / math.sqrt(hd)
+    rng = np.random.default_rng(7 * hd + total)
+    q = rng.standard_normal((S, nH, hd), dtype=np.float32)
+    k = rng.standard_normal((total, nKV, hd), dtype=np.float32)
+    v = rng.standard_normal((total, nKV, hd), dtype=np.float32)
+    dq = dev(q)
+    sc = _scratch(S, nH, nKV, c0, hd=hd)
+    # fp16 store
+    k16, v16 = k.astype(np.float16), v.astype(np.float16)
+    out = torch.full((S, nH, hd), float("nan"), device="cuda")
+    n_q = ops.prefill_f16_scratch_bytes(S, nH, 0, hd)             # q's twin and the counter are all it needs
+    ops.prefill_f16_kvhalf(dq, dev(k16), dev(v16), out, sc[:n_q], S, nH, nKV, hd, invSqrt=inv, cachePos=c0)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    want = oracle.attention_kv(q, k16, v16, S, nH, nKV, hd, c0, inv)
+    assert_close(host(out), want, rtol=RTOL16, atol=ATOL16, what=f"fp16 store, hd {hd}, rows {c0}..{total}")
+    # int8 store
+    k8, v8, ks, vs = oracle.quant_kv8(k, v, nKV, hd)
+    out.fill_(float("nan"))
+    ops.prefill_f16_i8(dq, dev(k8), dev(v8), dev(ks), dev(vs), out, sc, S, nH, nKV, hd, invSqrt=inv, cachePos=c0)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    want = oracle.attention_i8(q, k8, v8, ks, vs, S, nH, nKV, hd, c0, inv)
+    assert_close(host(out), want, rtol=RTOL16, atol=ATOL16, what=f"int8 store, hd {hd}, rows {c0}..{total}")
+
+
 def test_long_rows_and_peaked_scores():
     # 1536 rows: 12 query tiles, lazy rescale exercised by scores with a wide range
     q, k, v, got, inv = _run(1536, 4, 2, seed=5, scale=6.0)

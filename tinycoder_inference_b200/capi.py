@@ -193,6 +193,8 @@ SIGNATURES = {
                                           C.POINTER(_vp), _u32, _u32, _u32, _u32, _u32, _vp]),
     "tc_attn_prefill_f16_scratch_bytes": (_i, [_u32, _u32, _u32, _u32, _u32, _sz_p]),
     "tc_attn_prefill_f16": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_size_t, _u32, _u32, _u32, _u32, _u32, _f, _vp]),
+    "tc_attn_prefill_f16_kvhalf": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_size_t, _u32, _u32, _u32, _u32, _u32, _f, _vp]),
+    "tc_attn_prefill_f16_i8": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_size_t, _u32, _u32, _u32, _u32, _u32, _f, _vp]),
     "tc_attn_prefill_f16_kv8": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_size_t, _u32, _u32, _u32, _u32, _u32, _f, _vp, _vp, _vp,
                                      _vp, _u64, _u64, _vp]),
     "tc_attn_prefill_kv": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _u64, _f, _i, _vp]),

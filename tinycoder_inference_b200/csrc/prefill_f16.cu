@@ -56,16 +56,28 @@ struct PrefillMirror {
     uint64_t maxRows;  // rows the pool holds
 };
 
+// What the K/V rows of a call are read from: the f32 store (twins made here), the fp16 store (used in
+// place: its layout is the twins'), or the int8 store (twins made here: byte x the row's scale).
+struct PrefillKvSource {
+    int kind;             // 0 f32, 1 fp16, 2 int8
+    const void *k, *v;    // [rows][nKV][hd] of float / __half / int8_t
+    const float *ks, *vs; // int8: [rows][nKV] scales
+};
+
 // f32 -> fp16 twins of q, K and V in ONE launch (the reference's kF32ToF16 x3,
 // GpuElementwiseKernels.hpp:92-101; GPUComputeForward.cu:3957-3968), and -- the K/V rows being in
 // registers anyway -- the int8 rows of the new positions (one scale per row and kv head, amax / 127,
 // round-half-even: the arithmetic of kvQuantKernel, bit for bit).  q goes float4 by float4; a K/V
 // row of one kv head goes to a warp, lane i holding dims 4 i .. 4 i + 3 (head_dim <= 128).
+// With an int8 source (k8 != nullptr) the K/V rows are bytes and a scale per row and kv head instead of
+// floats, and there is no mirror to write.
 __global__ void __launch_bounds__(256)
 f32ToF16MirrorKernel(const float4 *__restrict__ q, const float4 *__restrict__ k, const float4 *__restrict__ v,
-                     uint2 *__restrict__ q16, uint2 *__restrict__ k16, uint2 *__restrict__ v16, size_t nq4,
-                     size_t kvRowHeads, uint32_t nvec, size_t mirrorFrom, PrefillMirror mir, uint32_t nKV,
-                     unsigned int *__restrict__ err, unsigned int *__restrict__ workCounter) {
+                     const uint32_t *__restrict__ k8, const uint32_t *__restrict__ v8, const float *__restrict__ ks8,
+                     const float *__restrict__ vs8, uint2 *__restrict__ q16, uint2 *__restrict__ k16,
+                     uint2 *__restrict__ v16, size_t nq4, size_t kvRowHeads, uint32_t nvec, size_t mirrorFrom,
+                     PrefillMirror mir, uint32_t nKV, unsigned int *__restrict__ err,
+                     unsigned int *__restrict__ workCounter) {
     // the attention launch that follows in the stream hands out its work items through this counter
     if (blockIdx.x == 0 && threadIdx.x == 0) *workCounter = 0u;
     const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -82,8 +94,16 @@ f32ToF16MirrorKernel(const float4 *__restrict__ q, const float4 *__restrict__ k,
     for (size_t rh = tid >> 5; rh < kvRowHeads; rh += stride >> 5) {
         float4 kx = make_float4(0.f, 0.f, 0.f, 0.f), vx = kx;
         if (active) {
-            kx = __ldg(k + rh * nvec + lane);
-            vx = __ldg(v + rh * nvec + lane);
+            if (k8 != nullptr) {
+                const uint32_t kb = __ldg(k8 + rh * nvec + lane), vb = __ldg(v8 + rh * nvec + lane);
+                const float sk = __ldg(ks8 + rh), sv = __ldg(vs8 + rh);
+                auto b = [](uint32_t w, int i) { return static_cast<float>(static_cast<int8_t>((w >> (8 * i)) & 0xffu)); };
+                kx = make_float4(b(kb, 0) * sk, b(kb, 1) * sk, b(kb, 2) * sk, b(kb, 3) * sk);
+                vx = make_float4(b(vb, 0) * sv, b(vb, 1) * sv, b(vb, 2) * sv, b(vb, 3) * sv);
+            } else {
+                kx = __ldg(k + rh * nvec + lane);
+                vx = __ldg(v + rh * nvec + lane);
+            }
             uint2 o;
             o.x = packHalf2(kx.x, kx.y);
             o.y = packHalf2(kx.z, kx.w);
@@ -661,11 +681,13 @@ int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t cachePos, uint32
     return TC_OK;
 }
 
-static int prefillF16Impl(const float *q, const float *kvK, const float *kvV, float *out, void *scratch,
+static int prefillF16Impl(const float *q, const tc::PrefillKvSource &src, float *out, void *scratch,
                           size_t scratchBytes, uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV,
                           uint32_t hd, float invSqrt, const tc::PrefillMirror &mir, tc_stream stream) {
     using namespace tc;
+    const void *kvK = src.k, *kvV = src.v;
     TC_REQUIRE(q && kvK && kvV && out && scratch, TC_EINVAL, "tc_attn_prefill_f16: null pointer");
+    TC_REQUIRE(src.kind != 2 || (src.ks && src.vs), TC_EINVAL, "tc_attn_prefill_f16: null scale pointer");
     TC_REQUIRE(hd == 64 || hd == 128, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 64 and 128)", hd);
     TC_REQUIRE(nKV > 0 && nHeads % nKV == 0, TC_EINVAL, "tc_attn_prefill_f16: nHeads %u not a multiple of nKV %u",
                nHeads, nKV);
@@ -675,9 +697,11 @@ static int prefillF16Impl(const float *q, const float *kvK, const float *kvV, fl
     if (seqLen == 0) return TC_OK;
     TC_REQUIRE(static_cast<uint64_t>(cachePos) + seqLen < (1ull << 31), TC_EUNSUPPORTED,
                "tc_attn_prefill_f16: %u + %u rows", cachePos, seqLen);
-    TC_REQUIRE(scratchBytes >= prefillScratchBytes(seqLen, cachePos, nHeads, nKV, hd), TC_EWORKSPACE,
-               "tc_attn_prefill_f16: scratch of %zu bytes, %zu needed", scratchBytes,
-               prefillScratchBytes(seqLen, cachePos, nHeads, nKV, hd));
+    // an fp16 store is read in place: only q's twin and the counter live in the scratch
+    const size_t need = src.kind == 1 ? prefillScratchBytes(seqLen, 0, nHeads, 0, hd)
+                                      : prefillScratchBytes(seqLen, cachePos, nHeads, nKV, hd);
+    TC_REQUIRE(scratchBytes >= need, TC_EWORKSPACE, "tc_attn_prefill_f16: scratch of %zu bytes, %zu needed",
+               scratchBytes, need);
     TC_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 1023u) == 0, TC_EINVAL,
                "tc_attn_prefill_f16: scratch needs 1024-byte alignment");
     const int sms = numSMs();
@@ -696,17 +720,24 @@ static int prefillF16Impl(const float *q, const float *kvK, const float *kvV, fl
     uint8_t *sc = static_cast<uint8_t *>(scratch);
     void *q16 = sc, *k16 = sc + al(qElems * 2), *v16 = sc + al(qElems * 2) + al(kvElems * 2);
     unsigned int *workCounter = reinterpret_cast<unsigned int *>(sc + al(qElems * 2) + 2 * al(kvElems * 2));
+    if (src.kind == 1) {
+        k16 = const_cast<void *>(kvK);
+        v16 = const_cast<void *>(kvV);
+        workCounter = reinterpret_cast<unsigned int *>(sc + al(qElems * 2));
+    }
     unsigned int *err = devErrorWord();
     TC_REQUIRE(err != nullptr, TC_ECUDA, "tc_attn_prefill_f16: no device error word");
     {
-        const size_t nq4 = qElems / 4, kvRowHeads = static_cast<size_t>(kvRows) * nKV;
+        const size_t nq4 = qElems / 4, kvRowHeads = src.kind == 1 ? 0 : static_cast<size_t>(kvRows) * nKV;
         const size_t threads = std::max(nq4, kvRowHeads * 32);
         const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((threads + 255) / 256, static_cast<size_t>(sms) * 16));
+        const bool i8 = src.kind == 2;
         f32ToF16MirrorKernel<<<blocks, 256, 0, st>>>(
-                reinterpret_cast<const float4 *>(q), reinterpret_cast<const float4 *>(kvK),
-                reinterpret_cast<const float4 *>(kvV), static_cast<uint2 *>(q16), static_cast<uint2 *>(k16),
-                static_cast<uint2 *>(v16), nq4, kvRowHeads, hd / 4, static_cast<size_t>(cachePos) * nKV, mir, nKV, err,
-                workCounter);
+                reinterpret_cast<const float4 *>(q), i8 ? nullptr : static_cast<const float4 *>(kvK),
+                i8 ? nullptr : static_cast<const float4 *>(kvV), i8 ? static_cast<const uint32_t *>(kvK) : nullptr,
+                i8 ? static_cast<const uint32_t *>(kvV) : nullptr, src.ks, src.vs, static_cast<uint2 *>(q16),
+                static_cast<uint2 *>(k16), static_cast<uint2 *>(v16), nq4, kvRowHeads, hd / 4,
+                static_cast<size_t>(cachePos) * nKV, mir, nKV, err, workCounter);
     }
     TC_CUDA_OK(cudaGetLastError());
     CUtensorMap tmQ, tmK, tmV;
@@ -757,8 +788,26 @@ int tc_attn_prefill_f16(const float *q, const float *kvK, const float *kvV, floa
                         uint32_t hd, float invSqrt, tc_stream stream) {
     tc::PrefillMirror none;
     memset(&none, 0, sizeof(none));
-    return prefillF16Impl(q, kvK, kvV, out, scratch, scratchBytes, seqLen, cachePos, nHeads, nKV, hd, invSqrt, none,
-                          stream);
+    const tc::PrefillKvSource src = {0, kvK, kvV, nullptr, nullptr};
+    return prefillF16Impl(q, src, out, scratch, scratchBytes, seqLen, cachePos, nHeads, nKV, hd, invSqrt, none, stream);
+}
+
+int tc_attn_prefill_f16_kvhalf(const float *q, const void *kvK16, const void *kvV16, float *out, void *scratch,
+                               size_t scratchBytes, uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV,
+                               uint32_t hd, float invSqrt, tc_stream stream) {
+    tc::PrefillMirror none;
+    memset(&none, 0, sizeof(none));
+    const tc::PrefillKvSource src = {1, kvK16, kvV16, nullptr, nullptr};
+    return prefillF16Impl(q, src, out, scratch, scratchBytes, seqLen, cachePos, nHeads, nKV, hd, invSqrt, none, stream);
+}
+
+int tc_attn_prefill_f16_i8(const float *q, const int8_t *k8, const int8_t *v8, const float *ks, const float *vs,
+                           float *out, void *scratch, size_t scratchBytes, uint32_t seqLen, uint32_t cachePos,
+                           uint32_t nHeads, uint32_t nKV, uint32_t hd, float invSqrt, tc_stream stream) {
+    tc::PrefillMirror none;
+    memset(&none, 0, sizeof(none));
+    const tc::PrefillKvSource src = {2, k8, v8, ks, vs};
+    return prefillF16Impl(q, src, out, scratch, scratchBytes, seqLen, cachePos, nHeads, nKV, hd, invSqrt, none, stream);
 }
 
 int tc_attn_prefill_f16_kv8(const float *q, const float *kvK, const float *kvV, float *out, void *scratch,
@@ -775,8 +824,8 @@ int tc_attn_prefill_f16_kv8(const float *q, const float *kvK, const float *kvV, 
     }
     tc::PrefillMirror mir;
     mir.k8 = k8, mir.v8 = v8, mir.ks = ks, mir.vs = vs, mir.dstRow = kv8Row, mir.maxRows = kv8MaxRows;
-    return prefillF16Impl(q, kvK, kvV, out, scratch, scratchBytes, seqLen, cachePos, nHeads, nKV, hd, invSqrt, mir,
-                          stream);
+    const tc::PrefillKvSource src = {0, kvK, kvV, nullptr, nullptr};
+    return prefillF16Impl(q, src, out, scratch, scratchBytes, seqLen, cachePos, nHeads, nKV, hd, invSqrt, mir, stream);
 }
 
 }  // extern "C"

@@ -249,6 +249,24 @@ def prefill_f16(q, kvK, kvV, out, scratch, seqLen, nHeads, nKV, hd, invSqrt=None
                                   invSqrt, _stream()))
 
 
+def prefill_f16_kvhalf(q, kvK16, kvV16, out, scratch, seqLen, nHeads, nKV, hd, invSqrt=None, cachePos=0):
+    """The tcgen05 prefill over an fp16 store (read in place; the scratch holds q's twin only)."""
+    if invSqrt is None:
+        invSqrt = 1.0 / math.sqrt(hd)
+    check(lib.tc_attn_prefill_f16_kvhalf(_ptr(q), _ptr(kvK16), _ptr(kvV16), _ptr(out), _ptr(scratch),
+                                         scratch.numel() * scratch.element_size(), seqLen, cachePos, nHeads, nKV, hd,
+                                         invSqrt, _stream()))
+
+
+def prefill_f16_i8(q, k8, v8, ks, vs, out, scratch, seqLen, nHeads, nKV, hd, invSqrt=None, cachePos=0):
+    """The tcgen05 prefill over an int8 store whose rows [0, cachePos + seqLen) are written."""
+    if invSqrt is None:
+        invSqrt = 1.0 / math.sqrt(hd)
+    check(lib.tc_attn_prefill_f16_i8(_ptr(q), _ptr(k8), _ptr(v8), _ptr(ks), _ptr(vs), _ptr(out), _ptr(scratch),
+                                     scratch.numel() * scratch.element_size(), seqLen, cachePos, nHeads, nKV, hd,
+                                     invSqrt, _stream()))
+
+
 def prefill_kv(q, kvK, kvV, out, seqLen, nHeads, nKV, hd, cachePos, invSqrt=None, dev_pos=None):
     if invSqrt is None:
         invSqrt = 1.0 / math.sqrt(hd)
