@@ -1011,9 +1011,9 @@ def main():
 
     # ---- end to end through the C ABI with HOST buffers ---------------------------
     # A step: the new token's q, k, v of every layer come from pinned host memory (one
-    # asynchronous copy each), then per layer k/v are quantised and appended at the last row
-    # and attention runs (the captured launch sequence of the step), and the step's outputs go
-    # back to pinned host memory; the host waits for them.
+    # asynchronous copy each), then per layer attention runs with k/v quantised into the last
+    # row by the decode launch itself (the captured launch sequence of the step), and the
+    # step's outputs go back to pinned host memory; the host waits for them.
     hq = torch.randn((layers, batch, nH, hd)).pin_memory()
     hk = torch.randn((layers, batch, nKV, hd)).pin_memory()
     hv = torch.randn((layers, batch, nKV, hd)).pin_memory()
@@ -1025,12 +1025,10 @@ def main():
 
     def e2e_layers():
         for l in range(layers):
-            ops.kv_quantize_i8_batch(dk[l], dv[l], k8[l], v8[l], ks[l], vs[l], batch, nKV, hd, rows_per_seq=rows,
-                                     pos=ctx - 1)
             nxt = None if args.no_next_prefetch else (k8[(l + 1) % layers], v8[(l + 1) % layers])
             ops.decode_i8_batch(dq[l], k8[l], v8[l], ks[l], vs[l], dout[l], ws, lens_arg, batch, nH, nKV, hd, ctx,
                                 chunks, rows_per_seq=rows, invSqrt=inv, pdl=not args.no_pdl, prefetch_rows=ctx - 1,
-                                next_kv=nxt, tickets=tickets)
+                                next_kv=nxt, tickets=tickets, append=(dk[l], dv[l]))
 
     if args.no_graph:
         e2e_run = e2e_layers

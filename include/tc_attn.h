@@ -209,6 +209,13 @@ typedef struct tc_decode_i8_batch {
      * another, and the merge launch with its hand-off disappears.  Calls that may run
      * concurrently (different streams) need counters of their own. */
     uint32_t *mergeTickets;
+    /* Optional (NULL = the rows are in the pool already): the new token's K and V rows, f32
+     * [batch][nKV][hd].  The launch then quantises them into row len - 1 of every sequence --
+     * the bytes and scales tc_kv_quantize_i8_batch writes -- before that row is read: the blocks
+     * that hold a sequence's last tile do it once the kernels ahead in the stream have completed,
+     * so the separate quantise launch between two layers' attention disappears.  k8 / v8 / ks / vs
+     * are written through in this case. */
+    const float *appendK, *appendV;
 } tc_decode_i8_batch;
 
 enum { TC_DECODE_PDL = 1u };

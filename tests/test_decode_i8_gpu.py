@@ -173,6 +173,56 @@ def test_partials_contract_and_merge_entry_point():
     assert all(torch.equal(a, b) for a, b in zip(ws, ws2))
 
 
+@pytest.mark.parametrize("hd,pdl,dev_lens", [(128, False, True), (128, True, False), (128, False, False), (256, False, True)])
+def test_new_rows_quantised_by_the_decode_launch(hd, pdl, dev_lens):
+    """appendK / appendV: the launch writes row len - 1 of every sequence itself -- the bytes and scales
+    of tc_kv_quantize_i8_batch -- and attends over it; output and pool equal quantise-then-decode."""
+    nH, nKV, B, numChunks = 16, 4, 3, 64
+    lens = np.array([700, 129, 1], np.uint32) if dev_lens else np.array([513, 513, 513], np.uint32)
+    rows_per_seq = 720 + 16
+    rng = np.random.default_rng(hd + int(pdl))
+    inv = 1.0 / math.sqrt(hd)
+    q = rng.standard_normal((B, nH, hd), dtype=np.float32)
+    newk = rng.standard_normal((B, nKV, hd), dtype=np.float32)
+    newv = rng.standard_normal((B, nKV, hd), dtype=np.float32)
+    newk[1, 2] = 0.0                                       # an all-zero row: scale 1
+    k8 = np.zeros((B, rows_per_seq, nKV, hd), np.int8)
+    v8 = np.zeros_like(k8)
+    ks = np.full((B, rows_per_seq, nKV), np.nan, np.float32)
+    vs = np.full_like(ks, np.nan)
+    want = np.zeros((B, nH, hd), np.float32)
+    for b, n in enumerate(lens):
+        k = np.concatenate([rng.standard_normal((n - 1, nKV, hd), dtype=np.float32), newk[b:b + 1]])
+        v = np.concatenate([rng.standard_normal((n - 1, nKV, hd), dtype=np.float32), newv[b:b + 1]])
+        a, c, d, e = oracle.quant_kv8(k, v, nKV, hd)
+        k8[b, :n - 1], v8[b, :n - 1], ks[b, :n - 1], vs[b, :n - 1] = a[:-1], c[:-1], d[:-1], e[:-1]   # the last row is missing
+        want[b] = oracle.attention_i8(q[b:b + 1], a, c, d, e, 1, nH, nKV, hd, int(n) - 1, inv)[0]
+    ws = ops.workspace(B, nH, hd, numChunks)
+    dl = dev(lens) if dev_lens else None
+    # reference arm: quantise launch, then decode
+    p1 = [dev(x) for x in (k8, v8, ks, vs)]
+    out1 = torch.full((B, nH, hd), float("nan"), device="cuda")
+    ops.kv_quantize_i8_batch(dev(newk), dev(newv), *p1, B, nKV, hd, rows_per_seq=rows_per_seq,
+                             **({"lens": dl, "len_add": -1} if dev_lens else {"pos": int(lens[0]) - 1}))
+    ops.decode_i8_batch(dev(q), *p1, out1, ws, dl, B, nH, nKV, hd, int(lens.max()), numChunks,
+                        rows_per_seq=rows_per_seq, invSqrt=inv)
+    # fused arm
+    p2 = [dev(x) for x in (k8, v8, ks, vs)]
+    out2 = torch.full((B, nH, hd), float("nan"), device="cuda")
+    ops.decode_i8_batch(dev(q), *p2, out2, ws, dl, B, nH, nKV, hd, int(lens.max()), numChunks,
+                        rows_per_seq=rows_per_seq, invSqrt=inv, append=(dev(newk), dev(newv)), pdl=pdl,
+                        prefetch_rows=int(lens.max()) - 1 if pdl else 0)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(host(out2), want, what="decode with the new rows appended by the launch")
+    # (the dependent-launch form merges with another kernel: same rule, another summation order)
+    assert torch.equal(out1, out2) if not pdl else torch.allclose(out1, out2, rtol=1e-5, atol=1e-6)
+    for a, b_, name in zip(p1, p2, ("k8", "v8", "ks", "vs")):
+        for s_ in range(B):
+            n = int(lens[s_])
+            assert torch.equal(a[s_, :n], b_[s_, :n]), f"{name}: pool rows of sequence {s_}"
+
+
 def test_dependent_launch_chain_and_host_lengths():
     """Three 'layers' back to back with programmatic dependent launch (KV rows of a
     layer stream in while the previous layer's kernels drain) give the same

@@ -147,6 +147,8 @@ class DecodeI8Batch(C.Structure):
         ("nextK8", C.c_void_p),
         ("nextV8", C.c_void_p),
         ("mergeTickets", C.c_void_p),
+        ("appendK", C.c_void_p),
+        ("appendV", C.c_void_p),
     ]
 
 

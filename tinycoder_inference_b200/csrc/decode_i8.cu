@@ -572,7 +572,16 @@ static int decodeI8Common(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_
     TC_REQUIRE(d->numChunks >= 1, TC_EWORKSPACE, "decode_i8: no chunk slots");
     // head_dim 128 runs on the tcgen05 integer path; this file's mma.sync kernel keeps head_dim
     // 256 and the causal rows mode
+    TC_REQUIRE((d->appendK == nullptr) == (d->appendV == nullptr), TC_EINVAL, "decode_i8: appendK and appendV come together");
     if (hd == 128 && !forceLegacyDecode()) return decodeI8Tc(d, lenHost, lenAdd, st);
+    if (d->appendK != nullptr) {
+        // this file's kernel reads the pool only: the new rows go in with the quantise launch
+        const int rc = tc_kv_quantize_i8_batch(d->appendK, d->appendV, const_cast<int8_t *>(d->k8),
+                                               const_cast<int8_t *>(d->v8), const_cast<float *>(d->ks),
+                                               const_cast<float *>(d->vs), d->batch, d->nKV, hd, d->rowsPerSeq, d->rowBase,
+                                               lenHost - 1u, d->lens, static_cast<int32_t>(lenAdd) - 1, d->totalRows, st);
+        if (rc != TC_OK) return rc;
+    }
     // work quantum: 32 tokens per warp when every warp of the machine gets at least ~12
     // of them, 16 otherwise (see DecodeI8Smem)
     const uint64_t warpTiles32 = static_cast<uint64_t>(d->batch) * d->nKV * ((d->maxLen + 31) / 32);

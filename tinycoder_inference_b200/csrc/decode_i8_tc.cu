@@ -43,6 +43,8 @@ struct DecodeTcParams {
     const float *q;
     float *out;
     const float *ks, *vs;
+    const float *appendK, *appendV;  // nullable: [batch][nKV][128] rows to quantise into row len - 1 first
+    int8_t *k8w, *v8w;               // the pools, for that row
     const int8_t *nextK8, *nextV8;  // nullable: pools of the next call (L2 prefetch)
     float *pAcc, *pM, *pL;
     uint32_t *tickets;           // nullable: [batch][nKV] arrival counters of the in-kernel merge (zero between calls)
@@ -157,7 +159,34 @@ __device__ __forceinline__ bool barOr(uint32_t id, uint32_t threads, bool pred) 
 }
 __device__ __forceinline__ float i2f(uint32_t x) { return __int2float_rn(static_cast<int>(x)); }
 
-template <int NWG, int NS>
+// One instance of the IEEE division for the cold code below.
+__device__ __noinline__ float ieeeDiv(float a, float b) { return __fdiv_rn(a, b); }
+
+// The new token's K and V row of one kv head into the int8 pool, by one warp (the arithmetic of
+// kvQuantKernel: amax / 127, IEEE divide, round-half-even; lane i owns dims 4 i .. 4 i + 3 of the 128).
+// Blocks that share the kv head write the same bytes.  Out of line and small: it runs once per launch
+// and kv head.  src: the row's 32 float4; dst: row x nKV + kv head of the pool.
+__device__ __noinline__ void appendNewRow(const float4 *src, uint32_t *pool8, float *scales, uint64_t dst,
+                                          uint32_t lane) {
+    const float4 x = __ldg(src + lane);
+    float m = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float sc = m > 0.0f ? ieeeDiv(m, 127.0f) : 1.0f;
+    if (lane == 0) scales[dst] = sc;
+    auto q8 = [](float q) -> uint32_t {
+        int qv = __float2int_rn(q);
+        qv = qv < -128 ? -128 : (qv > 127 ? 127 : qv);
+        return static_cast<uint32_t>(qv) & 0xffu;
+    };
+    pool8[dst * 32u + lane] = q8(ieeeDiv(x.x, sc)) | (q8(ieeeDiv(x.y, sc)) << 8) | (q8(ieeeDiv(x.z, sc)) << 16) |
+                              (q8(ieeeDiv(x.w, sc)) << 24);
+}
+
+// APPEND: the instantiation for calls that hand in the new token's rows.  It is a kernel of its own
+// because the mere presence of that (cold) code -- inlined or called, inside or behind the producer's
+// loop -- cost the 7B-shaped batch-1 step 0.5 us; calls without new rows run the other instantiation.
+template <int NWG, int NS, bool APPEND>
 __global__ void __launch_bounds__((4 * NWG + 9) * 32, 1)
 decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                  const __grid_constant__ CUtensorMap tmKn, const __grid_constant__ CUtensorMap tmVn,
@@ -240,9 +269,9 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             }
         };
         bool waited = !earlyOk;
-        for (uint32_t it = 0; it < nTiles; ++it) {
+        auto requestTile = [&](uint32_t it) -> bool {
             const uint32_t s = it % NS;
-            if (it >= NS && !mbarWaitClock(&emptyBar[s], ((it / NS) - 1u) & 1u, p.err, kDevErrEmptyWait)) break;
+            if (it >= NS && !mbarWaitClock(&emptyBar[s], ((it / NS) - 1u) & 1u, p.err, kDevErrEmptyWait)) return false;
             const uint32_t tok = t0 + it * T;
             if (!waited && (tok + T > p.prefetchRows || it >= p.earlyStages)) {
                 // rows the kernel in front may still be writing, or further ahead of the dependency
@@ -273,6 +302,31 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             }
             cpAsyncMbarArriveNoinc(&fullBar[s]);
             if (lane == 0) { if (it == 0) TC_STAMP(13); TC_STAMP(14); }
+            return true;
+        };
+        // The tile that holds the row of a token being appended (the last tile of the sequence's last
+        // chunk) is requested apart from the loop: the row goes into the pool first, once the kernels
+        // ahead have completed.
+        const bool appendHere = APPEND && p.appendK != nullptr && t1 == len;
+        const uint32_t nLoop = appendHere ? nTiles - 1u : nTiles;
+        bool okP = true;
+        for (uint32_t it = 0; okP && it < nLoop; ++it) okP = requestTile(it);
+        if (appendHere && okP) {
+            if (!waited) {
+                gridDepWait();
+                waited = true;
+            }
+            const size_t srcRow = (static_cast<size_t>(b) * p.nKV + kvHead) * 32u;
+            const uint64_t dst = (rowBase + len - 1u) * p.nKV + kvHead;
+            appendNewRow(reinterpret_cast<const float4 *>(p.appendK) + srcRow, reinterpret_cast<uint32_t *>(p.k8w),
+                         const_cast<float *>(p.ks), dst, lane);
+            appendNewRow(reinterpret_cast<const float4 *>(p.appendV) + srcRow, reinterpret_cast<uint32_t *>(p.v8w),
+                         const_cast<float *>(p.vs), dst, lane);
+            // the row is read back by TMA (the async proxy) and by the scale copies of the tile
+            __threadfence();
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            __syncwarp();
+            requestTile(nTiles - 1u);
         }
         // all tiles of this block are requested: the next call's rows follow them into L2 (requested
         // earlier they sit in front of this block's own tiles in the queue: 10.2 against 9.1 us)
@@ -720,6 +774,10 @@ int decodeI8Tc(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_t lenAdd, c
     prm.vs = d->vs;
     prm.nextK8 = d->nextK8;
     prm.nextV8 = d->nextV8;
+    prm.appendK = d->appendK;
+    prm.appendV = d->appendV;
+    prm.k8w = const_cast<int8_t *>(d->k8);
+    prm.v8w = const_cast<int8_t *>(d->v8);
     prm.pAcc = d->pAcc;
     prm.pM = d->pM;
     prm.pL = d->pL;
@@ -761,12 +819,15 @@ int decodeI8Tc(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_t lenAdd, c
     // (Four softmax warpgroups with a five-stage ring were measured and dropped: 11.5 against 8.3 us
     // per layer for the split launch alone at 32768 rows, 53.9 against 47.0 us at batch 8.)
     using Smem = DecodeTcSmem<2, 6>;
-    auto kern = decodeI8TcKernel<2, 6>;
+    auto kern = d->appendK != nullptr ? decodeI8TcKernel<2, 6, true> : decodeI8TcKernel<2, 6, false>;
     static bool attrDone[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attrDone[dev]) {
-        TC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal));
+        TC_CUDA_OK(cudaFuncSetAttribute(decodeI8TcKernel<2, 6, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Smem::kTotal));
+        TC_CUDA_OK(cudaFuncSetAttribute(decodeI8TcKernel<2, 6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Smem::kTotal));
         attrDone[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};

@@ -143,9 +143,11 @@ def decode_i8_noalloc(q, k8, v8, ks, vs, out, nHeads, nKV, hd, cachePos, invSqrt
 
 def decode_i8_batch(q, k8, v8, ks, vs, out, ws, lens, batch, nHeads, nKV, hd, maxLen, numChunks,
                     rows_per_seq=0, row_base=None, invSqrt=None, partials_only=False, pdl=False,
-                    prefetch_rows=0, next_kv=None, tickets=None):
+                    prefetch_rows=0, next_kv=None, tickets=None, append=None):
     """`batch` sequences in one pool; returns the chunk slots used per head.
-    lens=None: every sequence is maxLen rows long (host length)."""
+    lens=None: every sequence is maxLen rows long (host length).
+    append=(k, v): f32 [batch][nKV][hd] rows of the new token, quantised into row len - 1 of every
+    sequence by the launch itself."""
     if invSqrt is None:
         invSqrt = 1.0 / math.sqrt(hd)
     pAcc, pM, pL = ws
@@ -162,6 +164,8 @@ def decode_i8_batch(q, k8, v8, ks, vs, out, ws, lens, batch, nHeads, nKV, hd, ma
     if tickets is not None:      # zeroed uint32 [batch * nKV]: the kernel merges its own partials
         assert tickets.dtype == torch.int32 and tickets.numel() >= batch * nKV
         d.mergeTickets = tickets.data_ptr()
+    if append is not None:
+        d.appendK, d.appendV = append[0].data_ptr(), append[1].data_ptr()
     d.rowBase = row_base.data_ptr() if row_base is not None else None
     d.rowsPerSeq = rows_per_seq
     d.totalRows = k8.numel() // (nKV * hd)
