@@ -186,7 +186,7 @@ __device__ __noinline__ void appendNewRow(const float4 *src, uint32_t *pool8, fl
 // APPEND: the instantiation for calls that hand in the new token's rows.  It is a kernel of its own
 // because the mere presence of that (cold) code -- inlined or called, inside or behind the producer's
 // loop -- cost the 7B-shaped batch-1 step 0.5 us; calls without new rows run the other instantiation.
-template <int NWG, int NS, bool APPEND>
+template <int NWG, int NS, bool APPEND, bool TICKETS>
 __global__ void __launch_bounds__((4 * NWG + 9) * 32, 1)
 decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                  const __grid_constant__ CUtensorMap tmKn, const __grid_constant__ CUtensorMap tmVn,
@@ -654,7 +654,7 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 }
             }
         }
-        if (!p.directOut && p.tickets != nullptr) {
+        if (TICKETS && !p.directOut && p.tickets != nullptr) {
             // ---- merge inside the kernel: the block that arrives last at its (sequence, kv head)
             // counter folds all chunk partials of the kv head's q heads.  Nobody waits: every block
             // publishes its partial, takes a ticket and leaves unless the ticket is the last one.
@@ -819,14 +819,20 @@ int decodeI8Tc(const tc_decode_i8_batch *d, uint32_t lenHost, uint32_t lenAdd, c
     // (Four softmax warpgroups with a five-stage ring were measured and dropped: 11.5 against 8.3 us
     // per layer for the split launch alone at 32768 rows, 53.9 against 47.0 us at batch 8.)
     using Smem = DecodeTcSmem<2, 6>;
-    auto kern = d->appendK != nullptr ? decodeI8TcKernel<2, 6, true> : decodeI8TcKernel<2, 6, false>;
+    // (the in-kernel merge is an instantiation of its own for the same reason as the append)
+    auto kern = d->appendK != nullptr ? (fused ? decodeI8TcKernel<2, 6, true, true> : decodeI8TcKernel<2, 6, true, false>)
+                                      : (fused ? decodeI8TcKernel<2, 6, false, true> : decodeI8TcKernel<2, 6, false, false>);
     static bool attrDone[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attrDone[dev]) {
-        TC_CUDA_OK(cudaFuncSetAttribute(decodeI8TcKernel<2, 6, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TC_CUDA_OK(cudaFuncSetAttribute(decodeI8TcKernel<2, 6, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         Smem::kTotal));
-        TC_CUDA_OK(cudaFuncSetAttribute(decodeI8TcKernel<2, 6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        TC_CUDA_OK(cudaFuncSetAttribute(decodeI8TcKernel<2, 6, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Smem::kTotal));
+        TC_CUDA_OK(cudaFuncSetAttribute(decodeI8TcKernel<2, 6, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Smem::kTotal));
+        TC_CUDA_OK(cudaFuncSetAttribute(decodeI8TcKernel<2, 6, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         Smem::kTotal));
         attrDone[dev] = true;
     }
