@@ -165,11 +165,21 @@ int tc_kv_session_attend(tc_kv_session *s, uint32_t slot, float *q, const float 
             rc = tc_kv_append(kSrc, vSrc, kvK, kvV, c.kvHalf, 1, nKV, hd, pos, nullptr, c.maxSeqLen, stream);
             if (rc != TC_OK) return rc;
         }
-        rc = tc_kv_quantize_i8(kSrc, vSrc, k8, v8, ks, vs, 1, nKV, hd, pos, 0, nullptr, rows8Cap, stream);
-        if (rc != TC_OK) return rc;
-        rows8 = pos + 1u;
-        return tc_attn_decode_i8(q, k8, v8, ks, vs, attnOut, c.pAcc, c.pM, c.pL, nH, nKV, hd, pos, nullptr, rows8Cap,
-                                 c.numChunks, 0, s->invSqrt, stream);
+        // the decode launch quantises the new row into the pool itself (one launch instead of two)
+        tc_decode_i8_batch d;
+        memset(&d, 0, sizeof(d));
+        d.q = q, d.out = attnOut;
+        d.k8 = k8, d.v8 = v8, d.ks = ks, d.vs = vs;
+        d.pAcc = c.pAcc, d.pM = c.pM, d.pL = c.pL;
+        d.totalRows = rows8Cap;
+        d.batch = 1, d.nHeads = nH, d.nKV = nKV, d.hd = hd;
+        d.maxLen = pos + 1u;
+        d.numChunks = c.numChunks;
+        d.invSqrt = s->invSqrt;
+        d.appendK = kSrc, d.appendV = vSrc;
+        rc = tc_attn_decode_i8_batch(&d, stream);
+        if (rc == TC_OK) rows8 = pos + 1u;
+        return rc;
     }
 
     // ---- int8 as the store: quantise the rows straight into the pool, attend over it ----
