@@ -214,7 +214,8 @@ typedef struct tc_decode_i8_batch {
      * the bytes and scales tc_kv_quantize_i8_batch writes -- before that row is read: the blocks
      * that hold a sequence's last tile do it once the kernels ahead in the stream have completed,
      * so the separate quantise launch between two layers' attention disappears.  k8 / v8 / ks / vs
-     * are written through in this case. */
+     * are written through in this case.  A device length that puts the row outside totalRows
+     * skips the store and sets the row-bound bit of tc_device_status. */
     const float *appendK, *appendV;
 } tc_decode_i8_batch;
 

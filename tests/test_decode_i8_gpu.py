@@ -223,6 +223,31 @@ def test_new_rows_quantised_by_the_decode_launch(hd, pdl, dev_lens):
             assert torch.equal(a[s_, :n], b_[s_, :n]), f"{name}: pool rows of sequence {s_}"
 
 
+def test_new_row_past_the_pool_is_skipped_and_flagged():
+    """A device length that puts the appended row outside the pool: nothing is written there, the
+    error word carries the row-bound bit, nothing faults (the canary rows behind the pool stay)."""
+    nH, nKV, hd, rows = 8, 2, 128, 256
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    k8 = torch.randint(-128, 128, (rows + 8, nKV, hd), dtype=torch.int8, device="cuda", generator=g)
+    v8 = torch.randint(-128, 128, (rows + 8, nKV, hd), dtype=torch.int8, device="cuda", generator=g)
+    ks = torch.rand((rows + 8, nKV), device="cuda", generator=g)
+    vs = torch.rand((rows + 8, nKV), device="cuda", generator=g)
+    before = [x.clone() for x in (k8, v8, ks, vs)]
+    q = torch.randn((1, nH, hd), device="cuda", generator=g)
+    newk = torch.randn((1, nKV, hd), device="cuda", generator=g)
+    out = torch.empty((1, nH, hd), device="cuda")
+    ws = ops.workspace(1, nH, hd, 16)
+    lens = torch.tensor([rows + 1], dtype=torch.int32, device="cuda")     # row `rows` is one past the pool
+    # (the host bound covers the bad length, so the block of the last chunk gets to the append)
+    ops.decode_i8_batch(q, k8[:rows], v8[:rows], ks[:rows], vs[:rows], out, ws, lens, 1, nH, nKV, hd, rows + 8, 16,
+                        rows_per_seq=rows, append=(newk, newk))
+    torch.cuda.synchronize()
+    assert ops.device_status(raise_on_flags=False) == 32
+    for a, b_ in zip(before, (k8, v8, ks, vs)):
+        assert torch.equal(a, b_)
+
+
 def test_dependent_launch_chain_and_host_lengths():
     """Three 'layers' back to back with programmatic dependent launch (KV rows of a
     layer stream in while the previous layer's kernels drain) give the same

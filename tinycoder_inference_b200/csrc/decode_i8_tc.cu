@@ -318,14 +318,20 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             }
             const size_t srcRow = (static_cast<size_t>(b) * p.nKV + kvHead) * 32u;
             const uint64_t dst = (rowBase + len - 1u) * p.nKV + kvHead;
-            appendNewRow(reinterpret_cast<const float4 *>(p.appendK) + srcRow, reinterpret_cast<uint32_t *>(p.k8w),
-                         const_cast<float *>(p.ks), dst, lane);
-            appendNewRow(reinterpret_cast<const float4 *>(p.appendV) + srcRow, reinterpret_cast<uint32_t *>(p.v8w),
-                         const_cast<float *>(p.vs), dst, lane);
-            // the row is read back by TMA (the async proxy) and by the scale copies of the tile
-            __threadfence();
-            asm volatile("fence.proxy.async.global;" ::: "memory");
-            __syncwarp();
+            // a length read from device memory is checked where it is known: outside the pool the
+            // store is skipped and the error word says so
+            if (rowBase + len - 1u >= p.totalRows) {
+                if (lane == 0) atomicOr(p.err, kDevErrRowBound);
+            } else {
+                appendNewRow(reinterpret_cast<const float4 *>(p.appendK) + srcRow, reinterpret_cast<uint32_t *>(p.k8w),
+                             const_cast<float *>(p.ks), dst, lane);
+                appendNewRow(reinterpret_cast<const float4 *>(p.appendV) + srcRow, reinterpret_cast<uint32_t *>(p.v8w),
+                             const_cast<float *>(p.vs), dst, lane);
+                // the row is read back by TMA (the async proxy) and by the scale copies of the tile
+                __threadfence();
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                __syncwarp();
+            }
             requestTile(nTiles - 1u);
         }
         // all tiles of this block are requested: the next call's rows follow them into L2 (requested
