@@ -159,28 +159,38 @@ __device__ __forceinline__ bool barOr(uint32_t id, uint32_t threads, bool pred) 
 }
 __device__ __forceinline__ float i2f(uint32_t x) { return __int2float_rn(static_cast<int>(x)); }
 
-// One instance of the IEEE division for the cold code below.
-__device__ __noinline__ float ieeeDiv(float a, float b) { return __fdiv_rn(a, b); }
-
 // The new token's K and V row of one kv head into the int8 pool, by one warp (the arithmetic of
 // kvQuantKernel: amax / 127, IEEE divide, round-half-even; lane i owns dims 4 i .. 4 i + 3 of the 128).
-// Blocks that share the kv head write the same bytes.  Out of line and small: it runs once per launch
-// and kv head.  src: the row's 32 float4; dst: row x nKV + kv head of the pool.
-__device__ __noinline__ void appendNewRow(const float4 *src, uint32_t *pool8, float *scales, uint64_t dst,
-                                          uint32_t lane) {
-    const float4 x = __ldg(src + lane);
-    float m = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+// Blocks that share the kv head write the same bytes.  Both rows are loaded at once (they were pulled
+// towards L2 when the block started); the block's own TMA load and scale copies read the row back, so
+// the stores are ordered before the async proxy and nothing wider.  srcK / srcV: the rows' 32 float4;
+// dst: row x nKV + kv head of the pool.
+__device__ __forceinline__ void appendNewRow(const float4 *srcK, const float4 *srcV, uint32_t *k8w, uint32_t *v8w,
+                                             float *ksw, float *vsw, uint64_t dst, uint32_t lane) {
+    const float4 kx = __ldg(srcK + lane);
+    const float4 vx = __ldg(srcV + lane);
+    float mk = fmaxf(fmaxf(fabsf(kx.x), fabsf(kx.y)), fmaxf(fabsf(kx.z), fabsf(kx.w)));
+    float mv = fmaxf(fmaxf(fabsf(vx.x), fabsf(vx.y)), fmaxf(fabsf(vx.z), fabsf(vx.w)));
 #pragma unroll
-    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const float sc = m > 0.0f ? ieeeDiv(m, 127.0f) : 1.0f;
-    if (lane == 0) scales[dst] = sc;
-    auto q8 = [](float q) -> uint32_t {
-        int qv = __float2int_rn(q);
+    for (int o = 16; o; o >>= 1) {
+        mk = fmaxf(mk, __shfl_xor_sync(0xffffffffu, mk, o));
+        mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, o));
+    }
+    const float sk = mk > 0.0f ? __fdiv_rn(mk, 127.0f) : 1.0f;
+    const float sv = mv > 0.0f ? __fdiv_rn(mv, 127.0f) : 1.0f;
+    if (lane == 0) {
+        ksw[dst] = sk;
+        vsw[dst] = sv;
+    }
+    auto q8 = [](float x, float sc) -> uint32_t {
+        int qv = __float2int_rn(__fdiv_rn(x, sc));
         qv = qv < -128 ? -128 : (qv > 127 ? 127 : qv);
         return static_cast<uint32_t>(qv) & 0xffu;
     };
-    pool8[dst * 32u + lane] = q8(ieeeDiv(x.x, sc)) | (q8(ieeeDiv(x.y, sc)) << 8) | (q8(ieeeDiv(x.z, sc)) << 16) |
-                              (q8(ieeeDiv(x.w, sc)) << 24);
+    k8w[dst * 32u + lane] = q8(kx.x, sk) | (q8(kx.y, sk) << 8) | (q8(kx.z, sk) << 16) | (q8(kx.w, sk) << 24);
+    v8w[dst * 32u + lane] = q8(vx.x, sv) | (q8(vx.y, sv) << 8) | (q8(vx.z, sv) << 16) | (q8(vx.w, sv) << 24);
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+    __syncwarp();
 }
 
 // APPEND: the instantiation for calls that hand in the new token's rows.  It is a kernel of its own
@@ -268,6 +278,12 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 }
             }
         };
+        if (APPEND && p.appendK != nullptr && t1 == len && lane < 8u) {
+            // the rows this block will append, towards L2 (their final contents arrive there too)
+            const char *src = reinterpret_cast<const char *>((lane < 4u ? p.appendK : p.appendV) +
+                                                             (static_cast<size_t>(b) * p.nKV + kvHead) * 128u) + (lane & 3u) * 128u;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+        }
         bool waited = !earlyOk;
         auto requestTile = [&](uint32_t it) -> bool {
             const uint32_t s = it % NS;
@@ -323,14 +339,10 @@ decodeI8TcKernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             if (rowBase + len - 1u >= p.totalRows) {
                 if (lane == 0) atomicOr(p.err, kDevErrRowBound);
             } else {
-                appendNewRow(reinterpret_cast<const float4 *>(p.appendK) + srcRow, reinterpret_cast<uint32_t *>(p.k8w),
-                             const_cast<float *>(p.ks), dst, lane);
-                appendNewRow(reinterpret_cast<const float4 *>(p.appendV) + srcRow, reinterpret_cast<uint32_t *>(p.v8w),
-                             const_cast<float *>(p.vs), dst, lane);
-                // the row is read back by TMA (the async proxy) and by the scale copies of the tile
-                __threadfence();
-                asm volatile("fence.proxy.async.global;" ::: "memory");
-                __syncwarp();
+                appendNewRow(reinterpret_cast<const float4 *>(p.appendK) + srcRow,
+                             reinterpret_cast<const float4 *>(p.appendV) + srcRow, reinterpret_cast<uint32_t *>(p.k8w),
+                             reinterpret_cast<uint32_t *>(p.v8w), const_cast<float *>(p.ks), const_cast<float *>(p.vs), dst,
+                             lane);
             }
             requestTile(nTiles - 1u);
         }
