@@ -80,6 +80,7 @@ f32ToF16MirrorKernel(const float4 *__restrict__ q, const float4 *__restrict__ k,
                      unsigned int *__restrict__ workCounter) {
     // the attention launch that follows in the stream hands out its work items through this counter
     if (blockIdx.x == 0 && threadIdx.x == 0) *workCounter = 0u;
+    gridDepLaunch();  // the attention launch may set itself up while this one drains
     const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t i = tid; i < nq4; i += stride) {
@@ -322,6 +323,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // ------------------------ TMA producer and scheduler ------------------------
         if (lane == 0) {
             uint32_t item = blockIdx.x, g = 0;  // g: K/V tiles requested so far, over all items
+            gridDepWait();  // the twins and the work counter come from the launch in front
             itemSlots[0] = item;
             mbarArrive(&itemFull[0]);
             bool ok = true;
@@ -775,11 +777,22 @@ static int prefillF16Impl(const float *q, const tc::PrefillKvSource &src, float 
         attrDone[dev] = true;
     }
     const uint32_t grid = std::min<uint32_t>(prm.totalItems, static_cast<uint32_t>(sms));  // one block per SM
+    // programmatic dependent launch: the blocks allocate TMEM and set up their barriers while the twins
+    // launch drains; the producer waits for it before its first load (nothing else reads its outputs)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kPfThreads);
+    cfg.dynamicSmemBytes = hd == 64 ? PrefillF16Smem<64>::kTotal : PrefillF16Smem<128>::kTotal;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     if (hd == 64)
-        prefillF16Kernel<64><<<grid, kPfThreads, PrefillF16Smem<64>::kTotal, st>>>(tmQ, tmK, tmV, prm);
+        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, prefillF16Kernel<64>, tmQ, tmK, tmV, prm));
     else
-        prefillF16Kernel<128><<<grid, kPfThreads, PrefillF16Smem<128>::kTotal, st>>>(tmQ, tmK, tmV, prm);
-    TC_CUDA_OK(cudaGetLastError());
+        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, prefillF16Kernel<128>, tmQ, tmK, tmV, prm));
     return TC_OK;
 }
 
