@@ -137,6 +137,31 @@ def test_fp16_store_and_int8_store_as_the_kv_source(hd, nH, nKV, total, c0):
     assert_close(host(out), want, rtol=RTOL16, atol=ATOL16, what=f"int8 store, hd {hd}, rows {c0}..{total}")
 
 
+def test_many_work_items_per_block():
+    """12288 rows x 28 heads = 1344 work items for the persistent blocks (nine and more per block: the
+    item slots and every ring index wrap several times); a row sample against the oracle."""
+    from concurrent.futures import ThreadPoolExecutor
+    S, nH, nKV, hd = 12288, 28, 4, 128
+    inv = 1.0 / math.sqrt(hd)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(12288)
+    q = torch.randn((S, nH, hd), device="cuda", generator=g)
+    k = torch.randn((S, nKV, hd), device="cuda", generator=g)
+    v = torch.randn((S, nKV, hd), device="cuda", generator=g)
+    out = torch.full((S, nH, hd), float("nan"), device="cuda")
+    ops.prefill_f16(q, k, v, out, _scratch(S, nH, nKV, 0), S, nH, nKV, hd, invSqrt=inv)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    got = host(out)
+    assert np.isfinite(got).all()
+    rows = sorted(set(range(5, S, 1024)) | {0, 127, 128, 255, 256, 6143, 6144, S - 257, S - 129, S - 128, S - 1})
+    hq, hk, hv = host(q), host(k), host(v)
+    parts = np.array_split(np.array(rows, np.uint32), 8)
+    with ThreadPoolExecutor(8) as ex:
+        want = np.concatenate(list(ex.map(lambda r: oracle.prefill_f16_rows(hq, hk, hv, r, S, nH, nKV, hd, inv), parts)))
+    assert_close(got[rows], want, rtol=RTOL16, atol=ATOL16, what="12288 rows, row sample")
+
+
 def test_long_rows_and_peaked_scores():
     # 1536 rows: 12 query tiles, lazy rescale exercised by scores with a wide range
     q, k, v, got, inv = _run(1536, 4, 2, seed=5, scale=6.0)
