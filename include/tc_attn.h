@@ -332,8 +332,8 @@ int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t cachePos,
  * include/gpu/GpuAttentionKernels.hpp:323-353): causal attention of seqLen
  * query rows at positions cachePos .. cachePos + seqLen - 1 over cache rows
  * [0, cachePos + seqLen), fp16 operands, f32 accumulation, f32 softmax,
- * probabilities rounded to fp16.  head_dim 64 or 128 (TC_EUNSUPPORTED otherwise:
- * tc_attn_prefill_kv takes those shapes).  q f32 [seqLen][nHeads][hd]; kvK/kvV the f32
+ * probabilities rounded to fp16.  head_dim 64, 128 or 256 (TC_EUNSUPPORTED
+ * otherwise: tc_attn_prefill_kv takes those shapes).  q f32 [seqLen][nHeads][hd]; kvK/kvV the f32
  * cache from row 0 (the new rows already appended); out f32.  No seqLen cap
  * (the reference stops at 512 because it materialises the score matrix), and
  * no cachePos == 0 condition: the reference takes this path only for the

@@ -138,7 +138,7 @@ def test_dense_rotation_in_the_store_and_tensor_core_prefill():
     _check(*e.forward(4), "rope continued rows (tensor-core prefill over the existing cache)", tol=(2e-2, 2e-3))
 
 
-@pytest.mark.parametrize("hd", [128, 64])
+@pytest.mark.parametrize("hd", [128, 64, 256])
 def test_chunked_prompt_stays_on_the_tensor_core_prefill(hd):
     """With scratch for the whole window every chunk of a prompt -- not only the first, as in the
     reference (GPUComputeForward.cu:3828-3835) -- takes the fp16 tensor-core prefill."""

@@ -54,6 +54,35 @@ def test_head_dim_64(S, nH, nKV):
     assert_close(got, want, rtol=RTOL16, atol=ATOL16, what=f"prefill_f16 hd 64 S={S} nH={nH}")
 
 
+@pytest.mark.parametrize("S,nH,nKV", [(128, 1, 1), (300, 8, 2), (1, 4, 4), (129, 6, 1), (1100, 4, 2)])
+def test_head_dim_256(S, nH, nKV):
+    # the gated models' shape: one query tile per block, 32-token KV tiles, a 256-column accumulator
+    q, k, v, got, inv = _run(S, nH, nKV, seed=256 + S + nH, hd=256)
+    want = oracle.prefill_f16(q, k, v, S, nH, nKV, 256, inv)
+    assert_close(got, want, rtol=RTOL16, atol=ATOL16, what=f"prefill_f16 hd 256 S={S} nH={nH}")
+
+
+def test_head_dim_256_peaked_scores_continued_rows_and_mirror():
+    hd, nH, nKV = 256, 4, 2
+    q, k, v, got, inv = _run(700, nH, nKV, seed=12, scale=6.0, hd=hd)
+    q16, k16, v16 = (x.astype(np.float16) for x in (q, k, v))
+    exact = oracle.attention_f64(q16.astype(np.float32), k16, v16, None, None, 700, nH, nKV, hd, 0, inv)
+    assert_close(got, exact, rtol=RTOL16, atol=ATOL16, what="hd 256, peaked scores")
+    out = torch.full((250, nH, hd), float("nan"), device="cuda")
+    sc = _scratch(250, nH, nKV, 450, hd=hd)
+    k8 = torch.zeros((716, nKV, hd), dtype=torch.int8, device="cuda")
+    v8 = torch.zeros_like(k8)
+    ks = torch.zeros((716, nKV), device="cuda")
+    vs = torch.zeros_like(ks)
+    ops.prefill_f16(dev(q[450:]), dev(k), dev(v), out, sc, 250, nH, nKV, hd, invSqrt=inv, cachePos=450, kv8=(k8, v8, ks, vs))
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(host(out), got[450:], rtol=RTOL16, atol=ATOL16, what="hd 256: continued rows against the single call")
+    w8 = oracle.quant_kv8(k[450:], v[450:], nKV, hd)
+    for got8, want8, name in zip((k8, v8, ks, vs), w8, ("k8", "v8", "ks", "vs")):
+        assert np.array_equal(host(got8[450:700]), want8), f"hd 256 mirror {name}"
+
+
 def test_head_dim_64_peaked_scores_and_continued_rows():
     q, k, v, got, inv = _run(900, 4, 2, seed=11, scale=6.0, hd=64)
     q16, k16, v16 = (x.astype(np.float16) for x in (q, k, v))
@@ -135,6 +164,28 @@ def test_fp16_store_and_int8_store_as_the_kv_source(hd, nH, nKV, total, c0):
     assert ops.device_status() == 0
     want = oracle.attention_i8(q, k8, v8, ks, vs, S, nH, nKV, hd, c0, inv)
     assert_close(host(out), want, rtol=RTOL16, atol=ATOL16, what=f"int8 store, hd {hd}, rows {c0}..{total}")
+
+
+@pytest.mark.parametrize("S,nH,nKV,hd", [(1024, 28, 4, 128), (2048, 16, 2, 256), (900, 40, 8, 64)])
+def test_one_tile_items_with_several_items_per_block(S, nH, nKV, hd):
+    """Calls cut into one-tile work items (too few two-tile items for every SM; always at head_dim
+    256) with more items than blocks: tile B is absent in consecutive items of a block, and its warps
+    must not run a phase ahead of the producer.  A row sample against the oracle."""
+    inv = 1.0 / math.sqrt(hd)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(S + hd)
+    q = torch.randn((S, nH, hd), device="cuda", generator=g)
+    k = torch.randn((S, nKV, hd), device="cuda", generator=g)
+    v = torch.randn((S, nKV, hd), device="cuda", generator=g)
+    out = torch.full((S, nH, hd), float("nan"), device="cuda")
+    ops.prefill_f16(q, k, v, out, _scratch(S, nH, nKV, 0, hd=hd), S, nH, nKV, hd, invSqrt=inv)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    got = host(out)
+    assert np.isfinite(got).all()
+    rows = np.array(sorted(set(range(0, S, 61)) | {127, 128, S - 129, S - 128, S - 1}), np.uint32)
+    want = oracle.prefill_f16_rows(host(q), host(k), host(v), rows, S, nH, nKV, hd, inv)
+    assert_close(got[rows], want, rtol=RTOL16, atol=ATOL16, what=f"one-tile items, S={S} hd={hd}")
 
 
 def test_many_work_items_per_block():

@@ -203,7 +203,7 @@ uint64_t tc_context_overhead_bytes(uint32_t nHeads, uint32_t nKV, uint32_t hd, u
         if (tc_attn_exchange_bytes(static_cast<uint32_t>(qLocal), hd, ctxParts, &ex) == TC_OK) total += ex;
         total += qLocal * 64ull * (hd + 2ull) * 4ull;                    // the context split's own 64-slot partial block
     }
-    if (!kvStoreI8 && prefillChunk != 0 && (hd == 64 || hd == 128)) {
+    if (!kvStoreI8 && prefillChunk != 0 && (hd == 64 || hd == 128 || hd == 256)) {
         size_t tw = 0;                                                   // fp16 twins: q of a chunk, K/V of the GPU's rows
         const uint32_t chunk = prefillChunk < rows ? prefillChunk : static_cast<uint32_t>(rows);
         if (tc_attn_prefill_f16_scratch_bytes(chunk, static_cast<uint32_t>(rows) - chunk, static_cast<uint32_t>(qLocal),

@@ -188,7 +188,7 @@ int tc_kv_session_attend(tc_kv_session *s, uint32_t slot, float *q, const float 
         if (rc != TC_OK) return rc;
         s->rows8[slot] = pos + seqLen;
         // a multi-row call with scratch for the twins (bytes x row scale) takes the tensor-core prefill
-        if (seqLen > 1 && devPos == nullptr && !graphCapture && (hd == 64 || hd == 128) && c.prefillScratch != nullptr) {
+        if (seqLen > 1 && devPos == nullptr && !graphCapture && (hd == 64 || hd == 128 || hd == 256) && c.prefillScratch != nullptr) {
             size_t need = 0;
             if (tc_attn_prefill_f16_scratch_bytes(seqLen, pos, nH, nKV, hd, &need) == TC_OK && need <= c.prefillScratchBytes)
                 return tc_attn_prefill_f16_i8(q, k8, v8, ks, vs, attnOut, c.prefillScratch, c.prefillScratchBytes, seqLen,
@@ -218,14 +218,14 @@ int tc_kv_session_attend(tc_kv_session *s, uint32_t slot, float *q, const float 
     // every multi-row call on the f32 cache -- the first chunk of a prompt and the chunks behind it
     // (ModelForward.cpp:115-127 cuts prompts into 512-token calls) -- takes the tensor-core prefill
     // when the caller's scratch holds the fp16 twins of the rows it attends over
-    if (devPos == nullptr && !graphCapture && c.kvHalf && (hd == 64 || hd == 128) && c.prefillScratch != nullptr) {
+    if (devPos == nullptr && !graphCapture && c.kvHalf && (hd == 64 || hd == 128 || hd == 256) && c.prefillScratch != nullptr) {
         // the fp16 store is read in place: the scratch only has to hold q's twin
         size_t need = 0;
         if (tc_attn_prefill_f16_scratch_bytes(seqLen, 0, nH, 0, hd, &need) == TC_OK && need <= c.prefillScratchBytes)
             return tc_attn_prefill_f16_kvhalf(q, kvK, kvV, attnOut, c.prefillScratch, c.prefillScratchBytes, seqLen, pos,
                                               nH, nKV, hd, s->invSqrt, stream);
     }
-    if (devPos == nullptr && !graphCapture && !c.kvHalf && (hd == 64 || hd == 128) && c.prefillScratch != nullptr) {
+    if (devPos == nullptr && !graphCapture && !c.kvHalf && (hd == 64 || hd == 128 || hd == 256) && c.prefillScratch != nullptr) {
         size_t need = 0;
         if (tc_attn_prefill_f16_scratch_bytes(seqLen, pos, nH, nKV, hd, &need) == TC_OK && need <= c.prefillScratchBytes) {
             // With a decode pool that is current up to this call's first row, the launch that makes

@@ -42,7 +42,6 @@
 namespace tc {
 
 constexpr int kPfBM = 128;    // query rows per tile (two tiles per CTA)
-constexpr int kPfBN = 64;     // tokens per KV tile
 constexpr int kPfStages = 4;  // K and V ring depth
 constexpr float kPfLazyLog2 = 8.0f;
 
@@ -68,9 +67,11 @@ struct PrefillKvSource {
 // GpuElementwiseKernels.hpp:92-101; GPUComputeForward.cu:3957-3968), and -- the K/V rows being in
 // registers anyway -- the int8 rows of the new positions (one scale per row and kv head, amax / 127,
 // round-half-even: the arithmetic of kvQuantKernel, bit for bit).  q goes float4 by float4; a K/V
-// row of one kv head goes to a warp, lane i holding dims 4 i .. 4 i + 3 (head_dim <= 128).
+// row of one kv head goes to a warp, lane i holding dims 4 i .. 4 i + 3 (and 128 further on at head_dim 256).
 // With an int8 source (k8 != nullptr) the K/V rows are bytes and a scale per row and kv head instead of
 // floats, and there is no mirror to write.
+// MAXV: float4 per lane and row, 1 up to head_dim 128, 2 at 256.
+template <int MAXV>
 __global__ void __launch_bounds__(256)
 f32ToF16MirrorKernel(const float4 *__restrict__ q, const float4 *__restrict__ k, const float4 *__restrict__ v,
                      const uint32_t *__restrict__ k8, const uint32_t *__restrict__ v8, const float *__restrict__ ks8,
@@ -91,27 +92,33 @@ f32ToF16MirrorKernel(const float4 *__restrict__ q, const float4 *__restrict__ k,
         q16[i] = o;
     }
     const uint32_t lane = threadIdx.x & 31u;
-    const bool active = lane < nvec;
     for (size_t rh = tid >> 5; rh < kvRowHeads; rh += stride >> 5) {
-        float4 kx = make_float4(0.f, 0.f, 0.f, 0.f), vx = kx;
-        if (active) {
+        // lane i holds float4 i and, at head_dim 256, float4 i + 32 of the row
+        float4 kx[MAXV], vx[MAXV];
+        bool active[MAXV];
+#pragma unroll
+        for (int u = 0; u < MAXV; ++u) {
+            const uint32_t i4 = lane + 32u * u;
+            active[u] = i4 < nvec;
+            kx[u] = make_float4(0.f, 0.f, 0.f, 0.f), vx[u] = kx[u];
+            if (!active[u]) continue;
             if (k8 != nullptr) {
-                const uint32_t kb = __ldg(k8 + rh * nvec + lane), vb = __ldg(v8 + rh * nvec + lane);
+                const uint32_t kb = __ldg(k8 + rh * nvec + i4), vb = __ldg(v8 + rh * nvec + i4);
                 const float sk = __ldg(ks8 + rh), sv = __ldg(vs8 + rh);
                 auto b = [](uint32_t w, int i) { return static_cast<float>(static_cast<int8_t>((w >> (8 * i)) & 0xffu)); };
-                kx = make_float4(b(kb, 0) * sk, b(kb, 1) * sk, b(kb, 2) * sk, b(kb, 3) * sk);
-                vx = make_float4(b(vb, 0) * sv, b(vb, 1) * sv, b(vb, 2) * sv, b(vb, 3) * sv);
+                kx[u] = make_float4(b(kb, 0) * sk, b(kb, 1) * sk, b(kb, 2) * sk, b(kb, 3) * sk);
+                vx[u] = make_float4(b(vb, 0) * sv, b(vb, 1) * sv, b(vb, 2) * sv, b(vb, 3) * sv);
             } else {
-                kx = __ldg(k + rh * nvec + lane);
-                vx = __ldg(v + rh * nvec + lane);
+                kx[u] = __ldg(k + rh * nvec + i4);
+                vx[u] = __ldg(v + rh * nvec + i4);
             }
             uint2 o;
-            o.x = packHalf2(kx.x, kx.y);
-            o.y = packHalf2(kx.z, kx.w);
-            k16[rh * nvec + lane] = o;
-            o.x = packHalf2(vx.x, vx.y);
-            o.y = packHalf2(vx.z, vx.w);
-            v16[rh * nvec + lane] = o;
+            o.x = packHalf2(kx[u].x, kx[u].y);
+            o.y = packHalf2(kx[u].z, kx[u].w);
+            k16[rh * nvec + i4] = o;
+            o.x = packHalf2(vx[u].x, vx[u].y);
+            o.y = packHalf2(vx[u].z, vx[u].w);
+            v16[rh * nvec + i4] = o;
         }
         if (mir.k8 == nullptr || rh < mirrorFrom) continue;  // warp-uniform
         const size_t dst = mir.dstRow * nKV + (rh - mirrorFrom);
@@ -119,8 +126,9 @@ f32ToF16MirrorKernel(const float4 *__restrict__ q, const float4 *__restrict__ k,
             if (lane == 0) atomicOr(err, kDevErrRowBound);
             continue;
         }
-        float mk = fmaxf(fmaxf(fabsf(kx.x), fabsf(kx.y)), fmaxf(fabsf(kx.z), fabsf(kx.w)));
-        float mv = fmaxf(fmaxf(fabsf(vx.x), fabsf(vx.y)), fmaxf(fabsf(vx.z), fabsf(vx.w)));
+        auto amax4 = [](const float4 &x) { return fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))); };
+        float mk = amax4(kx[0]), mv = amax4(vx[0]);
+        if (MAXV > 1) mk = fmaxf(mk, amax4(kx[MAXV - 1])), mv = fmaxf(mv, amax4(vx[MAXV - 1]));
 #pragma unroll
         for (int o = 16; o; o >>= 1) {
             mk = fmaxf(mk, __shfl_xor_sync(0xffffffffu, mk, o));
@@ -137,11 +145,14 @@ f32ToF16MirrorKernel(const float4 *__restrict__ q, const float4 *__restrict__ k,
             qv = qv < -128 ? -128 : (qv > 127 ? 127 : qv);
             return static_cast<uint32_t>(qv) & 0xffu;
         };
-        if (active) {
-            reinterpret_cast<uint32_t *>(mir.k8)[dst * nvec + lane] =
-                    q8(kx.x, sk) | (q8(kx.y, sk) << 8) | (q8(kx.z, sk) << 16) | (q8(kx.w, sk) << 24);
-            reinterpret_cast<uint32_t *>(mir.v8)[dst * nvec + lane] =
-                    q8(vx.x, sv) | (q8(vx.y, sv) << 8) | (q8(vx.z, sv) << 16) | (q8(vx.w, sv) << 24);
+#pragma unroll
+        for (int u = 0; u < MAXV; ++u) {
+            if (!active[u]) continue;
+            const uint32_t i4 = lane + 32u * u;
+            reinterpret_cast<uint32_t *>(mir.k8)[dst * nvec + i4] =
+                    q8(kx[u].x, sk) | (q8(kx[u].y, sk) << 8) | (q8(kx[u].z, sk) << 16) | (q8(kx[u].w, sk) << 24);
+            reinterpret_cast<uint32_t *>(mir.v8)[dst * nvec + i4] =
+                    q8(vx[u].x, sv) | (q8(vx[u].y, sv) << 8) | (q8(vx[u].z, sv) << 16) | (q8(vx[u].w, sv) << 24);
         }
     }
 }
@@ -176,16 +187,19 @@ __device__ __forceinline__ unsigned long long pfTime() {
 #define PF_BLK(k) do { } while (0)
 #endif
 
-// HD = head_dim, 64 or 128: a tile is HD / 64 halves of 64 columns (128 bytes, one swizzle span) each
-template <int HD>
+// HD = head_dim (64, 128 or 256): a tile is HD / 64 halves of 64 columns (128 bytes, one swizzle span)
+// each.  BN = tokens per KV tile: 64, or 32 at head_dim 256, where one query tile and its 256-column
+// accumulator take the room two tiles take at head_dim 128 (a block then serves one query tile).
+template <int HD, int BN>
 struct PrefillF16Smem {
     static constexpr int kHalves = HD / 64;
+    static constexpr int kQTiles = HD > 128 ? 1 : 2;   // query tiles a block holds
     static constexpr int kQHalf = kPfBM * 128;         // 16 KB: 128 rows x 64 fp16
-    static constexpr int kKvHalf = kPfBN * 128;        // 8 KB: 64 rows x 64 fp16
+    static constexpr int kKvHalf = BN * 128;           // BN rows x 64 fp16
     static constexpr int kQTile = kHalves * kQHalf;    // head_dim 128: 32 KB
     static constexpr int kKvTile = kHalves * kKvHalf;  // head_dim 128: 16 KB
     static constexpr int kQ = 0;                       // two query tiles
-    static constexpr int kK01 = 2 * kQTile;            // K_0, K_1 (the products issued before the loop)
+    static constexpr int kK01 = kQTiles * kQTile;      // K_0, K_1 (the products issued before the loop)
     static constexpr int kStage = kK01 + 2 * kKvTile;  // stage s: K slot, then V slot
     static constexpr int kStageBytes = 2 * kKvTile;
     static constexpr int kBars = kStage + kPfStages * kStageBytes;
@@ -237,6 +251,7 @@ __device__ __forceinline__ uint64_t descAdvance(uint64_t d, uint32_t bytes) { re
 struct PfItem {
     uint32_t head, kvHead, m0, nA, nB, nTiles;
 };
+template <int BN>
 __device__ __forceinline__ PfItem pfItem(const PrefillF16Params &p, uint32_t item) {
     PfItem it;
     const uint32_t qb = p.nQTiles - 1u - item / p.nHeads;  // heavy query blocks (long causal prefixes) first
@@ -244,8 +259,8 @@ __device__ __forceinline__ PfItem pfItem(const PrefillF16Params &p, uint32_t ite
     it.kvHead = it.head / p.group;
     it.m0 = qb * p.itemRows;
     const bool activeB = p.itemRows > kPfBM && it.m0 + kPfBM < p.seqLen;
-    it.nA = (p.cachePos + it.m0 + kPfBM + kPfBN - 1u) / kPfBN;
-    it.nB = activeB ? (p.cachePos + it.m0 + 2u * kPfBM + kPfBN - 1u) / kPfBN : 0u;
+    it.nA = (p.cachePos + it.m0 + kPfBM + BN - 1u) / BN;
+    it.nB = activeB ? (p.cachePos + it.m0 + 2u * kPfBM + BN - 1u) / BN : 0u;
     it.nTiles = activeB ? it.nB : it.nA;
     return it;
 }
@@ -262,11 +277,12 @@ __device__ __forceinline__ PfItem pfItem(const PrefillF16Params &p, uint32_t ite
 // product has been issued, its first scores are in TMEM while the softmax threads still write this
 // item's output, and tile A moves on while tile B finishes its two extra diagonal tiles.
 constexpr int kPfThreads = 416;
-template <int HD>
+template <int HD, int BN>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const PrefillF16Params p) {
-    using L = PrefillF16Smem<HD>;
+    using L = PrefillF16Smem<HD, BN>;
+    constexpr int NC = BN / 32;  // 32-column chunks of a score row
     constexpr uint32_t NS = kPfStages;
     extern __shared__ uint8_t smemRaw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
@@ -328,7 +344,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             mbarArrive(&itemFull[0]);
             bool ok = true;
             for (uint32_t n = 0; ok && item < p.totalItems; ++n) {
-                const PfItem it = pfItem(p, item);
+                const PfItem it = pfItem<BN>(p, item);
                 PF_BLK(0);
 #ifdef TC_TRACE
                 if (p.trace) { unsigned sm; asm("mov.u32 %0, %%smid;" : "=r"(sm)); p.trace[8u * 64u * 4u + item * 8u + 6] = sm; }
@@ -340,9 +356,9 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     ok = false;
                     break;
                 }
-                mbarExpectTx(qFull, 2 * L::kQTile);
+                mbarExpectTx(qFull, L::kQTiles * L::kQTile);
 #pragma unroll
-                for (int x = 0; x < 2; ++x)
+                for (int x = 0; x < L::kQTiles; ++x)
 #pragma unroll
                     for (int h = 0; h < L::kHalves; ++h)
                         tmaLoad3D(smem + L::kQ + x * L::kQTile + h * L::kQHalf, &tmQ, qFull, 64 * h, it.head,
@@ -354,7 +370,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     uint8_t *kd = smem + L::kK01 + j * L::kKvTile;
 #pragma unroll
                     for (int h = 0; h < L::kHalves; ++h)
-                        tmaLoad3D(kd + h * L::kKvHalf, &tmK, k01Full, 64 * h, it.kvHead, j * kPfBN);
+                        tmaLoad3D(kd + h * L::kKvHalf, &tmK, k01Full, 64 * h, it.kvHead, j * BN);
                 }
                 // The next item is drawn late -- with the third last tile request, some six tiles before
                 // the consumers finish this item -- so that the blocks which finish first take the
@@ -376,8 +392,8 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     mbarExpectTx(&stFull[s], withK ? 2 * L::kKvTile : L::kKvTile);
 #pragma unroll
                     for (int h = 0; h < L::kHalves; ++h) {
-                        if (withK) tmaLoad3D(kd + h * L::kKvHalf, &tmK, &stFull[s], 64 * h, it.kvHead, (j + 2) * kPfBN);
-                        tmaLoad3D(vd + h * L::kKvHalf, &tmV, &stFull[s], 64 * h, it.kvHead, j * kPfBN);
+                        if (withK) tmaLoad3D(kd + h * L::kKvHalf, &tmK, &stFull[s], 64 * h, it.kvHead, (j + 2) * BN);
+                        tmaLoad3D(vd + h * L::kKvHalf, &tmV, &stFull[s], 64 * h, it.kvHead, j * BN);
                     }
                 }
                 if (!ok) break;
@@ -407,7 +423,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t x = (warp - 9u) & 1u;
         const bool pvRole = warp >= 11u;
         const uint32_t issue = lane == 0 ? 1u : 0u;
-        constexpr uint32_t idQK = umaInstrDescF16(kPfBM, kPfBN, 0, 0);
+        constexpr uint32_t idQK = umaInstrDescF16(kPfBM, BN, 0, 0);
         constexpr uint32_t idPV = umaInstrDescF16(kPfBM, HD, 0, 1);
         const uint64_t dQ = umaSmemDesc(smemAddr(smem + L::kQ + x * L::kQTile), 16, 1024);
         const uint64_t dK01 = umaSmemDesc(smemAddr(smem + L::kK01), 16, 1024);
@@ -431,14 +447,14 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t g = 0, t = 0, item = 0;  // K/V tiles consumed, tiles of X done, over all items
         bool ok = true;
         for (uint32_t n = 0; ok && takeItem(n, item); ++n) {
-            const PfItem it = pfItem(p, item);
+            const PfItem it = pfItem<BN>(p, item);
             const uint32_t myTiles = x == 0 ? it.nA : it.nB;
             if (!pvRole) {
                 if (myTiles != 0) {
                     ok = pfWait(qFull, n & 1u, p.err, kDevErrFullWait) && pfWait(k01Full, n & 1u, p.err, kDevErrFullWait);
                     ok = ok && issueQK(dK01, t) && issueQK(descAdvance(dK01, L::kKvTile), t + 1u);
+                    if (myTiles <= 2u) umaCommitIf(issue, &qFree[x]);
                 }
-                if (myTiles <= 2u) umaCommitIf(issue, &qFree[x]);
             }
             // Every stage is released by all four warps, also the ones past a tile's diagonal -- but
             // only after the stage has been filled: a warp with nothing to do must not run ahead and
@@ -458,7 +474,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     const uint64_t dV = descAdvance(dVs, s * L::kStageBytes);
                     const uint32_t tP = tS0 + 64u * (tt & 1u);
 #pragma unroll
-                    for (uint32_t ks = 0; ks < 4; ++ks)  // 16 tokens per step: 8 columns of fp16 P, 2 KB of V
+                    for (uint32_t ks = 0; ks < BN / 16; ++ks)  // 16 tokens per step: 8 columns of fp16 P, 2 KB of V
                         umaMmaTSIf(issue, tO, tP + ks * 8u, descAdvance(dV, ks * 2048u), idPV, (j > 0 || ks > 0) ? 1u : 0u);
                     umaCommitIf(issue, &pvDone[x]);
                     umaCommitIf(issue, &pvBuf[2u * x + (tt & 1u)]);
@@ -473,6 +489,11 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
                 umaCommitIf(issue, &stEmpty[s]);
             }
+            // A tile that is not there still hands in its phase of qFree, one per item -- but only
+            // behind the item's last stage: the producer fills that stage after it has looked at the
+            // previous phase, so this warp cannot complete two phases before the producer has seen
+            // the first (a parity wait cannot tell those apart).
+            if (!pvRole && myTiles == 0u && ok) umaCommitIf(issue, &qFree[x]);
             t += myTiles;
         }
         if (pvRole && ok) {
@@ -490,7 +511,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t t = 0, item = 0;  // tiles of X done over all items
         bool ok = true;
         for (uint32_t n = 0; ok && takeItem(n, item); ++n) {
-            const PfItem it = pfItem(p, item);
+            const PfItem it = pfItem<BN>(p, item);
             const uint32_t m0 = it.m0, head = it.head;
             const uint32_t rq = m0 + rowInBlock;  // query position
             const uint32_t myTiles = x == 0 ? it.nA : it.nB;
@@ -507,25 +528,25 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (row == 0) PF_STAMP(x, j, 1);
                 if (row == 0 && x == 0 && j == 0) PF_BLK(2);
                 tcFenceAfter();
-                uint32_t r[2][32];  // the 64 scores of this row
-                tmemLd32(tS + laneBase, r[0]);
-                tmemLd32(tS + laneBase + 32u, r[1]);
+                uint32_t r[NC][32];  // the BN scores of this row
+#pragma unroll
+                for (int c = 0; c < NC; ++c) tmemLd32(tS + laneBase + 32u * c, r[c]);
                 tmemLdWait();
                 if (row == 0 && x == 0) PF_STAMP(6u, j, 0);
-                if (64u * j + 63u > p.cachePos + m0 + x * kPfBM) {
+                if (BN * j + (BN - 1u) > p.cachePos + m0 + x * kPfBM) {
                     // causal edge (the tile reaches past the position of this tile's first row): token
                     // 64 j + c is visible iff it is not past the query position; relative to the block's
                     // first row that is 64 j - (cachePos + m0) + c <= rowInBlock
-                    const int32_t first = static_cast<int32_t>(64u * j) - static_cast<int32_t>(p.cachePos + m0);
+                    const int32_t first = static_cast<int32_t>(BN * j) - static_cast<int32_t>(p.cachePos + m0);
 #pragma unroll
-                    for (int c = 0; c < 2; ++c)
+                    for (int c = 0; c < NC; ++c)
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
                             if (first + c * 32 + i > static_cast<int32_t>(rowInBlock)) r[c][i] = 0xff800000u;  // -inf
                 }
                 float mxa = -INFINITY, mxb = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < 2; ++c)
+                for (int c = 0; c < NC; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
                         mxa = max3(mxa, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
@@ -576,7 +597,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const float2 scale2 = make_float2(p.scaleLog2, p.scaleLog2), negM2 = make_float2(-m, -m);
                 float psum = 0.0f;
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < NC; ++c) {
                     uint32_t h[16];
                     {
                         float2 sum2 = make_float2(0.0f, 0.0f);
@@ -678,7 +699,7 @@ extern "C" {
 int tc_attn_prefill_f16_scratch_bytes(uint32_t seqLen, uint32_t cachePos, uint32_t nHeads, uint32_t nKV, uint32_t hd,
                                       size_t *bytes) {
     TC_REQUIRE(bytes != nullptr, TC_EINVAL, "tc_attn_prefill_f16_scratch_bytes: null output");
-    TC_REQUIRE(hd == 64 || hd == 128, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 64 and 128)", hd);
+    TC_REQUIRE(hd == 64 || hd == 128 || hd == 256, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 64, 128 and 256)", hd);
     *bytes = tc::prefillScratchBytes(seqLen, cachePos, nHeads, nKV, hd);
     return TC_OK;
 }
@@ -690,7 +711,7 @@ static int prefillF16Impl(const float *q, const tc::PrefillKvSource &src, float 
     const void *kvK = src.k, *kvV = src.v;
     TC_REQUIRE(q && kvK && kvV && out && scratch, TC_EINVAL, "tc_attn_prefill_f16: null pointer");
     TC_REQUIRE(src.kind != 2 || (src.ks && src.vs), TC_EINVAL, "tc_attn_prefill_f16: null scale pointer");
-    TC_REQUIRE(hd == 64 || hd == 128, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 64 and 128)", hd);
+    TC_REQUIRE(hd == 64 || hd == 128 || hd == 256, TC_EUNSUPPORTED, "tc_attn_prefill_f16: head_dim %u (built for 64, 128 and 256)", hd);
     TC_REQUIRE(nKV > 0 && nHeads % nKV == 0, TC_EINVAL, "tc_attn_prefill_f16: nHeads %u not a multiple of nKV %u",
                nHeads, nKV);
     TC_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kvK) | reinterpret_cast<uintptr_t>(kvV) |
@@ -709,8 +730,12 @@ static int prefillF16Impl(const float *q, const tc::PrefillKvSource &src, float 
     const int sms = numSMs();
     // two query tiles per item keep both softmax warpgroups of a block busy; a call too short to give
     // every SM such an item (a 512-row chunk of a prompt: 2 x nHeads items) is cut into one-tile items
+    // (head_dim 256: a block holds one query tile, so its items are always one-tile items)
     const uint32_t itemRows =
-            static_cast<uint64_t>((seqLen + 2 * kPfBM - 1) / (2 * kPfBM)) * nHeads < static_cast<uint64_t>(sms) ? kPfBM : 2 * kPfBM;
+            hd == 256 || static_cast<uint64_t>((seqLen + 2 * kPfBM - 1) / (2 * kPfBM)) * nHeads < static_cast<uint64_t>(sms)
+                    ? kPfBM
+                    : 2 * kPfBM;
+    const uint32_t bn = hd == 256 ? 32u : 64u;  // tokens per KV tile
     const uint32_t nQTiles = (seqLen + itemRows - 1) / itemRows;
     TC_REQUIRE(static_cast<uint64_t>(nQTiles) * nHeads < (1ull << 31), TC_EUNSUPPORTED,
                "tc_attn_prefill_f16: grid too large");
@@ -734,7 +759,8 @@ static int prefillF16Impl(const float *q, const tc::PrefillKvSource &src, float 
         const size_t threads = std::max(nq4, kvRowHeads * 32);
         const uint32_t blocks = static_cast<uint32_t>(std::min<size_t>((threads + 255) / 256, static_cast<size_t>(sms) * 16));
         const bool i8 = src.kind == 2;
-        f32ToF16MirrorKernel<<<blocks, 256, 0, st>>>(
+        auto conv = hd > 128 ? f32ToF16MirrorKernel<2> : f32ToF16MirrorKernel<1>;
+        conv<<<blocks, 256, 0, st>>>(
                 reinterpret_cast<const float4 *>(q), i8 ? nullptr : static_cast<const float4 *>(kvK),
                 i8 ? nullptr : static_cast<const float4 *>(kvV), i8 ? static_cast<const uint32_t *>(kvK) : nullptr,
                 i8 ? static_cast<const uint32_t *>(kvV) : nullptr, src.ks, src.vs, static_cast<uint2 *>(q16),
@@ -745,9 +771,9 @@ static int prefillF16Impl(const float *q, const tc::PrefillKvSource &src, float 
     CUtensorMap tmQ, tmK, tmV;
     int rc = f16Map(q16, hd, nHeads, seqLen, kPfBM, &tmQ);
     if (rc != TC_OK) return rc;
-    rc = f16Map(k16, hd, nKV, kvRows, kPfBN, &tmK);
+    rc = f16Map(k16, hd, nKV, kvRows, bn, &tmK);
     if (rc != TC_OK) return rc;
-    rc = f16Map(v16, hd, nKV, kvRows, kPfBN, &tmV);
+    rc = f16Map(v16, hd, nKV, kvRows, bn, &tmV);
     if (rc != TC_OK) return rc;
     PrefillF16Params prm;
     prm.out = out;
@@ -770,10 +796,12 @@ static int prefillF16Impl(const float *q, const tc::PrefillKvSource &src, float 
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attrDone[dev]) {
-        TC_CUDA_OK(cudaFuncSetAttribute(prefillF16Kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        PrefillF16Smem<64>::kTotal));
-        TC_CUDA_OK(cudaFuncSetAttribute(prefillF16Kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        PrefillF16Smem<128>::kTotal));
+        TC_CUDA_OK(cudaFuncSetAttribute(prefillF16Kernel<64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        PrefillF16Smem<64, 64>::kTotal));
+        TC_CUDA_OK(cudaFuncSetAttribute(prefillF16Kernel<128, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        PrefillF16Smem<128, 64>::kTotal));
+        TC_CUDA_OK(cudaFuncSetAttribute(prefillF16Kernel<256, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        PrefillF16Smem<256, 32>::kTotal));
         attrDone[dev] = true;
     }
     const uint32_t grid = std::min<uint32_t>(prm.totalItems, static_cast<uint32_t>(sms));  // one block per SM
@@ -782,7 +810,8 @@ static int prefillF16Impl(const float *q, const tc::PrefillKvSource &src, float 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kPfThreads);
-    cfg.dynamicSmemBytes = hd == 64 ? PrefillF16Smem<64>::kTotal : PrefillF16Smem<128>::kTotal;
+    cfg.dynamicSmemBytes = hd == 64 ? PrefillF16Smem<64, 64>::kTotal
+                                    : (hd == 128 ? PrefillF16Smem<128, 64>::kTotal : PrefillF16Smem<256, 32>::kTotal);
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -790,9 +819,11 @@ static int prefillF16Impl(const float *q, const tc::PrefillKvSource &src, float 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (hd == 64)
-        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, prefillF16Kernel<64>, tmQ, tmK, tmV, prm));
+        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, prefillF16Kernel<64, 64>, tmQ, tmK, tmV, prm));
+    else if (hd == 128)
+        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, prefillF16Kernel<128, 64>, tmQ, tmK, tmV, prm));
     else
-        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, prefillF16Kernel<128>, tmQ, tmK, tmV, prm));
+        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, prefillF16Kernel<256, 32>, tmQ, tmK, tmV, prm));
     return TC_OK;
 }
 
