@@ -10,31 +10,36 @@
 // scores, probabilities rounded to fp16 -- but flash-style, so the score matrix
 // never exists and the sequence length is not capped at 512.
 //
-// One CTA = one q head x 256 query rows = two 128-row query tiles A and B; KV tiles of 64
-// tokens.  Warp roles:
-//   warps 0-3 / 4-7  softmax of tile A / B: thread r owns query row r, reads its 64 scores
-//              of a KV tile from TMEM (tcgen05.ld), keeps (m, l), writes the fp16
-//              probabilities over the first 32 columns of the same S buffer (tcgen05.st) as
-//              the A operand of the PV product, rescales O in TMEM only when the row maximum
-//              ran ahead by 2^8 (lazy rescale); packed f32x2 arithmetic;
-//   warp 8     TMA producer: both Q tiles and K_0, K_1 once, then a four-stage ring whose
-//              stage j holds what step j of the MMA warps consumes, K_{j+2} and V_j
-//              (cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA shared-memory
-//              layout, so no register pass touches the operands);
-//   warps 9, 10  MMA issuers of tile A / B: lane 0 issues tcgen05.mma -- S_X(j) = Q_X K_j^T
-//              (M128 N64 K16 x8), O_X += P_X(j) V_j (A from TMEM, B = V MN-major from shared
-//              memory, K16 x4) -- and tcgen05.commit onto mbarriers.  One warp per query tile:
-//              the waits and bookkeeping of one tile's step overlap the other tile's issue.
-// S is DOUBLE-BUFFERED per query tile: S_X(j+2) is issued right behind O_X += P_X(j) V_j into
-// the buffer that P_X(j) just left, so S_X(j+1) is already waiting when the softmax of tile j
-// finishes -- the softmax warps never wait for the tensor pipe, and the tensor pipe always has
-// the other buffer's and the other tile's products queued.  (With one S buffer per tile the
-// chain softmax -> PV -> QK^T -> softmax left both pipes idle about half of the time.)
-// Causality: a query tile only visits KV tiles up to its diagonal, the last two are masked
-// element-wise; heavy (late) query blocks are scheduled first.
-// TMEM (512 columns): O_A, O_B (128 each, f32), S_{A,0}, S_{A,1}, S_{B,0}, S_{B,1} (64 each).
-// Every wait is bounded; a wait that runs out records an error bit, the CTA drains and
-// frees its TMEM before it returns.
+// One persistent block per SM walks work items: a q head x 256 query rows = two 128-row query
+// tiles A and B (one tile per item for short calls and at head_dim 256), KV tiles of 64 tokens (32
+// at head_dim 256).  The first item of a block is its index, the following ones come from a
+// counter, heavy (late) query blocks first; the mbarriers are initialised once, every ring index
+// counts on from item to item, so the next item's loads and first score products run under the
+// current item's epilogue.  Warp roles:
+//   warps 0-3 / 4-7  softmax of tile A / B: thread r owns query row r, reads its scores of a KV
+//              tile from TMEM (tcgen05.ld), keeps (m, l), writes the fp16 probabilities over the
+//              first columns of the same S buffer (tcgen05.st) as the A operand of the PV product,
+//              rescales O in TMEM only when the row maximum ran ahead by 2^8 (lazy rescale);
+//              packed f32x2 arithmetic; normalises and stores the output rows (32-byte stores);
+//   warp 8     TMA producer and scheduler: the query tiles and K_0, K_1 per item, then a four-stage
+//              ring whose stage j holds what step j of the MMA warps consumes, K_{j+2} and V_j
+//              (cp.async.bulk.tensor, 128-byte swizzle = the canonical UMMA shared-memory layout,
+//              so no register pass touches the operands); draws the next item late in the current;
+//   warps 9, 10  issue the score products of tile A / B: S_X(t) = Q_X K^T (M128 N64 K16 per
+//              instruction), tcgen05.commit onto the softmax warps' barrier;
+//   warps 11, 12  issue the P.V products of tile A / B: O_X += P_X(t) V (A from TMEM, B = V
+//              MN-major from shared memory).  Issuing an instruction costs its thread about a
+//              hundred cycles and threads of different warps issue concurrently, hence four warps.
+// S is DOUBLE-BUFFERED per query tile: S_X(t+2) goes into the buffer P_X(t) leaves once its P.V
+// product is complete, so S_X(t+1) is there when the softmax of tile t finishes.  TMEM (512
+// columns): O_A, O_B (128 each, f32; one O of 256 at head_dim 256), S_{A,0}, S_{A,1}, S_{B,0},
+// S_{B,1} (64 each).  Causality: a query tile only visits KV tiles up to its diagonal, the last
+// two or three are masked element-wise; the query rows may sit behind an existing cache.
+// In front of the kernel one launch makes the fp16 twins of q, K and V (from the f32 store, or
+// from the int8 store's bytes and scales; an fp16 store is read in place) and, on request, the int8
+// pool rows of the call's new positions; the attention kernel is its programmatic dependent.
+// Every wait is bounded; a wait that runs out records an error bit, every other wait of the launch
+// then gives up at once, the block frees its TMEM and returns.
 #include <algorithm>
 
 #include "tc_tcgen05.cuh"
