@@ -188,6 +188,41 @@ def test_one_tile_items_with_several_items_per_block(S, nH, nKV, hd):
     assert_close(got[rows], want, rtol=RTOL16, atol=ATOL16, what=f"one-tile items, S={S} hd={hd}")
 
 
+def test_seeded_random_shapes():
+    """Forty seeded shapes -- head_dim 64 / 128 / 256, 1 to 40 q heads in groups of 1 to 8, 1 to 2600 query
+    rows behind 0 to 1500 cached rows, so one-tile and two-tile items, one to a dozen items per block,
+    tile B present, absent and ragged -- each against the oracle on a row sample."""
+    rng = np.random.default_rng(20261125)
+    for case in range(40):
+        hd = int(rng.choice([64, 128, 256]))
+        nKV = int(rng.choice([1, 2, 4, 8]))
+        group = int(rng.choice([1, 2, 3, 5, 7, 8]))
+        nH = nKV * group
+        if nH > 40:
+            nKV, nH = 4, 4 * group
+        S = int(rng.choice([1, 2, 127, 128, 129, 255, 256, 257, 300, 511, 640, 900, 1024, 1500, 2600]))
+        c0 = int(rng.choice([0, 0, 1, 63, 64, 200, 513, 1500]))
+        if (c0 + S) * nH > 60000:           # keep the oracle quick
+            c0 = 0
+            S = min(S, 60000 // nH)
+        inv = 1.0 / math.sqrt(hd)
+        g = torch.Generator(device="cuda")
+        g.manual_seed(1000 + case)
+        q = torch.randn((S, nH, hd), device="cuda", generator=g)
+        k = torch.randn((c0 + S, nKV, hd), device="cuda", generator=g)
+        v = torch.randn((c0 + S, nKV, hd), device="cuda", generator=g)
+        out = torch.full((S, nH, hd), float("nan"), device="cuda")
+        ops.prefill_f16(q, k, v, out, _scratch(S, nH, nKV, c0, hd=hd), S, nH, nKV, hd, invSqrt=inv, cachePos=c0)
+        torch.cuda.synchronize()
+        what = f"case {case}: S={S} cachePos={c0} nH={nH} nKV={nKV} hd={hd}"
+        assert ops.device_status(raise_on_flags=False) == 0, what
+        got = host(out)
+        assert np.isfinite(got).all(), what
+        rows = np.array(sorted(set(range(0, S, max(1, S // 12))) | {S - 1, min(S - 1, 127), min(S - 1, 128)}), np.uint32)
+        want = oracle.prefill_f16_rows(host(q), host(k), host(v), rows, S, nH, nKV, hd, inv, cachePos=c0)
+        assert_close(got[rows], want, rtol=RTOL16, atol=ATOL16, what=what)
+
+
 def test_many_work_items_per_block():
     """12288 rows x 28 heads = 1344 work items for the persistent blocks (nine and more per block: the
     item slots and every ring index wrap several times); a row sample against the oracle."""
