@@ -248,6 +248,54 @@ def test_new_row_past_the_pool_is_skipped_and_flagged():
         assert torch.equal(a, b_)
 
 
+def test_seeded_random_batches():
+    """Thirty seeded batches: 1 to 5 sequences of 1 to 6000 rows, 1 to 8 kv heads with 1 to 12 q heads
+    each (more than 8 take a second launch), head_dim 128 and 256, device or host lengths, chunk
+    slot counts from 1 up, the new rows appended by the launch or not -- each against the oracle."""
+    rng = np.random.default_rng(77)
+    for case in range(30):
+        hd = int(rng.choice([128, 128, 128, 256]))
+        nKV = int(rng.choice([1, 2, 4, 8]))
+        group = int(rng.choice([1, 2, 4, 5, 7, 8, 12]))
+        nH = nKV * group
+        B = int(rng.integers(1, 6))
+        dev_lens = bool(rng.integers(0, 2))
+        top = int(rng.choice([40, 300, 1500, 6000]))
+        lens = rng.integers(1, top + 1, B).astype(np.uint32) if dev_lens else np.full(B, int(rng.integers(1, top + 1)), np.uint32)
+        append = bool(rng.integers(0, 2))
+        numChunks = int(rng.choice([1, 3, 16, 64]))
+        rows_per_seq = int(lens.max()) + 16
+        inv = 1.0 / math.sqrt(hd)
+        q = rng.standard_normal((B, nH, hd), dtype=np.float32)
+        k8 = np.zeros((B, rows_per_seq, nKV, hd), np.int8)
+        v8 = np.zeros_like(k8)
+        ks = np.full((B, rows_per_seq, nKV), np.nan, np.float32)
+        vs = np.full_like(ks, np.nan)
+        newk = np.zeros((B, nKV, hd), np.float32)
+        newv = np.zeros_like(newk)
+        want = np.zeros((B, nH, hd), np.float32)
+        for b, n in enumerate(lens):
+            n = int(n)
+            k = rng.standard_normal((n, nKV, hd), dtype=np.float32)
+            v = rng.standard_normal((n, nKV, hd), dtype=np.float32)
+            a, c, d, e = oracle.quant_kv8(k, v, nKV, hd)
+            m = n - 1 if append else n                      # with append the last row is handed in as f32
+            k8[b, :m], v8[b, :m], ks[b, :m], vs[b, :m] = a[:m], c[:m], d[:m], e[:m]
+            newk[b], newv[b] = k[n - 1], v[n - 1]
+            want[b] = oracle.attention_i8(q[b:b + 1], a, c, d, e, 1, nH, nKV, hd, n - 1, inv)[0]
+        out = torch.full((B, nH, hd), float("nan"), device="cuda")
+        ws = ops.workspace(B, nH, hd, numChunks)
+        for w in ws:
+            w.fill_(float("nan"))
+        ops.decode_i8_batch(dev(q), dev(k8), dev(v8), dev(ks), dev(vs), out, ws, dev(lens) if dev_lens else None, B, nH,
+                            nKV, hd, int(lens.max()), numChunks, rows_per_seq=rows_per_seq, invSqrt=inv,
+                            append=(dev(newk), dev(newv)) if append else None)
+        torch.cuda.synchronize()
+        what = f"case {case}: lens={lens.tolist()} nH={nH} nKV={nKV} hd={hd} chunks={numChunks} append={append} dev_lens={dev_lens}"
+        assert ops.device_status(raise_on_flags=False) == 0, what
+        assert_close(host(out), want, what=what)
+
+
 def test_dependent_launch_chain_and_host_lengths():
     """Three 'layers' back to back with programmatic dependent launch (KV rows of a
     layer stream in while the previous layer's kernels drain) give the same
