@@ -326,11 +326,13 @@ int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    // In plain stream order the sliced form is faster (batch-1 decode step at ctx 32768: 13.7 us per
-    // layer against 15.0); under programmatic dependent launch its 4x as many blocks are resident next
-    // to the decode blocks they wait for and the step gets slower (13.5 against 13.0), so that path
-    // keeps the block-per-head form.
-    if (q81 == nullptr && !pdl) {
+    // The sliced form (a block per head and 32-dim slice) is the faster merge in plain stream order.
+    // Under programmatic dependent launch its blocks are resident next to the decode blocks they wait
+    // for: with one sequence that still wins (7B shape, 32768 rows: 11.7 us per layer against 12.5 with
+    // a block per head; 131072 rows of the 32B shape 48.1 against 49.2), with a batch of sequences the
+    // 4x as many blocks get in the way (batch 8: 49.4 against 46.1 us; 64 ragged sequences 201 against
+    // 190), so a batch keeps the block-per-head form there.
+    if (q81 == nullptr && (!pdl || static_cast<uint64_t>(nHeads) * seqLen <= 64u)) {
         cfg.gridDim = dim3(nHeads, seqLen, hd / 32u);
         TC_CUDA_OK(cudaLaunchKernelEx(&cfg, mergeSliceKernel, pAcc, pM, pL, out, nHeads, numChunks, activeHost, hd,
                                       devLens, lenAdd, chunkTokens, chunksPerRank, rankStride));
