@@ -192,21 +192,24 @@ mergePartialsKernel(const float *__restrict__ pAcc, const float *__restrict__ pM
     }
 }
 
-// The same merge cut into 32-dim slices: grid (head, token, hd / 32), so that the accumulator
-// rows a block has to pull through one SM's L2 port shrink from chunks x hd floats to
-// chunks x 32 (at 128 chunks x 128 dims that is 64 KB against 16 KB; the merge sits on the
-// critical path of a batch-1 decode step and is pure latency).  Thread t owns float4 t % 8 of
-// the slice and the chunks t / 8, t / 8 + 32, ...; (m, l) and the weights are recomputed by every
-// slice's block -- a few hundred bytes.  No Q8_1 epilogue here (that needs the whole head).
-__global__ void __launch_bounds__(256)
+// The same merge cut into slices of 4 SL4 dims: grid (head, token, hd / (4 SL4)), so that the
+// accumulator rows a block has to pull through one SM's L2 port shrink from chunks x hd floats to
+// chunks x 4 SL4 (at 128 chunks x 128 dims that is 64 KB against 16 KB with 32-dim slices; the merge
+// sits on the critical path of a batch-1 decode step and is pure latency).  Thread t owns float4
+// t % SL4 of the slice and the chunks t / SL4, t / SL4 + CL, ...; (m, l) and the weights are recomputed
+// by every slice's block -- a few hundred bytes.  No Q8_1 epilogue here (that needs the whole head).
+// SL4 = float4 per slice (8: 32-dim slices, 4: 16-dim slices); 256 / SL4 chunk lanes.
+template <int SL4, int T>
+__global__ void __launch_bounds__(T)
 mergeSliceKernel(const float *__restrict__ pAcc, const float *__restrict__ pM, const float *__restrict__ pL,
                  float *__restrict__ out, uint32_t nHeads, uint32_t numChunks, uint32_t activeHost, uint32_t hd,
                  const uint32_t *__restrict__ devLens, uint32_t lenAdd, uint32_t chunkTokens, uint32_t chunksPerRank,
                  uint64_t rankStride) {
-    constexpr int NW = 8;
+    constexpr int NW = T / 32;
     const uint32_t head = blockIdx.x, s = blockIdx.y, slice = blockIdx.z;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t v4 = threadIdx.x & 7u, cl = threadIdx.x >> 3;
+    constexpr uint32_t CL = T / SL4;  // chunk lanes
+    const uint32_t v4 = threadIdx.x % SL4, cl = threadIdx.x / SL4;
     const uint64_t headRow = static_cast<uint64_t>(s) * nHeads + head;
     auto mlOff = [&](uint32_t c) -> uint64_t {
         if (rankStride == 0) return headRow * numChunks + c;
@@ -230,73 +233,106 @@ mergeSliceKernel(const float *__restrict__ pAcc, const float *__restrict__ pM, c
     }
     __shared__ float sw[kMergeMaxChunks], sl[kMergeMaxChunks];
     __shared__ float sred[NW];
-    __shared__ float4 sacc[NW][8];
+    __shared__ float4 sacc[NW][SL4];
 
-    constexpr int kB = 8;  // 8 x 32 chunk lanes = 256 chunks per batch
+    constexpr int kB = 256 / CL;  // kB x CL chunk lanes = 256 chunks per batch
     float4 a[kB];
     auto loadBatch = [&](uint32_t c0) {
 #pragma unroll
         for (int u = 0; u < kB; ++u) {
-            const uint32_t c = c0 + cl + 32u * u;
-            const uint32_t cc = c < active ? c : (active ? active - 1 : 0);  // always a valid address
-            a[u] = reinterpret_cast<const float4 *>(pAcc + accOff(cc) + 32u * slice)[v4];
+            const uint32_t c = c0 + cl + CL * u;
+            // lanes past the live chunks load nothing (their weight is zero below)
+            if (c0 + CL * u < active) {
+                const uint32_t cc = c < active ? c : active - 1;  // always a valid address
+                a[u] = reinterpret_cast<const float4 *>(pAcc + accOff(cc) + 4u * SL4 * slice)[v4];
+            } else {
+                a[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
     };
     if (active) loadBatch(0);
-    float M = kNegBig;
-    for (uint32_t c = threadIdx.x; c < active; c += 256) {
-        const float m = pM[mlOff(c)];
-        sw[c] = m;
-        sl[c] = pL[mlOff(c)];
-        M = fmaxf(M, m);
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    if (lane == 0) sred[warp] = M;
-    __syncthreads();
-    M = sred[0];
-#pragma unroll
-    for (int w2 = 1; w2 < NW; ++w2) M = fmaxf(M, sred[w2]);
-    __syncthreads();
-    float lsum = 0.0f;
-    for (uint32_t c = threadIdx.x; c < active; c += 256) {
-        const float lc = sl[c];
-        const float w = lc > 0.0f ? exp2f((sw[c] - M) * kLog2e) : 0.0f;
-        sw[c] = w;
-        lsum = fmaf(w, lc > 0.0f ? lc : 0.0f, lsum);
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-    if (lane == 0) sred[warp] = lsum;
-    __syncthreads();  // also publishes the weights
-    lsum = 0.0f;
-#pragma unroll
-    for (int w2 = 0; w2 < NW; ++w2) lsum += sred[w2];
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (uint32_t c0 = 0; c0 < active; c0 += 32u * kB) {
-        if (c0) loadBatch(c0);
+    float lsum = 0.0f;
+    if (active <= 64u) {
+        // Up to 64 chunks (the usual case): every warp works out the maximum, the weights and the row
+        // sum for itself -- lane c holds chunks c and c + 32 -- so nothing goes through shared memory
+        // and no block-wide barrier stands between the loads and the weighted sum.
+        float m0 = kNegBig, m1 = kNegBig, l0 = 0.0f, l1 = 0.0f;
+        if (lane < active) m0 = pM[mlOff(lane)], l0 = pL[mlOff(lane)];
+        if (lane + 32u < active) m1 = pM[mlOff(lane + 32u)], l1 = pL[mlOff(lane + 32u)];
+        float M = fmaxf(m0, m1);
 #pragma unroll
-        for (int u = 0; u < kB; ++u) {
-            const uint32_t c = c0 + cl + 32u * u;
-            const float w = c < active ? sw[c < active ? c : 0] : 0.0f;
+        for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float w0 = l0 > 0.0f ? exp2f((m0 - M) * kLog2e) : 0.0f;
+        const float w1 = l1 > 0.0f ? exp2f((m1 - M) * kLog2e) : 0.0f;
+        lsum = fmaf(w0, l0 > 0.0f ? l0 : 0.0f, w1 * (l1 > 0.0f ? l1 : 0.0f));
+#pragma unroll
+        for (int o = 16; o; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+#pragma unroll
+        for (int u = 0; u < static_cast<int>(64u / CL); ++u) {
+            const uint32_t c = cl + CL * u;  // its weight sits in lane c % 32, slot c / 32
+            const float wa = __shfl_sync(0xffffffffu, w0, c & 31u), wb = __shfl_sync(0xffffffffu, w1, c & 31u);
+            const float w = c < 32u ? wa : wb;
             const float4 v = w != 0.0f ? a[u] : make_float4(0.f, 0.f, 0.f, 0.f);  // empty chunk: select, never multiply
             acc.x = fmaf(w, v.x, acc.x);
             acc.y = fmaf(w, v.y, acc.y);
             acc.z = fmaf(w, v.z, acc.z);
             acc.w = fmaf(w, v.w, acc.w);
         }
-    }
-    // a warp holds 4 chunk lanes x 8 float4: fold the chunk lanes, then the warps
+    } else {
+        float M = kNegBig;
+        for (uint32_t c = threadIdx.x; c < active; c += T) {
+            const float m = pM[mlOff(c)];
+            sw[c] = m;
+            sl[c] = pL[mlOff(c)];
+            M = fmaxf(M, m);
+        }
 #pragma unroll
-    for (int o = 8; o <= 16; o <<= 1) {
+        for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        if (lane == 0) sred[warp] = M;
+        __syncthreads();
+        M = sred[0];
+#pragma unroll
+        for (int w2 = 1; w2 < NW; ++w2) M = fmaxf(M, sred[w2]);
+        __syncthreads();
+        for (uint32_t c = threadIdx.x; c < active; c += T) {
+            const float lc = sl[c];
+            const float w = lc > 0.0f ? exp2f((sw[c] - M) * kLog2e) : 0.0f;
+            sw[c] = w;
+            lsum = fmaf(w, lc > 0.0f ? lc : 0.0f, lsum);
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+        if (lane == 0) sred[warp] = lsum;
+        __syncthreads();  // also publishes the weights
+        lsum = 0.0f;
+#pragma unroll
+        for (int w2 = 0; w2 < NW; ++w2) lsum += sred[w2];
+        for (uint32_t c0 = 0; c0 < active; c0 += CL * kB) {
+            if (c0) loadBatch(c0);
+#pragma unroll
+            for (int u = 0; u < kB; ++u) {
+                const uint32_t c = c0 + cl + CL * u;
+                const float w = c < active ? sw[c < active ? c : 0] : 0.0f;
+                const float4 v = w != 0.0f ? a[u] : make_float4(0.f, 0.f, 0.f, 0.f);  // empty chunk: select, never multiply
+                acc.x = fmaf(w, v.x, acc.x);
+                acc.y = fmaf(w, v.y, acc.y);
+                acc.z = fmaf(w, v.z, acc.z);
+                acc.w = fmaf(w, v.w, acc.w);
+            }
+        }
+    }  // more than 64 chunks
+    // a warp holds 32 / SL4 chunk lanes x SL4 float4: fold the chunk lanes, then the warps
+#pragma unroll
+    for (int o = SL4; o <= 16; o <<= 1) {
         acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
         acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
         acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
         acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
     }
-    if (lane < 8) sacc[warp][lane] = acc;
+    if (lane < SL4) sacc[warp][lane] = acc;
     __syncthreads();
-    if (threadIdx.x < 8) {
+    if (threadIdx.x < SL4) {
         float4 r = sacc[0][threadIdx.x];
 #pragma unroll
         for (int w2 = 1; w2 < NW; ++w2) {
@@ -307,7 +343,7 @@ mergeSliceKernel(const float *__restrict__ pAcc, const float *__restrict__ pM, c
             r.w += x.w;
         }
         const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
-        reinterpret_cast<float4 *>(out + headRow * hd + 32u * slice)[threadIdx.x] =
+        reinterpret_cast<float4 *>(out + headRow * hd + 4u * SL4 * slice)[threadIdx.x] =
                 make_float4(r.x * inv, r.y * inv, r.z * inv, r.w * inv);
     }
 }
@@ -333,8 +369,16 @@ int launchMerge(const float *pAcc, const float *pM, const float *pL, float *out,
     // 4x as many blocks get in the way (batch 8: 49.4 against 46.1 us; 64 ragged sequences 201 against
     // 190), so a batch keeps the block-per-head form there.
     if (q81 == nullptr && (!pdl || static_cast<uint64_t>(nHeads) * seqLen <= 64u)) {
+        // one sequence: 16-dim slices, twice the blocks (7B shape at 32768 rows: 11.36 us per layer
+        // against 11.67 with 32-dim slices, 11.38 with 8-dim, 12.17 with 4-dim ones)
+        if (static_cast<uint64_t>(nHeads) * seqLen <= 64u) {
+            cfg.gridDim = dim3(nHeads, seqLen, hd / 16u);
+            TC_CUDA_OK(cudaLaunchKernelEx(&cfg, mergeSliceKernel<4, 256>, pAcc, pM, pL, out, nHeads, numChunks, activeHost, hd,
+                                          devLens, lenAdd, chunkTokens, chunksPerRank, rankStride));
+            return TC_OK;
+        }
         cfg.gridDim = dim3(nHeads, seqLen, hd / 32u);
-        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, mergeSliceKernel, pAcc, pM, pL, out, nHeads, numChunks, activeHost, hd,
+        TC_CUDA_OK(cudaLaunchKernelEx(&cfg, mergeSliceKernel<8, 256>, pAcc, pM, pL, out, nHeads, numChunks, activeHost, hd,
                                       devLens, lenAdd, chunkTokens, chunksPerRank, rankStride));
         return TC_OK;
     }
