@@ -308,7 +308,7 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         for (int i = 0; i < 4; ++i) {
             mbarInit(&sFull[i], 1);
-            mbarInit(&pFull[i], 128);
+            mbarInit(&pFull[i], 4);  // one arrival per warp
             mbarInit(&pvBuf[i], 1);
             mbarInit(&itemFull[i], 1);
         }
@@ -622,7 +622,8 @@ prefillF16Kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 l = l * alpha + psum;
                 tmemStWait();
                 tcFenceBefore();
-                mbarArrive(&pFull[2u * x + b]);
+                __syncwarp();
+                if (lane == 0) mbarArrive(&pFull[2u * x + b]);
                 if (row == 0) PF_STAMP(x, j, 2);
                 if (row == 0 && j + 1u == myTiles) PF_BLK(3u + x);
             }
