@@ -866,6 +866,8 @@ def main():
                     help="skip the secondary measurements (`also`) and the sustained replay of the default line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream order between the kernels of a step")
+    ap.add_argument("--e2e-plain-copies", action="store_true",
+                    help="diagnostic: the end-to-end step's host copies issued around its graph, not as nodes of it")
     ap.add_argument("--partials-only", action="store_true", help="diagnostic: skip the merge launch")
     ap.add_argument("--fused-merge", action="store_true",
                     help="merge the chunk partials inside the decode kernel (last-arriving block) instead of a second launch")
@@ -1010,25 +1012,33 @@ def main():
     us_per_layer = ms_per_step * 1e3 / layers
 
     # ---- end to end through the C ABI with HOST buffers ---------------------------
-    # A step: the new token's q, k, v of every layer come from pinned host memory (one
-    # asynchronous copy each), then per layer attention runs with k/v quantised into the last
-    # row by the decode launch itself (the captured launch sequence of the step), and the
-    # step's outputs go back to pinned host memory; the host waits for them.
-    hq = torch.randn((layers, batch, nH, hd)).pin_memory()
-    hk = torch.randn((layers, batch, nKV, hd)).pin_memory()
-    hv = torch.randn((layers, batch, nKV, hd)).pin_memory()
+    # A step: the new token's q, k, v of every layer come from one pinned host buffer (one
+    # asynchronous copy), then per layer attention runs with k/v quantised into the last row by
+    # the decode launch itself, and the step's outputs go back to pinned host memory; the host
+    # waits for them.  The two copies are nodes of the step's captured graph, so a step is one
+    # graph launch and one wait (--e2e-plain-copies: three input copies and the output copy
+    # issued around the graph instead).
+    nq, nk = layers * batch * nH * hd, layers * batch * nKV * hd
+    hin = torch.randn(nq + 2 * nk).pin_memory()
+    din = torch.empty(nq + 2 * nk, device=dev)
+    hq, hk, hv = hin[:nq], hin[nq:nq + nk], hin[nq + nk:]
+    dq = din[:nq].view(layers, batch, nH, hd)
+    dk = din[nq:nq + nk].view(layers, batch, nKV, hd)
+    dv = din[nq + nk:].view(layers, batch, nKV, hd)
     hout = torch.empty((layers, batch, nH, hd)).pin_memory()
-    dq = torch.empty((layers, batch, nH, hd), device=dev)
-    dk = torch.empty((layers, batch, nKV, hd), device=dev)
-    dv = torch.empty((layers, batch, nKV, hd), device=dev)
     dout = torch.empty((layers, batch, nH, hd), device=dev)
+    copies_inside = not args.e2e_plain_copies
 
     def e2e_layers():
+        if copies_inside:
+            din.copy_(hin, non_blocking=True)
         for l in range(layers):
             nxt = None if args.no_next_prefetch else (k8[(l + 1) % layers], v8[(l + 1) % layers])
             ops.decode_i8_batch(dq[l], k8[l], v8[l], ks[l], vs[l], dout[l], ws, lens_arg, batch, nH, nKV, hd, ctx,
                                 chunks, rows_per_seq=rows, invSqrt=inv, pdl=not args.no_pdl, prefetch_rows=ctx - 1,
                                 next_kv=nxt, tickets=tickets, append=(dk[l], dv[l]))
+        if copies_inside:
+            hout.copy_(dout, non_blocking=True)
 
     if args.no_graph:
         e2e_run = e2e_layers
@@ -1046,11 +1056,13 @@ def main():
         e2e_run = g2.replay
 
     def e2e_step():
-        dq.copy_(hq, non_blocking=True)
-        dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True)
+        if not copies_inside:
+            din[:nq].copy_(hq, non_blocking=True)
+            din[nq:nq + nk].copy_(hk, non_blocking=True)
+            din[nq + nk:].copy_(hv, non_blocking=True)
         e2e_run()
-        hout.copy_(dout, non_blocking=True)
+        if not copies_inside:
+            hout.copy_(dout, non_blocking=True)
         torch.cuda.synchronize()
 
     e2e_steps = max(3, min(args.steps, 50))
@@ -1090,7 +1102,10 @@ def main():
                      "note": "algorithmic bytes per layer / (step time / layers); split and merge launches both inside"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms_per_step,
                 "h2d_bytes_per_step": layers * batch * (nH + 2 * nKV) * hd * 4,
-                "d2h_bytes_per_step": layers * batch * nH * hd * 4},
+                "d2h_bytes_per_step": layers * batch * nH * hd * 4,
+                "copies": ("one H2D and one D2H copy from/to pinned memory as nodes of the step's graph"
+                           if copies_inside and not args.no_graph else
+                           "H2D copies before and one D2H copy after the step's launches, from/to pinned memory")},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks, "device_error_flags": dev_flags,
     }
