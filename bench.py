@@ -404,13 +404,11 @@ def run_prefill(args, steps=None, warmup=None, chunk=0, with_cpu=True, with_e2e=
         sampler.start()
     ms_per_step = _time_steps(step, steps, warmup, dev)
     # attention launches alone (the dominant kernel with its fp16 twins), same inputs
-    reps = max(3, min(steps, 20))
-
     def attn_only():
-        for r in range(reps):
-            layer(q[r % layers], k[r % layers], v[r % layers], out[r % layers], r % layers, mirror=False)
+        for l in range(layers):
+            layer(q[l], k[l], v[l], out[l], l, mirror=False)
 
-    kern_ms = _time_steps(attn_only, 1, 1, dev) / reps
+    kern_ms = _time_steps(attn_only, max(3, min(steps, 20)), 3, dev) / layers
     clocks = sampler.stop() if rank == 0 else None
     e2e = None
     if with_e2e:
