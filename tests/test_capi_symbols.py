@@ -39,3 +39,31 @@ def test_invalid_arguments_are_rejected_on_the_host():
     assert capi.lib.tc_attn_workspace_bytes(2, 28, 128, 64, C.byref(a), C.byref(C.c_size_t()),
                                             C.byref(C.c_size_t())) == 0
     assert a.value == 2 * 28 * 64 * 128 * 4
+
+
+def test_prefill_entry_points_check_their_arguments_on_the_host():
+    lib = capi.lib
+    n = C.c_size_t()
+    al = lambda x: (x + 1023) & ~1023
+    # q twin + K and V twins of every cached row (1 KB aligned each) + 1 KB for the work counter
+    for hd in (64, 128, 256):
+        assert lib.tc_attn_prefill_f16_scratch_bytes(512, 1024, 28, 4, hd, C.byref(n)) == 0
+        assert n.value == al(512 * 28 * hd * 2) + 2 * al(1536 * 4 * hd * 2) + 1024
+    assert lib.tc_attn_prefill_f16_scratch_bytes(512, 0, 28, 4, 96, C.byref(n)) == capi.TC_EUNSUPPORTED
+    assert lib.tc_attn_prefill_f16_scratch_bytes(512, 0, 28, 4, 128, None) == capi.TC_EINVAL
+    # fake, suitably aligned addresses: every check below fails before anything is dereferenced or launched
+    p = C.c_void_p(1 << 20)
+    args = (p, p, p, p, p, 1 << 30, 512, 0, 28, 4, 128, 0.088, None)
+    assert lib.tc_attn_prefill_f16(None, p, p, p, p, 1 << 30, 512, 0, 28, 4, 128, 0.088, None) == capi.TC_EINVAL
+    assert lib.tc_attn_prefill_f16(p, p, p, p, p, 1 << 30, 512, 0, 28, 4, 96, 0.088, None) == capi.TC_EUNSUPPORTED
+    assert lib.tc_attn_prefill_f16(p, p, p, p, p, 1 << 30, 512, 0, 28, 5, 128, 0.088, None) == capi.TC_EINVAL
+    assert lib.tc_attn_prefill_f16(p, p, p, p, C.c_void_p((1 << 20) + 8), 1 << 30, 512, 0, 28, 4, 128, 0.088,
+                                   None) == capi.TC_EINVAL                       # misaligned scratch
+    assert lib.tc_attn_prefill_f16(p, p, p, p, p, 4096, 512, 0, 28, 4, 128, 0.088, None) == capi.TC_EWORKSPACE
+    assert lib.tc_attn_prefill_f16(p, p, p, p, p, 1 << 30, 0, 0, 28, 4, 128, 0.088, None) == 0   # no rows: nothing to do
+    # the int8 store needs its scales, the mirror its pool, and the mirror's rows have to fit the pool
+    assert lib.tc_attn_prefill_f16_i8(p, p, p, None, None, p, p, 1 << 30, 512, 0, 28, 4, 128, 0.088,
+                                      None) == capi.TC_EINVAL
+    assert lib.tc_attn_prefill_f16_kv8(*args[:12], None, p, p, p, 0, 4096, None) == capi.TC_EINVAL
+    assert lib.tc_attn_prefill_f16_kv8(*args[:12], p, p, p, p, 4000, 4096 + 16, None) == capi.TC_ECONTEXT_FULL
+    assert b"pass the pool" in lib.tc_last_error()
