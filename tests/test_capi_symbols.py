@@ -67,3 +67,31 @@ def test_prefill_entry_points_check_their_arguments_on_the_host():
     assert lib.tc_attn_prefill_f16_kv8(*args[:12], None, p, p, p, 0, 4096, None) == capi.TC_EINVAL
     assert lib.tc_attn_prefill_f16_kv8(*args[:12], p, p, p, p, 4000, 4096 + 16, None) == capi.TC_ECONTEXT_FULL
     assert b"pass the pool" in lib.tc_last_error()
+
+
+def test_decode_batch_descriptor_is_checked_on_the_host():
+    lib = capi.lib
+    p = 1 << 20   # a fake, aligned address: every check below fails before anything is dereferenced or launched
+
+    def desc(**kw):
+        d = capi.DecodeI8Batch()
+        for f in ("q", "out", "k8", "v8", "ks", "vs", "pAcc", "pM", "pL"):
+            setattr(d, f, p)
+        d.rowsPerSeq, d.totalRows, d.batch, d.nHeads, d.nKV, d.hd = 4096, 4096, 1, 28, 4, 128
+        d.maxLen, d.numChunks, d.invSqrt = 4096, 64, 0.088
+        for k, v in kw.items():
+            setattr(d, k, v)
+        return d
+
+    call = lambda d: lib.tc_attn_decode_i8_batch(C.byref(d), None)
+    assert call(desc(q=None)) == capi.TC_EINVAL
+    assert call(desc(hd=96)) == capi.TC_EUNSUPPORTED
+    assert call(desc(nKV=5)) == capi.TC_EINVAL
+    assert call(desc(batch=0)) == capi.TC_EINVAL
+    assert call(desc(maxLen=0)) == capi.TC_EINVAL
+    assert call(desc(totalRows=1 << 31)) == capi.TC_EUNSUPPORTED
+    assert call(desc(k8=p + 4)) == capi.TC_EINVAL                 # misaligned pool
+    assert call(desc(numChunks=0)) == capi.TC_EWORKSPACE
+    # the rows of a new token come as a pair
+    assert call(desc(appendK=p)) == capi.TC_EINVAL and b"come together" in lib.tc_last_error()
+    assert call(desc(appendV=p)) == capi.TC_EINVAL
